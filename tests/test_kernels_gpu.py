@@ -1,0 +1,360 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+BF16 = torch.bfloat16
+
+
+def _F():
+    from tileinfer_b200.ops import functional as F
+    F.L()
+    return F
+
+
+def _rand_w(n, k, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(n, k, device="cuda", generator=g) * 0.05).to(BF16).float()
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 16, 37])
+@pytest.mark.parametrize("N,K", [(1552, 384), (5120, 2176), (8192, 5120)])
+@pytest.mark.parametrize("quant", [True, False])
+def test_gemv_store(M, N, K, quant):
+    F = _F()
+    w = _rand_w(N, K, seed=N + K)
+    W = F.LinearW(w, quant)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(BF16)
+    ws = F.GemvWorkspace()
+    y = F.gemv(W, x, ws=ws)
+    ref = x.float() @ W.dense().float().t()
+    torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
+    # split-k counters must be back at zero for the next launch
+    assert int(ws.counters.abs().sum()) == 0
+    y2 = F.gemv(W, x, ws=ws)
+    assert torch.equal(y, y2), "deterministic across launches"
+
+
+@pytest.mark.parametrize("M", [1, 5, 16])
+def test_gemv_norm_prologue_and_swiglu(M):
+    F = _F()
+    H, I = 5120, 2176
+    w = _rand_w(2 * I, H, seed=3)
+    W = F.LinearW(w, True)
+    h = (torch.randn(M, H, device="cuda") * 2).to(BF16)
+    nw = (torch.randn(H, device="cuda") * 0.1).to(BF16)
+    ws = F.GemvWorkspace()
+    act = F.gemv(W, h, xmode=F.XNORM, epi=F.EPI_SWIGLU, norm_w=nw, ws=ws)
+    hf = h.float()
+    xn = (hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + nw.float())).to(BF16).float()
+    gu = (xn @ W.dense().float().t()).to(BF16).float()
+    ref = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]
+    torch.testing.assert_close(act.float(), ref, rtol=3e-2, atol=3e-2)
+
+
+def test_gemv_rowpar_residual_tp1_and_f32():
+    F = _F()
+    N, K, M = 5120, 768, 4
+    W = F.LinearW(_rand_w(N, K, seed=5), True)
+    x = (torch.randn(M, K, device="cuda")).to(BF16)
+    r = (torch.randn(M, N, device="cuda")).to(BF16)
+    ws = F.GemvWorkspace()
+    out = F.gemv(W, x, epi=F.EPI_ROWPAR, resid=r, ws=ws)
+    ref = r.float() + x.float() @ W.dense().float().t()
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=3e-2)
+    lg = F.gemv(W, x, epi=F.EPI_F32, ws=ws)
+    torch.testing.assert_close(lg, x.float() @ W.dense().float().t(), rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("tp", [2, 4])
+def test_gemv_rowpar_allreduce_emulated_ranks(tp):
+    """All ranks of a TP group emulated on ONE GPU inside one cooperative launch: the tagged-packet
+    all-reduce in the GEMV epilogue must equal the sum of the per-rank partial products."""
+    import ctypes
+    F = _F()
+    from tileinfer_b200.ops.lib import GemvParams
+    from tileinfer_b200.parallel.symm_mem import LocalRanks
+    N, Kfull, M = 5120, 2048, 3
+    K = Kfull // tp
+    wfull = _rand_w(N, Kfull, seed=7)
+    x = (torch.randn(M, Kfull, device="cuda")).to(BF16)
+    resid = (torch.randn(M, N, device="cuda")).to(BF16)
+    ranks = LocalRanks(tp, N, m_cap=16)
+    ncta = 148 // tp
+    Ws, outs, params, keep = [], [], [], []
+    for r in range(tp):
+        W = F.LinearW(wfull[:, r * K:(r + 1) * K].contiguous(), True)
+        xr = x[:, r * K:(r + 1) * K].contiguous()
+        out = torch.zeros(M, N, dtype=BF16, device="cuda")
+        ws = F.GemvWorkspace()
+        p = F.make_gemv_params(W, xr, out, M, epi=F.EPI_ROWPAR, resid=resid, ws=ws, comm=ranks.view(r), order=0, ncta=ncta)
+        Ws.append(W); outs.append(out); params.append(p); keep.append((xr, ws))
+    size = ctypes.sizeof(GemvParams)
+    blob = b"".join(bytes(p) for p in params)
+    dev_params = torch.frombuffer(bytearray(blob), dtype=torch.uint8).cuda()
+    rc = F.L().ti_gemv_ranks(ctypes.byref(params[0]), dev_params.data_ptr(), tp, F.W_INT8, F.XGLOBAL, F.EPI_ROWPAR, ncta,
+                             torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(ranks.ctrl[1]) == 0, "no peer wait may time out"
+    ref = resid.float()
+    for r in range(tp):
+        ref = ref + x[:, r * K:(r + 1) * K].float() @ Ws[r].dense().float().t()
+    for r in range(tp):
+        torch.testing.assert_close(outs[r].float(), ref, rtol=2e-2, atol=3e-2)
+        assert torch.equal(outs[r], outs[0]), "every rank must hold bit-identical results"
+    assert size * tp == dev_params.numel()
+
+
+def test_bounded_wait_reports_timeout_and_context_survives():
+    F = _F()
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    result = torch.full((1,), 7, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    # nothing ever sets the flag: the wait must give up after its 20 ms budget
+    assert F.L().ti_wait_flag_probe(flag.data_ptr(), 1, 20_000_000, status.data_ptr(), result.data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    assert int(result) == 0 and int(status) & 1
+    flag.fill_(5)
+    status.zero_()
+    assert F.L().ti_wait_flag_probe(flag.data_ptr(), 3, 20_000_000, status.data_ptr(), result.data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    assert int(result) == 1 and int(status) == 0
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0
+
+
+def test_pointwise():
+    F = _F()
+    M, H = 5, 5120
+    x = torch.randn(M, H, device="cuda").to(BF16)
+    a = torch.randn(M, H, device="cuda").to(BF16)
+    w = (torch.randn(H, device="cuda") * 0.1).to(BF16)
+    y = F.rmsnorm(x, w, 1e-6)
+    xf = x.float()
+    ref = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + w.float())
+    torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
+    r = torch.empty_like(x)
+    y = F.rmsnorm(x, w, 1e-6, add=a, r_out=r)
+    s = (x.float() + a.float()).to(BF16)
+    assert torch.equal(r, s)
+    sf = s.float()
+    torch.testing.assert_close(y.float(), sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + w.float()),
+                               rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(F.act_mul(x, a, mode=0).float(), torch.nn.functional.silu(x.float()) * a.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(F.act_mul(x, a, mode=1).float(), x.float() * torch.sigmoid(a.float()), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(F.swiglu_interleaved(x).float(),
+                               torch.nn.functional.silu(x.float()[:, 0::2]) * x.float()[:, 1::2], rtol=2e-2, atol=2e-2)
+    table = torch.randn(100, H, device="cuda").to(BF16)
+    ids = torch.tensor([3, 99, 0, 7, 50], device="cuda")
+    out = torch.empty(M, H, dtype=BF16, device="cuda")
+    step = torch.zeros(1, dtype=torch.int32, device="cuda")
+    F.embed(ids, table, out, step.data_ptr())
+    assert torch.equal(out, table[ids]) and int(step) == 1
+
+
+@pytest.mark.parametrize("dk,hk,hv,state_bf16", [(128, 2, 6, False), (64, 4, 8, False), (128, 2, 6, True)])
+def test_gdn_step_matches_recurrence(dk, hk, hv, state_bf16):
+    from tileinfer_b200.models.reference_cpu import gdn_recurrent, l2norm, rmsnorm, softplus20
+    F = _F()
+    torch.manual_seed(0)
+    dv = dk
+    lens = [1, 7, 33]
+    S, T = len(lens), sum(lens)
+    nch = 2 * dk + dv
+    kd, vd = hk * dk, hv * dv
+    ld = 2 * kd + 2 * vd + 2 * hv + 6
+    proj = (torch.randn(T, ld, device="cuda")).to(BF16)
+    conv_w = torch.randn(2 * kd + vd, 4, device="cuda") * 0.5
+    A_log = torch.randn(hv, device="cuda") * 0.5
+    dt_bias = torch.randn(hv, device="cuda") * 0.5
+    norm_w = 1 + 0.1 * torch.randn(dv, device="cuda")
+    slots = torch.tensor([2, 0, 3], dtype=torch.int32, device="cuda")
+    sdt = BF16 if state_bf16 else torch.float32
+    state = (torch.randn(4, hv, dk, dv, device="cuda") * 0.1).to(sdt)
+    hist = (torch.randn(4, 3, 2 * kd + vd, device="cuda")).to(BF16)      # logical conv history per slot
+    # kernel layout: every v-head keeps [q of its k-head | k of its k-head | its v] history
+    rep = hv // hk
+    cs = torch.zeros(4, hv, 3, nch, dtype=BF16, device="cuda")
+    for vh in range(hv):
+        kh = vh // rep
+        cs[:, vh, :, :dk] = hist[:, :, kh * dk:(kh + 1) * dk]
+        cs[:, vh, :, dk:2 * dk] = hist[:, :, kd + kh * dk:kd + (kh + 1) * dk]
+        cs[:, vh, :, 2 * dk:] = hist[:, :, 2 * kd + vh * dv:2 * kd + (vh + 1) * dv]
+    state0, cs0 = state.clone(), cs.clone()
+    cu = torch.tensor([0, 1, 8, 41], dtype=torch.int32, device="cuda")
+    out = torch.zeros(T, vd, dtype=BF16, device="cuda")
+    snap_rel = torch.tensor([[0], [3], [16]], dtype=torch.int32, device="cuda")
+    snap_state = torch.zeros(S, 1, hv, dk, dv, device="cuda")
+    snap_conv = torch.zeros(S, 1, hv, 3, nch, dtype=BF16, device="cuda")
+    p = F.GdnParams()
+    p.proj, p.conv_w, p.neg_a_exp = proj.data_ptr(), conv_w.data_ptr(), (-A_log.exp()).contiguous().data_ptr()
+    neg = (-A_log.exp()).contiguous()
+    p.neg_a_exp, p.dt_bias, p.norm_w = neg.data_ptr(), dt_bias.data_ptr(), norm_w.data_ptr()
+    p.state, p.conv_state, p.slots, p.cu, p.out = state.data_ptr(), cs.data_ptr(), slots.data_ptr(), cu.data_ptr(), out.data_ptr()
+    p.snap_rel, p.snap_state, p.snap_conv, p.num_snap = snap_rel.data_ptr(), snap_state.data_ptr(), snap_conv.data_ptr(), 1
+    p.ld, p.hk, p.hv, p.eps = ld, hk, hv, 1e-6
+    F.gdn_step(p, S, dk, dv, state_bf16)
+    torch.cuda.synchronize()
+    tol = dict(rtol=3e-2, atol=3e-2)
+    for s in range(S):
+        t0, t1, slot = int(cu[s]), int(cu[s + 1]), int(slots[s])
+        raw = proj[t0:t1, :2 * kd + vd].float()
+        seq = torch.cat([hist[slot].float(), raw], 0)
+        conv = torch.nn.functional.silu((seq.unfold(0, 4, 1) * conv_w[None]).sum(-1))
+        Tn = t1 - t0
+        q = l2norm(conv[:, :kd].reshape(Tn, hk, dk)).repeat_interleave(rep, 1) * dk ** -0.5
+        k = l2norm(conv[:, kd:2 * kd].reshape(Tn, hk, dk)).repeat_interleave(rep, 1)
+        v = conv[:, 2 * kd:].reshape(Tn, hv, dv)
+        z = proj[t0:t1, 2 * kd + vd:2 * kd + 2 * vd].float().reshape(Tn, hv, dv)
+        b = proj[t0:t1, 2 * kd + 2 * vd:2 * kd + 2 * vd + hv].float()
+        a = proj[t0:t1, 2 * kd + 2 * vd + hv:2 * kd + 2 * vd + 2 * hv].float()
+        g = -A_log.exp()[None] * softplus20(a + dt_bias[None])
+        o, Sn = gdn_recurrent(q, k, v, g, torch.sigmoid(b), state0[slot].float())
+        ref = rmsnorm(o, norm_w, 1e-6, one_plus=False) * torch.nn.functional.silu(z)
+        torch.testing.assert_close(out[t0:t1].float(), ref.reshape(Tn, vd), **tol)
+        torch.testing.assert_close(state[slot].float(), Sn, **tol)
+        # conv history afterwards = last three raw inputs
+        last3 = seq[-3:]
+        torch.testing.assert_close(cs[slot, 0, :, :dk].float(), last3[:, :dk], rtol=0, atol=1e-2)
+        torch.testing.assert_close(cs[slot, hv - 1, :, 2 * dk:].float(), last3[:, 2 * kd + (hv - 1) * dv:], rtol=0, atol=1e-2)
+        n = int(snap_rel[s, 0])
+        if n > 0:
+            _, Ssnap = gdn_recurrent(q[:n], k[:n], v[:n], g[:n], torch.sigmoid(b)[:n], state0[slot].float())
+            torch.testing.assert_close(snap_state[s, 0], Ssnap, **tol)
+    # untouched slot stays untouched
+    assert torch.equal(state[1], state0[1]) and torch.equal(cs[1], cs0[1])
+
+
+@pytest.mark.parametrize("D,hq,hkv,rot", [(256, 6, 1, 64), (64, 6, 1, 16), (128, 8, 2, 32), (256, 3, 1, 64)])
+def test_paged_attention_prefill_and_decode(D, hq, hkv, rot):
+    from tileinfer_b200.models.reference_cpu import rmsnorm, rope_partial
+    F = _F()
+    torch.manual_seed(1)
+    G = hq // hkv
+    nb = 64
+    theta = 1e7
+    # sequence 0: prefill of 37 tokens after 20 cached; sequence 1: decode token at context 70; sequence 2: prefill of 5 from scratch
+    ctx0, lens = [20, 69, 0], [37, 1, 5]
+    S, T = 3, sum(lens)
+    ld = hq * 2 * D + 2 * hkv * D
+    qn = (torch.randn(D, device="cuda") * 0.1).to(BF16)
+    kn = (torch.randn(D, device="cuda") * 0.1).to(BF16)
+    kcache = torch.zeros(nb, hkv, 16, D, dtype=BF16, device="cuda")
+    vcache = torch.zeros(nb, hkv, D, 16, dtype=BF16, device="cuda")
+    perm = torch.randperm(nb).tolist()
+    tables = [perm[0:8], perm[8:16], perm[16:24]]
+    maxb = 8
+
+    def run(proj, positions, slot_mapping, qg, num_qg, nsplit, Tn):
+        qbuf = torch.zeros(Tn, hq, D, dtype=BF16, device="cuda")
+        q = F.QkvPrepParams()
+        q.proj, q.q_norm, q.k_norm, q.positions, q.slot_mapping = proj.data_ptr(), qn.data_ptr(), kn.data_ptr(), positions.data_ptr(), slot_mapping.data_ptr()
+        q.q_out, q.kcache, q.vcache = qbuf.data_ptr(), kcache.data_ptr(), vcache.data_ptr()
+        q.ld, q.hq, q.hkv, q.rotary_dim, q.eps, q.log2_theta = ld, hq, hkv, rot, 1e-6, math.log2(theta)
+        F.qkv_prep(q, Tn, D)
+        bt = torch.zeros(S, maxb, dtype=torch.int32)
+        for s in range(S):
+            bt[s] = torch.tensor(tables[s], dtype=torch.int32)
+        bt = bt.cuda()
+        items = num_qg * hkv * nsplit
+        o_part = torch.empty(items * 16 * D, device="cuda")
+        ml = torch.empty(items * 32, device="cuda")
+        out = torch.zeros(Tn, hq * D, dtype=BF16, device="cuda")
+        a = F.AttnParams()
+        a.q, a.kcache, a.vcache, a.block_tables, a.positions = qbuf.data_ptr(), kcache.data_ptr(), vcache.data_ptr(), bt.data_ptr(), positions.data_ptr()
+        a.qg_seq, a.qg_tok0, a.qg_ntok = qg[0].data_ptr(), qg[1].data_ptr(), qg[2].data_ptr()
+        a.o_part, a.ml_part, a.gate_src, a.out = o_part.data_ptr(), ml.data_ptr(), proj.data_ptr(), out.data_ptr()
+        a.hq, a.hkv, a.max_blocks, a.nsplit, a.ld, a.num_qg = hq, hkv, maxb, nsplit, ld, num_qg
+        a.scale_log2e = D ** -0.5 * 1.4426950408889634
+        F.attn_paged(a, D)
+        torch.cuda.synchronize()
+        return out, qbuf
+
+    def slot(s, pos):
+        return tables[s][pos // 16] * 16 + pos % 16
+
+    # reference K/V history (full precision path on the same bf16 inputs)
+    hist_k = [[] for _ in range(S)]
+    hist_v = [[] for _ in range(S)]
+
+    def ref_step(proj, seqs, starts, ns):
+        outs = []
+        t = 0
+        for s, st, n in zip(seqs, starts, ns):
+            rows = proj[t:t + n].float()
+            pos = torch.arange(st, st + n, device="cuda")
+            qg_ = rows[:, :hq * 2 * D].reshape(n, hq, 2 * D)
+            qq, gate = qg_[..., :D], qg_[..., D:].reshape(n, hq * D)
+            kk = rows[:, hq * 2 * D:hq * 2 * D + hkv * D].reshape(n, hkv, D)
+            vv = rows[:, hq * 2 * D + hkv * D:].reshape(n, hkv, D)
+            qq = rope_partial(rmsnorm(qq, qn, 1e-6).to(BF16).float(), pos, rot, theta).to(BF16).float()
+            kk = rope_partial(rmsnorm(kk, kn, 1e-6).to(BF16).float(), pos, rot, theta).to(BF16).float()
+            hist_k[s].append(kk); hist_v[s].append(vv.to(BF16).float())
+            K = torch.cat(hist_k[s]); V = torch.cat(hist_v[s])
+            L = K.shape[0]
+            sc = torch.einsum("tkgd,lkd->tkgl", qq.reshape(n, hkv, G, D), K) * D ** -0.5
+            mask = torch.arange(L, device="cuda")[None] > pos[:, None]
+            pr = torch.softmax(sc.masked_fill(mask[:, None, None], float("-inf")), -1)
+            o = torch.einsum("tkgl,lkd->tkgd", pr, V).reshape(n, hq * D) * torch.sigmoid(gate)
+            outs.append(o)
+            t += n
+        return torch.cat(outs)
+
+    gt = 2 if G * 2 <= 16 else 1
+    # step A: fill the caches of sequences 0 and 1 with their context (as one prefill each)
+    nsA = [ctx0[0], ctx0[1]]
+    TA = sum(nsA)
+    projA = (torch.randn(TA, ld, device="cuda")).to(BF16)
+    posA = torch.tensor(list(range(nsA[0])) + list(range(nsA[1])), dtype=torch.int32, device="cuda")
+    slotsA = torch.tensor([slot(0, p) for p in range(nsA[0])] + [slot(1, p) for p in range(nsA[1])], dtype=torch.long, device="cuda")
+    qgA = [[], [], []]
+    t = 0
+    for s, n in zip([0, 1], nsA):
+        for a0 in range(t, t + n, gt):
+            qgA[0].append(s); qgA[1].append(a0); qgA[2].append(min(gt, t + n - a0))
+        t += n
+    qgA = torch.tensor(qgA, dtype=torch.int32, device="cuda")
+    outA, _ = run(projA, posA, slotsA, qgA, qgA.shape[1], 1, TA)
+    refA = ref_step(projA, [0, 1], [0, 0], nsA)
+    torch.testing.assert_close(outA.float(), refA, rtol=3e-2, atol=3e-2)
+    # step B: mixed batch with split-KV
+    projB = (torch.randn(T, ld, device="cuda")).to(BF16)
+    posB = torch.tensor(sum([list(range(c, c + n)) for c, n in zip(ctx0, lens)], []), dtype=torch.int32, device="cuda")
+    slotsB = torch.tensor(sum([[slot(s, p) for p in range(c, c + n)] for s, (c, n) in enumerate(zip(ctx0, lens))], []),
+                          dtype=torch.long, device="cuda")
+    qgB = [[], [], []]
+    t = 0
+    for s, n in enumerate(lens):
+        for a0 in range(t, t + n, gt):
+            qgB[0].append(s); qgB[1].append(a0); qgB[2].append(min(gt, t + n - a0))
+        t += n
+    qgB[0].append(0); qgB[1].append(0); qgB[2].append(0)      # a padding group is skipped
+    qgB = torch.tensor(qgB, dtype=torch.int32, device="cuda")
+    outB, _ = run(projB, posB, slotsB, qgB, qgB.shape[1], 3, T)
+    refB = ref_step(projB, [0, 1, 2], ctx0, lens)
+    torch.testing.assert_close(outB.float(), refB, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("k", [1, 50, 64])
+def test_topk(k):
+    F = _F()
+    torch.manual_seed(2)
+    M, V = 5, 31040
+    logits = torch.randn(M, V, device="cuda")
+    logits[0, 17] = logits[0, 4000] = 9.0        # tie: the smaller token id wins
+    from tileinfer_b200.models.hybrid_b200 import _RunMixin
+
+    class Dummy(_RunMixin):
+        pass
+    d = Dummy()
+    d.v_local, d.dev, d.vocab_start, d.tp, d.rank, d.peer, d._launches = V, torch.device("cuda"), 1000, 1, 0, None, 0
+    vals, idx = d._topk_rows(logits, M, k)
+    torch.cuda.synchronize()
+    rv, ri = torch.topk(logits, k, dim=-1)
+    torch.testing.assert_close(vals, rv)
+    assert int(idx[0, 0]) == 1017
+    assert torch.equal(idx[1:].long() - 1000, ri[1:])

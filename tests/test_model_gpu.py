@@ -1,0 +1,92 @@
+"""Tiny hybrid model on the GPU path against the fp32 CPU oracle, plus the engine end to end."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _prompt(n, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, 1023, (n,), generator=g).tolist()
+
+
+def _near_greedy(tokens, prompt, quant, slack=0.06):
+    """Every generated token must be (nearly) the oracle's arg-max given the same history."""
+    from tileinfer_b200.models.config import TINY_HYBRID
+    from tileinfer_b200.models.reference_cpu import naive_logits
+    from tileinfer_b200.models.weights import RandomWeights
+    full = list(prompt) + list(tokens)
+    lg = naive_logits(TINY_HYBRID, RandomWeights(TINY_HYBRID, 0), full, quant=quant)
+    worst = 0.0
+    for i, t in enumerate(tokens):
+        row = lg[len(prompt) - 1 + i]
+        worst = max(worst, float(row.max() - row[t]))
+    assert worst <= slack, f"token off the oracle arg-max by {worst}"
+
+
+@pytest.mark.parametrize("quant", ["bf16", "w8a16"])
+def test_forward_logits_match_oracle(quant):
+    from tileinfer_b200.models.config import TINY_HYBRID
+    from tileinfer_b200.models.hybrid_b200 import B200HybridModel
+    from tileinfer_b200.models.reference_cpu import Batch, naive_logits
+    from tileinfer_b200.models.weights import RandomWeights
+    src = RandomWeights(TINY_HYBRID, 0)
+    p = _prompt(45)
+    ref = naive_logits(TINY_HYBRID, src, p, quant="w8a16" if quant == "w8a16" else "none")
+    m = B200HybridModel(TINY_HYBRID, src, quant=quant)
+    m.alloc_cache(16, 16, 3)
+    table = [9, 3, 12]
+    slots = torch.tensor([table[i // 16] * 16 + i % 16 for i in range(len(p))])
+    ids = torch.tensor(p)
+    # chunk 1 (32 tokens), chunk 2 (12 tokens), then one decode token: three different code paths
+    cuts = [(0, 32), (32, 44), (44, 45)]
+    for a, b in cuts:
+        h = m.forward(Batch(ids[a:b], torch.arange(a, b), [0, b - a], [b], [table], slots[a:b], [1]))
+        lg = m.logits(h)[0].float().cpu()
+        err = float((lg - ref[b - 1]).abs().max())
+        assert err < 0.05, f"logits error {err} after tokens [{a},{b})"
+    assert m.peer_status() == 0
+
+
+@pytest.mark.parametrize("quant,eager", [("w8a16", False), ("w8a16", True), ("bf16", False)])
+def test_engine_gpu_generate(quant, eager):
+    from tileinfer_b200.engine.llm import LLM
+    from tileinfer_b200.engine.sampling_params import SamplingParams
+    llm = LLM("preset:tiny-hybrid", quantization=quant, enforce_eager=eager, num_kvcache_blocks=128, max_num_seqs=8,
+              max_model_len=512, max_prefill_chunk_tokens=32)
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    prompts = [_prompt(17, 1), _prompt(70, 2), _prompt(5, 3)]
+    outs = llm.generate_token_ids(prompts, sp)
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12
+        _near_greedy(o, p, quant="w8a16" if quant == "w8a16" else "none")
+    if not eager:
+        assert llm.model_runner.model.launches_per_decode_step > 0
+    # sampling path (top-k candidates on the device, seeded draw on the host)
+    sp2 = SamplingParams(temperature=0.8, top_k=20, max_tokens=8, ignore_eos=True)
+    o2 = llm.generate_token_ids([prompts[0]], sp2)[0]
+    assert len(o2) == 8 and all(0 <= t < 1024 for t in o2)
+    # constrained path (full logits on the host)
+    sp3 = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True, allowed_token_ids=[5, 6, 7])
+    assert set(llm.generate_token_ids([prompts[0]], sp3)[0]) <= {5, 6, 7}
+
+
+def test_prefix_reuse_and_swap_on_gpu():
+    from tileinfer_b200.engine.llm import LLM
+    from tileinfer_b200.engine.sampling_params import SamplingParams
+    llm = LLM("preset:tiny-hybrid", quantization="w8a16", num_kvcache_blocks=40, max_num_seqs=4, max_model_len=512,
+              prefix_state_stride=16, swap_space_bytes=64 << 20)
+    sp = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True)
+    shared = _prompt(48, 5)
+    a = llm.generate_token_ids([shared + _prompt(9, 6)], sp)[0]
+    b = llm.generate_token_ids([shared + _prompt(9, 6)], sp)[0]          # full prefix hit
+    st = llm.stats()
+    assert st["prefix_hits"] >= 1 and st["prefix_hit_tokens"] >= 48
+    _near_greedy(b, shared + _prompt(9, 6), "w8a16")
+    # memory pressure: 4 sequences x (up to 9 blocks) > 40 blocks -> preemption by swapping
+    prompts = [_prompt(100, 10 + i) for i in range(4)]
+    outs = llm.generate_token_ids(prompts, SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True))
+    st = llm.stats()
+    assert st["preemptions"] >= 1 and st["swaps_out"] >= 1 and st["swaps_in"] >= 1
+    for p, o in zip(prompts, outs):
+        _near_greedy(o, p, "w8a16")

@@ -1,0 +1,527 @@
+"""The hybrid model on one B200 (one tensor-parallel rank): weights in kernel layout, KV / DeltaNet
+pools, the fused decode step (CUDA-graph captured) and the variable-length prefill / mixed step.
+
+Replaces the reference's patched HuggingFace layers (model/qwen_36.py:242-1147) and the device half of
+its ModelRunner (engine/model_runner.py:135-498).  Per decoder layer the decode step launches
+
+  DeltaNet:   in_proj GEMV [RMSNorm fused in]  ->  gdn step (conv + delta rule + gated norm, in place)
+              -> out_proj GEMV [all-reduce + residual fused in]
+  attention:  qkv GEMV [RMSNorm fused in] -> qk-norm + RoPE + KV store -> paged attention (+ merge, gate)
+              -> o_proj GEMV [all-reduce + residual fused in]
+  MLP:        gate_up GEMV [RMSNorm in, SwiGLU out] -> down GEMV [all-reduce + residual fused in]
+
+i.e. 5-7 launches and no separate collective, against 12-14 launches plus two NCCL all-reduces in the
+reference (model/qwen_36.py:710-809, 939-1133).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..ops import functional as F
+from ..ops.functional import (EPI_F32, EPI_ROWPAR, EPI_STORE, EPI_SWIGLU, XGLOBAL, XNORM, AttnParams, GdnParams,
+                              GemvWorkspace, LinearW, QkvPrepParams, TopkParams, ptr)
+from .config import ModelConfig
+from .weights import ShardSpec, shard_layer
+
+BF16 = torch.bfloat16
+
+
+class _Layer:
+    pass
+
+
+class _ModelBase:
+    def __init__(self, cfg: ModelConfig, src, *, quant="w8a16", tp=1, rank=0, comm=None, config=None):
+        assert torch.cuda.is_available(), "B200HybridModel needs a CUDA device"
+        F.L()   # load (or build) the kernel library now: fail loudly if it is missing
+        self.cfg, self.tp, self.rank, self.comm = cfg, tp, rank, comm
+        self.dev = torch.device("cuda", torch.cuda.current_device())
+        cfg.validate_tp(tp)
+        self.quant = quant
+        self.state_bf16 = bool(config is not None and config.gdn_state_dtype == "bf16")
+        self.fused = True if config is None else bool(config.fused_collectives)
+        q8 = quant == "w8a16"
+        c = cfg
+        self.hq = c.num_q_heads // tp
+        self.hkv = c.kv_heads_per_rank(tp)
+        self.hk = c.gdn_num_k_heads // tp
+        self.hv = c.gdn_num_v_heads // tp
+        self.D, self.dk, self.dv = c.head_dim, c.gdn_head_k_dim, c.gdn_head_v_dim
+        self.H = c.hidden_size
+        self.I = c.intermediate_size // tp
+        self.nch = 2 * self.dk + self.dv
+        assert (self.dk, self.dv) in ((128, 128), (64, 64)), "gdn kernel instances: 128x128 and 64x64"
+        assert self.D in (64, 128, 256)
+        sh = ShardSpec(tp, rank)
+        dev = self.dev
+        self.layers = []
+        for i in range(c.num_layers):
+            lw = shard_layer(c, src, i, sh)
+            L = _Layer()
+            L.is_gdn = c.is_gdn(i)
+            L.input_norm = lw["input_norm"].to(dev, BF16).contiguous()
+            L.post_norm = lw["post_norm"].to(dev, BF16).contiguous()
+            L.gate_up = LinearW(lw["gate_up"], q8, dev)
+            L.down = LinearW(lw["down"], q8, dev)
+            if L.is_gdn:
+                L.in_proj = LinearW(lw["in_proj"], q8, dev)
+                L.out = LinearW(lw["out"], q8, dev)
+                L.conv_w = lw["conv_w"].to(dev, torch.float32).contiguous()
+                L.neg_a_exp = (-torch.exp(lw["A_log"].float())).to(dev).contiguous()
+                L.dt_bias = lw["dt_bias"].to(dev, torch.float32).contiguous()
+                L.norm_w = lw["norm_w"].to(dev, torch.float32).contiguous()
+            else:
+                L.qkv = LinearW(lw["qkv"], q8, dev)
+                L.o = LinearW(lw["o"], q8, dev)
+                L.q_norm = lw["q_norm"].to(dev, BF16).contiguous()
+                L.k_norm = lw["k_norm"].to(dev, BF16).contiguous()
+            self.layers.append(L)
+            del lw
+        self.embed = src.get("embed").to(dev, BF16).contiguous()
+        self.final_norm = src.get("final_norm").to(dev, BF16).contiguous()
+        head = src.get("lm_head")
+        if tp > 1:
+            assert c.vocab_size % tp == 0
+            vs = c.vocab_size // tp
+            head = head[rank * vs:(rank + 1) * vs]
+            self.vocab_start = rank * vs
+        else:
+            self.vocab_start = 0
+        self.lm_head = LinearW(head, False, dev)
+        self.v_local = self.lm_head.N
+        del head
+        torch.cuda.empty_cache()
+
+        self.ws = GemvWorkspace(dev)
+        self.peer = None
+        if tp > 1 and self.fused:
+            from ..parallel.symm_mem import PeerComm
+            self.peer = PeerComm(comm, self.H, m_cap=64)
+        self.ctrl = self.peer.ctrl if self.peer is not None else torch.zeros(4, dtype=torch.int32, device=dev)
+        self.step_ptr = self.ctrl.data_ptr()
+        self.block_size = 16
+        self.kv = None
+        self.graphs = {}
+        self.snapshots = {}
+        self._order = 0
+        self.host_steps = 0
+        self.proj_cols = max([L.in_proj.N for L in self.layers if L.is_gdn] + [L.qkv.N for L in self.layers if not L.is_gdn])
+        self.mix_cols = max(self.hv * self.dv, self.hq * self.D)
+        self.launches_per_decode_step = 0
+        self._launches = 0
+
+    # ------------------------------------------------------------------ caches
+    def weight_bytes(self) -> int:
+        n = self.lm_head.nbytes()
+        for L in self.layers:
+            for name in ("gate_up", "down", "in_proj", "out", "qkv", "o"):
+                w = getattr(L, name, None)
+                if w is not None:
+                    n += w.nbytes()
+        return n
+
+    def _state_bytes_per_slot(self) -> int:
+        ng = self.cfg.num_gdn_layers
+        return ng * self.hv * (self.dk * self.dv * (2 if self.state_bf16 else 4) + 3 * self.nch * 2)
+
+    def cache_bytes_per_block(self) -> int:
+        return self.cfg.num_attn_layers * 2 * 16 * self.hkv * self.D * 2
+
+    def auto_num_blocks(self, util, block_size, num_slots, max_num_seqs, max_model_len) -> int:
+        free, total = torch.cuda.mem_get_info()
+        budget = free - (1.0 - util) * total - num_slots * self._state_bytes_per_slot() - (2 << 30)
+        n = int(budget // self.cache_bytes_per_block())
+        cap = max_num_seqs * (max_model_len // block_size + 2) + 64
+        n = min(n, cap)
+        if n < max_model_len // block_size + 2:
+            raise RuntimeError(f"not enough GPU memory for one sequence of {max_model_len} tokens ({n} KV blocks)")
+        return n
+
+    def alloc_cache(self, num_blocks: int, block_size: int, num_slots: int):
+        assert block_size == 16
+        c, dev = self.cfg, self.dev
+        na, ng = c.num_attn_layers, c.num_gdn_layers
+        self.num_blocks, self.num_slots = num_blocks, num_slots
+        self.kv = torch.zeros(max(na, 1), 2, num_blocks, self.hkv * 16 * self.D, dtype=BF16, device=dev)
+        sdt = BF16 if self.state_bf16 else torch.float32
+        self.rec = torch.zeros(max(ng, 1), num_slots, self.hv, self.dk, self.dv, dtype=sdt, device=dev)
+        self.conv = torch.zeros(max(ng, 1), num_slots, self.hv, 3, self.nch, dtype=BF16, device=dev)
+
+    def zero_state(self, slot: int):
+        self.rec[:, slot].zero_()
+        self.conv[:, slot].zero_()
+
+    def state_out(self, slot: int):
+        return self.rec[:, slot].float().cpu(), self.conv[:, slot].cpu()
+
+    def state_in(self, slot: int, st):
+        self.rec[:, slot].copy_(st[0].to(self.dev, non_blocking=True))
+        self.conv[:, slot].copy_(st[1].to(self.dev, non_blocking=True))
+
+    def blocks_out(self, block_ids: list):
+        idx = torch.tensor(block_ids, dtype=torch.long, device=self.dev)
+        return self.kv[:, :, idx].cpu()
+
+    def blocks_in(self, block_ids: list, data):
+        idx = torch.tensor(block_ids, dtype=torch.long, device=self.dev)
+        self.kv[:, :, idx] = data.to(self.dev)
+
+    def take_snapshots(self):
+        out, self.snapshots = self.snapshots, {}
+        return out
+
+
+class _Ctx:
+    """Device tensors of one step (static for CUDA-graph buckets, fresh for eager steps)."""
+    snap_rel = None
+    snap_state = None
+    snap_conv = None
+    num_snap = 0
+    cu = None
+
+
+class _StepMixin:
+    # ------------------------------------------------------------------ buffers
+    def _alloc_ctx(self, T: int, S: int, max_blocks: int, num_qg: int, nsplit: int) -> _Ctx:
+        dev, x = self.dev, _Ctx()
+        x.T, x.S, x.max_blocks, x.num_qg, x.nsplit = T, S, max_blocks, num_qg, nsplit
+        x.ids = torch.zeros(T, dtype=torch.long, device=dev)
+        x.positions = torch.zeros(T, dtype=torch.int32, device=dev)
+        x.slot_mapping = torch.full((T,), -1, dtype=torch.long, device=dev)
+        x.slots = torch.zeros(S, dtype=torch.int32, device=dev)
+        x.block_tables = torch.zeros(S, max_blocks, dtype=torch.int32, device=dev)
+        x.qg = torch.zeros(3, max(num_qg, 1), dtype=torch.int32, device=dev)      # seq, tok0, ntok
+        x.h = [torch.zeros(T, self.H, dtype=BF16, device=dev) for _ in range(2)]
+        x.proj = torch.zeros(T, self.proj_cols, dtype=BF16, device=dev)
+        x.mix = torch.zeros(T, self.mix_cols, dtype=BF16, device=dev)
+        x.act = torch.zeros(T, self.I, dtype=BF16, device=dev)
+        if self.cfg.num_attn_layers:
+            x.qbuf = torch.zeros(T, self.hq * self.D, dtype=BF16, device=dev)
+            items = max(num_qg, 1) * self.hkv * nsplit
+            x.o_part = torch.empty(items * 16 * self.D, dtype=torch.float32, device=dev)
+            x.ml_part = torch.empty(items * 32, dtype=torch.float32, device=dev)
+        return x
+
+    # ------------------------------------------------------------------ launches
+    def _gemv(self, W: LinearW, x, out, M, *, xmode, epi, norm_w=None, resid=None, ldo=None):
+        """y = x W^T in row chunks of 16; counts launches; assigns collective order numbers."""
+        for m0 in range(0, M, 16):
+            m = min(16, M - m0)
+            order = 0
+            if epi == EPI_ROWPAR:
+                order = self._order
+                self._order += 1
+            p = F.make_gemv_params(
+                W, x[m0:m0 + m], out[m0:m0 + m], m, xmode=xmode, epi=epi, norm_w=norm_w,
+                resid=None if resid is None else resid[m0:m0 + m], ws=self.ws, eps=self.cfg.rms_eps,
+                ldx=x.stride(0), ldo=out.stride(0) if ldo is None else ldo,
+                comm=self.peer if epi == EPI_ROWPAR else None, order=order)
+            F.gemv_launch(p, W.wt, xmode, epi)
+            self._launches += 1
+
+    def _rowpar(self, W: LinearW, x, resid, out, M):
+        """Row-parallel projection + all-reduce + residual add -> out."""
+        if self.tp == 1 or self.peer is not None:
+            self._gemv(W, x, out, M, xmode=XGLOBAL, epi=EPI_ROWPAR, resid=resid)
+            return
+        # baseline: partial sums in bf16, NCCL all-reduce, separate residual add (the reference's structure)
+        part = torch.empty(M, W.N, dtype=BF16, device=self.dev)
+        self._gemv(W, x, part, M, xmode=XGLOBAL, epi=EPI_STORE)
+        self.comm.all_reduce(part)
+        torch.add(resid[:M], part, out=out[:M])
+        self._launches += 2
+
+    def _run_layers(self, x: _Ctx):
+        c, T, S = self.cfg, x.T, x.S
+        eps = c.rms_eps
+        F.embed(x.ids, self.embed, x.h[0], self.step_ptr)
+        self._launches += 1
+        self._order = 0
+        cur, nxt = x.h[0], x.h[1]
+        ig = ia = 0
+        for L in self.layers:
+            if L.is_gdn:
+                self._gemv(L.in_proj, cur, x.proj, T, xmode=XNORM, epi=EPI_STORE, norm_w=L.input_norm)
+                p = GdnParams()
+                p.proj, p.conv_w, p.neg_a_exp, p.dt_bias, p.norm_w = ptr(x.proj), ptr(L.conv_w), ptr(L.neg_a_exp), ptr(L.dt_bias), ptr(L.norm_w)
+                p.state, p.conv_state = ptr(self.rec[ig]), ptr(self.conv[ig])
+                p.slots, p.cu, p.out = ptr(x.slots), ptr(x.cu), ptr(x.mix)
+                p.ld, p.hk, p.hv, p.eps = x.proj.stride(0), self.hk, self.hv, eps
+                if x.snap_rel is not None:
+                    p.snap_rel, p.num_snap = ptr(x.snap_rel), x.num_snap
+                    p.snap_state, p.snap_conv = ptr(x.snap_state[ig]), ptr(x.snap_conv[ig])
+                F.gdn_step(p, S, self.dk, self.dv, self.state_bf16)
+                self._launches += 1
+                # the kernel writes [T, hv*dv] densely
+                mix = x.mix.view(-1)[:T * self.hv * self.dv].view(T, self.hv * self.dv)
+                self._rowpar(L.out, mix, cur, nxt, T)
+                ig += 1
+            else:
+                self._gemv(L.qkv, cur, x.proj, T, xmode=XNORM, epi=EPI_STORE, norm_w=L.input_norm)
+                q = QkvPrepParams()
+                q.proj, q.q_norm, q.k_norm = ptr(x.proj), ptr(L.q_norm), ptr(L.k_norm)
+                q.positions, q.slot_mapping, q.q_out = ptr(x.positions), ptr(x.slot_mapping), ptr(x.qbuf)
+                q.kcache, q.vcache = ptr(self.kv[ia, 0]), ptr(self.kv[ia, 1])
+                q.ld, q.hq, q.hkv, q.rotary_dim = x.proj.stride(0), self.hq, self.hkv, c.rotary_dim
+                q.eps, q.log2_theta = eps, math.log2(c.rope_theta)
+                F.qkv_prep(q, T, self.D)
+                a = AttnParams()
+                a.q, a.kcache, a.vcache = ptr(x.qbuf), ptr(self.kv[ia, 0]), ptr(self.kv[ia, 1])
+                a.block_tables, a.positions = ptr(x.block_tables), ptr(x.positions)
+                a.qg_seq, a.qg_tok0, a.qg_ntok = ptr(x.qg[0]), ptr(x.qg[1]), ptr(x.qg[2])
+                a.o_part, a.ml_part, a.gate_src = ptr(x.o_part), ptr(x.ml_part), ptr(x.proj)
+                mix = x.mix.view(-1)[:T * self.hq * self.D].view(T, self.hq * self.D)
+                a.out = ptr(mix)
+                a.hq, a.hkv, a.max_blocks, a.nsplit = self.hq, self.hkv, x.max_blocks, x.nsplit
+                a.ld, a.num_qg = x.proj.stride(0), x.num_qg
+                a.scale_log2e = self.D ** -0.5 * 1.4426950408889634
+                F.attn_paged(a, self.D)
+                self._launches += 3
+                self._rowpar(L.o, mix, cur, nxt, T)
+                ia += 1
+            cur, nxt = nxt, cur
+            self._gemv(L.gate_up, cur, x.act, T, xmode=XNORM, epi=EPI_SWIGLU, norm_w=L.post_norm)
+            self._rowpar(L.down, x.act, cur, nxt, T)
+            cur, nxt = nxt, cur
+        return cur
+
+
+class _RunMixin:
+    # ------------------------------------------------------------------ helpers
+    def _tokens_per_group(self) -> int:
+        return 2 if (self.hq // self.hkv) * 2 <= 16 else 1
+
+    def _topk_geometry(self, k: int):
+        V = self.v_local
+        max_chunks = min(128, 8192 // k)
+        cs = -(-V // max_chunks)
+        cs = max(256, -(-cs // 256) * 256)
+        assert cs <= 4096, "vocabulary shard too large for the top-k kernel"
+        return -(-V // cs), cs
+
+    def _make_topk(self, logits, n, k, order=65000):
+        chunks, cs = self._topk_geometry(k)
+        dev = self.dev
+        t = _Ctx()
+        t.ws_val = torch.empty(n * chunks * k, dtype=torch.float32, device=dev)
+        t.ws_idx = torch.empty(n * chunks * k, dtype=torch.int32, device=dev)
+        t.out_val = torch.empty(n, self.tp * k if self.peer is not None else k, dtype=torch.float32, device=dev)
+        t.out_idx = torch.empty_like(t.out_val, dtype=torch.int32)
+        p = TopkParams()
+        p.logits, p.ws_val, p.ws_idx, p.out_val, p.out_idx = ptr(logits), ptr(t.ws_val), ptr(t.ws_idx), ptr(t.out_val), ptr(t.out_idx)
+        p.M, p.V, p.ld, p.k, p.chunks, p.chunk_size = n, self.v_local, logits.stride(0), k, chunks, cs
+        p.vocab_start = self.vocab_start
+        p.tp, p.rank, p.order, p.m_cap = 1, 0, order, 0
+        if self.peer is not None:
+            p.tp, p.rank, p.m_cap = self.tp, self.rank, self.peer.m_cap
+            for r in range(self.tp):
+                p.peer_buf[r] = self.peer.cand_ptrs[r]
+            p.step_ptr, p.status, p.timeout_ns = self.peer.step_ptr, self.peer.status_ptr, self.peer.timeout_ns
+        t.params = p
+        return t
+
+    def _lm_head(self, hidden, logits, n):
+        self._gemv(self.lm_head, hidden, logits, n, xmode=XNORM, epi=EPI_F32, norm_w=self.final_norm)
+
+    def _topk_rows(self, logits, n, k):
+        """Per-rank top-k (+ fused candidate exchange); rows in chunks of the peer buffer capacity."""
+        cap = self.peer.m_cap if self.peer is not None else n
+        outs = []
+        for ci, m0 in enumerate(range(0, n, cap)):
+            m = min(cap, n - m0)
+            t = self._make_topk(logits[m0:m0 + m], m, k, order=65000 + ci)
+            F.topk(t.params)
+            self._launches += 2
+            outs.append(t)
+        return torch.cat([t.out_val for t in outs]), torch.cat([t.out_idx for t in outs])
+
+    # ------------------------------------------------------------------ eager variable-length step
+    def _fill_ctx(self, x: _Ctx, batch, host=None):
+        """Copies the batch description into the device tensors of `x`."""
+        S, T = batch.num_seqs, batch.cu_seqlens[-1]
+        gt = self._tokens_per_group()
+        qg_seq, qg_tok0, qg_ntok = [], [], []
+        for s in range(S):
+            t0, t1 = batch.cu_seqlens[s], batch.cu_seqlens[s + 1]
+            for a in range(t0, t1, gt):
+                qg_seq.append(s); qg_tok0.append(a); qg_ntok.append(min(gt, t1 - a))
+        return qg_seq, qg_tok0, qg_ntok
+
+    @torch.no_grad()
+    def forward(self, batch):
+        """Eager step over a flattened batch (prefill chunks and/or decode tokens).  Returns the
+        residual-stream rows of the last token of every sequence [S, H] (the final norm is fused
+        into the lm_head kernel)."""
+        dev = self.dev
+        S, T = batch.num_seqs, batch.cu_seqlens[-1]
+        qg_seq, qg_tok0, qg_ntok = self._fill_ctx(None, batch)
+        nq = len(qg_seq)
+        max_blocks = max(len(b) for b in batch.block_tables)
+        nsplit = 1 if nq * self.hkv >= 148 else max(1, min(32, -(-296 // (nq * self.hkv))))
+        x = self._alloc_ctx(T, S, max_blocks, nq, nsplit)
+        x.ids.copy_(batch.input_ids, non_blocking=True)
+        x.positions.copy_(batch.positions.to(torch.int32), non_blocking=True)
+        x.slot_mapping.copy_(batch.slot_mapping, non_blocking=True)
+        x.slots.copy_(torch.tensor(batch.state_slots, dtype=torch.int32), non_blocking=True)
+        x.cu = torch.tensor(batch.cu_seqlens, dtype=torch.int32, device=dev)
+        bt = torch.zeros(S, max_blocks, dtype=torch.int32)
+        for s, b in enumerate(batch.block_tables):
+            bt[s, :len(b)] = torch.tensor(b, dtype=torch.int32)
+        x.block_tables.copy_(bt, non_blocking=True)
+        x.qg.copy_(torch.tensor([qg_seq, qg_tok0, qg_ntok], dtype=torch.int32), non_blocking=True)
+        snaps = []
+        if batch.snapshot_at and any(batch.snapshot_at):
+            ns = max(len(p) for p in batch.snapshot_at)
+            rel = torch.zeros(S, ns, dtype=torch.int32)
+            for s, pts in enumerate(batch.snapshot_at):
+                start = batch.context_lens[s] - (batch.cu_seqlens[s + 1] - batch.cu_seqlens[s])
+                for j, a in enumerate(pts):
+                    rel[s, j] = a - start
+                    snaps.append((s, j, a))
+            ng = max(self.cfg.num_gdn_layers, 1)
+            x.snap_rel, x.num_snap = rel.to(dev), ns
+            x.snap_state = torch.zeros(ng, S, ns, self.hv, self.dk, self.dv, dtype=torch.float32, device=dev)
+            x.snap_conv = torch.zeros(ng, S, ns, self.hv, 3, self.nch, dtype=BF16, device=dev)
+        cur = self._run_layers(x)
+        last = torch.tensor([c - 1 for c in batch.cu_seqlens[1:]], dtype=torch.long, device=dev)
+        hidden = cur[last]
+        for s, j, a in snaps:
+            self.snapshots[(s, a)] = (x.snap_state[:, s, j].cpu(), x.snap_conv[:, s, j].cpu())
+        self.host_steps += 1
+        return hidden
+
+    @torch.no_grad()
+    def logits(self, hidden) -> torch.Tensor:
+        n = hidden.shape[0]
+        hidden = hidden.contiguous()
+        out = torch.empty(n, self.v_local, dtype=torch.float32, device=self.dev)
+        self._lm_head(hidden, out, n)
+        return out
+
+    # ------------------------------------------------------------------ CUDA-graph decode
+    def capture_decode_graphs(self, max_num_seqs, max_graph_bs, max_model_len, padding_slot):
+        self.padding_slot = padding_slot
+        self.graph_max_blocks = max_model_len // 16 + 2
+        top = min(max_num_seqs, max_graph_bs)
+        if self.peer is not None:
+            top = min(top, self.peer.m_cap)      # one candidate exchange per step covers m_cap rows
+        self.buckets = []
+        b = 1
+        while b < top:
+            self.buckets.append(b)
+            b *= 2
+        self.buckets.append(top)
+        self.graph_pool = None
+        for b in self.buckets:
+            self._get_graph(b, 1)
+
+    def _get_graph(self, B: int, k: int):
+        key = (B, k)
+        g = self.graphs.get(key)
+        if g is not None:
+            return g
+        dev = self.dev
+        nsplit = max(1, min(32, -(-296 // (B * self.hkv))))
+        base = self.graphs.get((B, 1))
+        g = _Ctx()
+        if base is not None:      # same bucket, other k: share the input tensors
+            g.x = base.x
+            g.host = base.host
+        else:
+            g.x = self._alloc_ctx(B, B, self.graph_max_blocks, B, nsplit)
+            x = g.x
+            g.host = {
+                "ids": torch.zeros(B, dtype=torch.long).pin_memory(),
+                "positions": torch.zeros(B, dtype=torch.int32).pin_memory(),
+                "slot_mapping": torch.full((B,), -1, dtype=torch.long).pin_memory(),
+                "slots": torch.full((B,), self.padding_slot, dtype=torch.int32).pin_memory(),
+                "block_tables": torch.zeros(B, self.graph_max_blocks, dtype=torch.int32).pin_memory(),
+                "qg": torch.zeros(3, B, dtype=torch.int32).pin_memory(),
+            }
+            x.slots.fill_(self.padding_slot)
+        x = g.x
+        g.logits = torch.zeros(B, self.v_local, dtype=torch.float32, device=dev)
+        g.topk = self._make_topk(g.logits, B, k)
+        g.k = k
+
+        def body():
+            cur = self._run_layers(x)
+            self._lm_head(cur, g.logits, B)
+            F.topk(g.topk.params)
+            self._launches += 2
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            body()                                   # warm-up (padding inputs touch only the padding slot)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        if self.comm is not None:
+            self.comm.barrier()
+        self._launches = 0
+        g.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g.graph, pool=self.graph_pool):
+            body()
+        g.launches = self._launches
+        self.launches_per_decode_step = g.launches
+        if self.graph_pool is None:
+            self.graph_pool = g.graph.pool()
+        self.graphs[key] = g
+        return g
+
+    def _decode_graph_step(self, batch, k: int):
+        n = batch.num_seqs
+        B = next(b for b in self.buckets if b >= n)
+        g = self._get_graph(B, k)
+        h, x = g.host, g.x
+        h["ids"][:n] = batch.input_ids
+        h["positions"][:n] = batch.positions
+        h["slot_mapping"][:n] = batch.slot_mapping
+        h["slot_mapping"][n:] = -1
+        h["slots"][:n] = torch.tensor(batch.state_slots, dtype=torch.int32)
+        h["slots"][n:] = self.padding_slot
+        bt = h["block_tables"]
+        for s, b in enumerate(batch.block_tables):
+            bt[s, :len(b)] = torch.tensor(b, dtype=torch.int32)
+        qg = h["qg"]
+        qg[0, :n] = torch.arange(n, dtype=torch.int32)
+        qg[1, :n] = torch.arange(n, dtype=torch.int32)
+        qg[2, :n] = 1
+        qg[2, n:] = 0
+        x.ids.copy_(h["ids"], non_blocking=True)
+        x.positions.copy_(h["positions"], non_blocking=True)
+        x.slot_mapping.copy_(h["slot_mapping"], non_blocking=True)
+        x.slots.copy_(h["slots"], non_blocking=True)
+        x.block_tables.copy_(bt, non_blocking=True)
+        x.qg.copy_(qg, non_blocking=True)
+        g.graph.replay()
+        self.host_steps += 1
+        return g.topk.out_val[:n], g.topk.out_idx[:n]
+
+    @torch.no_grad()
+    def forward_and_sample(self, batch, sample_rows, k: int):
+        """Runs the step and returns the top-k candidates (values, global token ids) of the rows that
+        sample, already gathered over the tensor-parallel group: ([n, tp*k], [n, tp*k])."""
+        k = 1 if k <= 1 else 64
+        decode_only = batch.cu_seqlens[-1] == batch.num_seqs and len(sample_rows) == batch.num_seqs
+        if decode_only and self.graphs and batch.num_seqs <= self.buckets[-1] \
+                and max(len(b) for b in batch.block_tables) <= self.graph_max_blocks:
+            vals, idx = self._decode_graph_step(batch, k)
+        else:
+            hidden = self.forward(batch)
+            rows = torch.tensor(sample_rows, dtype=torch.long, device=self.dev)
+            lg = self.logits(hidden[rows])
+            vals, idx = self._topk_rows(lg, len(sample_rows), k)
+        if self.peer is None and self.tp > 1:
+            vals = torch.cat(self.comm.all_gather(vals.contiguous()), dim=-1)
+            idx = torch.cat(self.comm.all_gather(idx.contiguous()), dim=-1)
+        return vals, idx
+
+    def peer_status(self) -> int:
+        return int(self.ctrl[1].item())
+
+
+class B200HybridModel(_ModelBase, _StepMixin, _RunMixin):
+    """See the module docstring."""

@@ -1,0 +1,156 @@
+// Sampling front-end on the vocabulary shard of one rank: per-row top-k of the lm_head logits and the
+// exchange of the k candidates between tensor-parallel ranks, so that every rank ends up with the
+// same tp*k (value, token id) pairs and can sample without a broadcast.
+//
+// The logits themselves come from the bf16 GEMV (final RMSNorm fused in its prologue, fp32 output).
+// Replaces kernels/lm_head_topk.py:6-582 (fused argmax only, indices round-tripped through fp32) and
+// the torch.topk + 2x all_gather + rank-0 broadcast of engine/model_runner.py:1012-1083, 879-883.
+// Indices stay integers; ties resolve to the smallest token id.
+//
+// Stage 1: grid (rows, chunks): each block keeps its chunk of the row in registers and extracts the
+// k best by repeated block-wide arg-max.  Stage 2: one block per row merges chunks*k candidates the
+// same way, then (tp > 1) stores its k winners as tagged packets into every peer's buffer and waits,
+// bounded, for the peers' packets.
+#include "common.cuh"
+
+namespace ti {
+
+struct TopkParams {
+  const float* logits;           // [M, ld]
+  float* ws_val;                 // [M, chunks, k]
+  int* ws_idx;                   // [M, chunks, k]
+  float* out_val;                // [M, tp*k]
+  int* out_idx;                  // [M, tp*k] global token ids
+  const unsigned* step_ptr;
+  unsigned* status;
+  uint64_t peer_buf[kMaxRanks];  // packet buffers [2][tp][m_cap][64] x 16 bytes
+  unsigned long long timeout_ns;
+  int M, V, ld, k, chunks, chunk_size, vocab_start;
+  int tp, rank, order, m_cap;
+};
+
+struct Best { float v; int i; };
+TI_DEVICE bool better(const Best& a, const Best& b) { return a.v > b.v || (a.v == b.v && a.i < b.i); }
+
+TI_DEVICE Best block_argmax(Best b, Best* sm) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other{__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
+    if (better(other, b)) b = other;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (lane == 0) sm[warp] = b;
+  __syncthreads();
+  Best r = sm[0];
+  for (int w = 1; w < nw; ++w)
+    if (better(sm[w], r)) r = sm[w];
+  __syncthreads();
+  return r;
+}
+
+constexpr int kNoIdx = 0x7fffffff;
+
+template <int EPT>
+TI_DEVICE void select_topk(float (&val)[EPT], int (&idx)[EPT], int k, float* out_v, int* out_i, Best* sm) {
+  for (int j = 0; j < k; ++j) {
+    Best b{-INFINITY, kNoIdx};
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+      Best c{val[e], idx[e]};
+      if (idx[e] != kNoIdx && better(c, b)) b = c;
+    }
+    const Best w = block_argmax(b, sm);
+#pragma unroll
+    for (int e = 0; e < EPT; ++e)
+      if (idx[e] == w.i) idx[e] = kNoIdx;          // taken
+    if (threadIdx.x == 0) {
+      out_v[j] = w.i == kNoIdx ? -INFINITY : w.v;
+      out_i[j] = w.i == kNoIdx ? -1 : w.i;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) topk_stage1_kernel(const __grid_constant__ TopkParams p) {
+  constexpr int EPT = 16;
+  __shared__ Best sm[8];
+  const int m = blockIdx.x, c = blockIdx.y;
+  const int lo = c * p.chunk_size, hi = min(p.V, lo + p.chunk_size);
+  float val[EPT];
+  int idx[EPT];
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) {
+    const int i = lo + threadIdx.x + e * 256;
+    const bool ok = i < hi;
+    val[e] = ok ? p.logits[(size_t)m * p.ld + i] : -INFINITY;
+    idx[e] = ok ? i : kNoIdx;
+  }
+  const size_t o = ((size_t)m * p.chunks + c) * p.k;
+  select_topk<EPT>(val, idx, p.k, p.ws_val + o, p.ws_idx + o, sm);
+}
+
+__global__ void __launch_bounds__(256) topk_stage2_kernel(const __grid_constant__ TopkParams p) {
+  constexpr int EPT = 32;
+  __shared__ Best sm[8];
+  __shared__ float fin_v[64];
+  __shared__ int fin_i[64];
+  const int m = blockIdx.x;
+  const int nc = p.chunks * p.k;
+  float val[EPT];
+  int idx[EPT];
+#pragma unroll
+  for (int e = 0; e < EPT; ++e) {
+    const int i = threadIdx.x + e * 256;
+    const bool ok = i < nc && p.ws_idx[(size_t)m * nc + i] >= 0;
+    val[e] = ok ? p.ws_val[(size_t)m * nc + i] : -INFINITY;
+    idx[e] = ok ? p.ws_idx[(size_t)m * nc + i] : kNoIdx;
+  }
+  select_topk<EPT>(val, idx, p.k, fin_v, fin_i, sm);
+  __syncthreads();
+  const int kk = p.k;
+  if (p.tp == 1) {
+    for (int j = threadIdx.x; j < kk; j += 256) {
+      p.out_val[(size_t)m * kk + j] = fin_v[j];
+      p.out_idx[(size_t)m * kk + j] = fin_i[j] < 0 ? -1 : fin_i[j] + p.vocab_start;
+    }
+    return;
+  }
+  // ---- candidate all-gather over peer memory: one 16-byte packet pair per candidate
+  const unsigned tag = (*p.step_ptr) * 65536u + (unsigned)p.order + 1u;
+  const int slot = p.order & 1;
+  for (int j = threadIdx.x; j < kk; j += 256) {
+    const float v = fin_v[j];
+    const int gi = fin_i[j] < 0 ? -1 : fin_i[j] + p.vocab_start;
+    const size_t mine = ((((size_t)slot * p.tp + p.rank) * p.m_cap + m) * 64 + j) * 16;
+    for (int q = 0; q < p.tp; ++q)
+      if (q != p.rank) ll_store2(reinterpret_cast<uint8_t*>(p.peer_buf[q]) + mine, v, __int_as_float(gi), tag);
+    const uint8_t* local = reinterpret_cast<const uint8_t*>(p.peer_buf[p.rank]);
+    for (int r = 0; r < p.tp; ++r) {
+      float a = v, b = __int_as_float(gi);
+      if (r != p.rank) {
+        const size_t off = ((((size_t)slot * p.tp + r) * p.m_cap + m) * 64 + j) * 16;
+        ll_wait2(local + off, tag, a, b, p.timeout_ns, p.status);
+      }
+      p.out_val[((size_t)m * p.tp + r) * kk + j] = a;
+      p.out_idx[((size_t)m * p.tp + r) * kk + j] = __float_as_int(b);
+    }
+  }
+}
+
+}  // namespace ti
+
+extern "C" {
+
+int ti_topk_params_size() { return (int)sizeof(ti::TopkParams); }
+
+int ti_topk(const ti::TopkParams* p, void* stream) {
+  if (p->M <= 0) return 0;
+  if (p->k < 1 || p->k > 64 || p->chunk_size > 4096 || p->chunks * p->k > 8192) return -2;
+  if ((long long)p->chunks * p->chunk_size < p->V) return -3;
+  if (p->tp > ti::kMaxRanks || (p->tp > 1 && p->M > p->m_cap)) return -5;
+  cudaStream_t st = (cudaStream_t)stream;
+  ti::topk_stage1_kernel<<<dim3(p->M, p->chunks), 256, 0, st>>>(*p);
+  ti::topk_stage2_kernel<<<p->M, 256, 0, st>>>(*p);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

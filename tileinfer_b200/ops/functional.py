@@ -1,0 +1,228 @@
+"""Tensor-level wrappers of the sm_100a kernels (torch tensors in, launches on the current stream).
+
+Nothing here allocates unless the docstring says so; the model keeps its activations, workspaces and
+parameter blocks alive, which also makes every launch capturable into a CUDA graph.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import lib as _l
+from .lib import GemvParams, MAX_RANKS, check, ptr, stream
+
+_I, _P, _F = ctypes.c_int, ctypes.c_void_p, ctypes.c_float
+
+XGLOBAL, XNORM = 0, 1
+EPI_STORE, EPI_SWIGLU, EPI_ROWPAR, EPI_F32 = 0, 1, 2, 3
+W_INT8, W_BF16 = 0, 1
+NUM_SMS = 148
+GEMV_WARPS = 16
+
+
+class GdnParams(ctypes.Structure):
+    _fields_ = [("proj", _P), ("conv_w", _P), ("neg_a_exp", _P), ("dt_bias", _P), ("norm_w", _P), ("state", _P),
+                ("conv_state", _P), ("slots", _P), ("cu", _P), ("out", _P), ("snap_rel", _P), ("snap_state", _P),
+                ("snap_conv", _P), ("ld", _I), ("hk", _I), ("hv", _I), ("num_snap", _I), ("eps", _F)]
+
+
+class QkvPrepParams(ctypes.Structure):
+    _fields_ = [("proj", _P), ("q_norm", _P), ("k_norm", _P), ("positions", _P), ("slot_mapping", _P),
+                ("q_out", _P), ("kcache", _P), ("vcache", _P), ("ld", _I), ("hq", _I), ("hkv", _I),
+                ("rotary_dim", _I), ("eps", _F), ("log2_theta", _F)]
+
+
+class AttnParams(ctypes.Structure):
+    _fields_ = [("q", _P), ("kcache", _P), ("vcache", _P), ("block_tables", _P), ("positions", _P),
+                ("qg_seq", _P), ("qg_tok0", _P), ("qg_ntok", _P), ("o_part", _P), ("ml_part", _P),
+                ("gate_src", _P), ("out", _P), ("hq", _I), ("hkv", _I), ("max_blocks", _I), ("nsplit", _I),
+                ("ld", _I), ("num_qg", _I), ("scale_log2e", _F)]
+
+
+class TopkParams(ctypes.Structure):
+    _fields_ = [("logits", _P), ("ws_val", _P), ("ws_idx", _P), ("out_val", _P), ("out_idx", _P),
+                ("step_ptr", _P), ("status", _P), ("peer_buf", ctypes.c_uint64 * MAX_RANKS),
+                ("timeout_ns", ctypes.c_ulonglong),
+                ("M", _I), ("V", _I), ("ld", _I), ("k", _I), ("chunks", _I), ("chunk_size", _I),
+                ("vocab_start", _I), ("tp", _I), ("rank", _I), ("order", _I), ("m_cap", _I)]
+
+
+_l.register("ti_embed", _I, [_P, _P, _P, _I, _I, _I, _P, _P])
+_l.register("ti_rmsnorm", _I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _P])
+_l.register("ti_act_mul", _I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P])
+_l.register("ti_swiglu_interleaved", _I, [_P, _P, _I, _I, _I, _I, _P])
+_l.register("ti_gdn_params_size", _I, [])
+_l.register("ti_gdn_step", _I, [ctypes.POINTER(GdnParams), _I, _I, _I, _I, _P])
+_l.register("ti_qkv_prep_params_size", _I, [])
+_l.register("ti_attn_params_size", _I, [])
+_l.register("ti_qkv_prep", _I, [ctypes.POINTER(QkvPrepParams), _I, _I, _P])
+_l.register("ti_attn_paged", _I, [ctypes.POINTER(AttnParams), _I, _P])
+_l.register("ti_topk_params_size", _I, [])
+_l.register("ti_topk", _I, [ctypes.POINTER(TopkParams), _P])
+_l.register("ti_symm_alloc", _I, [ctypes.POINTER(_P), ctypes.c_size_t])
+_l.register("ti_symm_free", _I, [_P])
+_l.register("ti_ipc_handle_size", _I, [])
+_l.register("ti_ipc_get_handle", _I, [_P, _P])
+_l.register("ti_ipc_open", _I, [_P, ctypes.POINTER(_P)])
+_l.register("ti_ipc_close", _I, [_P])
+_l.register("ti_memset_async", _I, [_P, _I, ctypes.c_size_t, _P])
+_l.register("ti_wait_flag_probe", _I, [_P, ctypes.c_uint, ctypes.c_ulonglong, _P, _P, _P])
+
+_checked = False
+
+
+def L():
+    global _checked
+    lib = _l.lib()
+    if not _checked:
+        for fn, st in (("ti_gdn_params_size", GdnParams), ("ti_qkv_prep_params_size", QkvPrepParams),
+                       ("ti_attn_params_size", AttnParams), ("ti_topk_params_size", TopkParams)):
+            if getattr(lib, fn)() != ctypes.sizeof(st):
+                raise RuntimeError(f"{st.__name__} layout mismatch between Python and CUDA")
+        _checked = True
+    return lib
+
+
+# ------------------------------------------------------------------------------------ GEMV
+class LinearW:
+    """A weight matrix in kernel layout: 512-byte tiles [N/8][K/64 or K/32][8][64 B] (+ bf16 row scales)."""
+
+    def __init__(self, w: torch.Tensor, quantize: bool, device="cuda"):
+        from ..models.weights import pad_rows, quantize_int8_rowwise, tile_bf16, tile_int8
+        self.N, self.K = w.shape
+        w = pad_rows(w.to(device), 8)
+        self.n_pad = w.shape[0]
+        if quantize:
+            assert self.K % 64 == 0, self.K
+            q, s = quantize_int8_rowwise(w)
+            self.tiles = tile_int8(q)
+            self.scale = s.contiguous()
+            self.wt, self.tile_k = W_INT8, 64
+        else:
+            assert self.K % 32 == 0, self.K
+            self.tiles = tile_bf16(w.to(torch.bfloat16))
+            self.scale = None
+            self.wt, self.tile_k = W_BF16, 32
+        self.KB = self.K // self.tile_k
+        self.n_tiles = self.n_pad // 8
+
+    def dense(self) -> torch.Tensor:
+        """Row-major bf16 copy [N, K] (tests and the prefill GEMM baseline)."""
+        from ..models.weights import untile_int8
+        if self.wt == W_INT8:
+            return (untile_int8(self.tiles).float() * self.scale.float()[:, None])[:self.N].to(torch.bfloat16)
+        nt, kt = self.tiles.shape[:2]
+        return self.tiles.permute(0, 2, 1, 3).reshape(nt * 8, kt * 32)[:self.N]
+
+    def nbytes(self) -> int:
+        return self.tiles.numel() * self.tiles.element_size()
+
+
+def plan_split(n_tiles: int, KB: int, ncta: int = NUM_SMS, min_kb: int = 4):
+    """(S, kb_per_split): enough (row-tile, k-range) units to occupy every warp about twice."""
+    warps = ncta * GEMV_WARPS
+    S = max(1, min(math.ceil(2 * warps / n_tiles), KB // min_kb if KB >= min_kb else 1))
+    kbps = math.ceil(KB / S)
+    S = math.ceil(KB / kbps)
+    return S, kbps
+
+
+class GemvWorkspace:
+    """Split-k partial buffer and per-tile arrival counters shared by all GEMV launches of a stream."""
+
+    def __init__(self, device="cuda", max_units: int = 1 << 16, max_tiles: int = 1 << 16):
+        self.ws = torch.empty(max_units * 128, dtype=torch.float32, device=device)
+        self.counters = torch.zeros(max_tiles, dtype=torch.int32, device=device)
+        self.max_units, self.max_tiles = max_units, max_tiles
+
+
+def make_gemv_params(W: LinearW, x, out, M, *, xmode=XGLOBAL, epi=EPI_STORE, norm_w=None, resid=None, ws=None,
+                     eps=1e-6, ldx=None, ldo=None, comm=None, order=0, ncta=NUM_SMS) -> GemvParams:
+    p = GemvParams()
+    p.w, p.scale, p.x, p.norm_w = ptr(W.tiles), ptr(W.scale), ptr(x), ptr(norm_w)
+    p.out, p.resid = ptr(out), ptr(resid)
+    S, kbps = plan_split(W.n_tiles, W.KB, ncta)
+    if S > 1:
+        assert ws is not None and W.n_tiles * S <= ws.max_units and W.n_tiles <= ws.max_tiles
+        p.ws, p.counters = ptr(ws.ws), ptr(ws.counters)
+    p.M, p.N, p.n_tiles, p.K, p.KB, p.S, p.kb_per_split = M, W.N, W.n_tiles, W.K, W.KB, S, kbps
+    p.ldx = ldx if ldx is not None else (x.stride(0) if x.dim() > 1 else W.K)
+    p.ldo = ldo if ldo is not None else (out.stride(0) if out.dim() > 1 else W.N)
+    p.eps = eps
+    p.tp, p.rank, p.order, p.m_cap = 1, 0, order, 0
+    if comm is not None and comm.tp > 1:
+        p.tp, p.rank, p.m_cap = comm.tp, comm.rank, comm.m_cap
+        for r in range(comm.tp):
+            p.peer_ll[r] = comm.ll_ptrs[r]
+        p.step_ptr, p.status, p.timeout_ns = comm.step_ptr, comm.status_ptr, comm.timeout_ns
+    return p
+
+
+def gemv_launch(p: GemvParams, wt: int, xmode: int, epi: int, ncta: int = NUM_SMS):
+    check(L().ti_gemv(ctypes.byref(p), wt, xmode, epi, ncta, stream()), "ti_gemv")
+
+
+def gemv(W: LinearW, x: torch.Tensor, *, out=None, xmode=XGLOBAL, epi=EPI_STORE, norm_w=None, resid=None, ws=None,
+         eps=1e-6, comm=None, order=0) -> torch.Tensor:
+    """Convenience form (allocates `out`); loops over chunks of 16 rows."""
+    M = x.shape[0]
+    if out is None:
+        cols = W.N // 2 if epi == EPI_SWIGLU else W.N
+        dt = torch.float32 if epi == EPI_F32 else torch.bfloat16
+        out = torch.empty(M, cols, dtype=dt, device=x.device)
+    for m0 in range(0, M, 16):
+        m = min(16, M - m0)
+        p = make_gemv_params(W, x[m0:m0 + m], out[m0:m0 + m], m, xmode=xmode, epi=epi, norm_w=norm_w,
+                             resid=None if resid is None else resid[m0:m0 + m], ws=ws, eps=eps,
+                             ldx=x.stride(0), ldo=out.stride(0), comm=comm, order=order)
+        gemv_launch(p, W.wt, xmode, epi)
+    return out
+
+
+# ------------------------------------------------------------------------------------ pointwise
+def embed(ids, table, out, step_ptr=0):
+    M, H = out.shape
+    check(L().ti_embed(ptr(ids), ptr(table), ptr(out), M, H, table.shape[0], step_ptr, stream()), "ti_embed")
+
+
+def rmsnorm(x, w, eps, *, add=None, out=None, r_out=None, one_plus=True):
+    M, H = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    check(L().ti_rmsnorm(ptr(x), ptr(add), ptr(w), ptr(out), ptr(r_out), M, H, eps, int(one_plus), stream()), "ti_rmsnorm")
+    return out
+
+
+def act_mul(a, b, out=None, mode=0):
+    M, n = a.shape
+    if out is None:
+        out = torch.empty(M, n, dtype=torch.bfloat16, device=a.device)
+    check(L().ti_act_mul(ptr(a), ptr(b), ptr(out), M, n, a.stride(0), b.stride(0), out.stride(0), mode, stream()), "ti_act_mul")
+    return out
+
+
+def swiglu_interleaved(gu, out=None):
+    M, n2 = gu.shape
+    if out is None:
+        out = torch.empty(M, n2 // 2, dtype=torch.bfloat16, device=gu.device)
+    check(L().ti_swiglu_interleaved(ptr(gu), ptr(out), M, n2 // 2, gu.stride(0), out.stride(0), stream()), "ti_swiglu")
+    return out
+
+
+# ------------------------------------------------------------------------------------ launches by params
+def gdn_step(p: GdnParams, num_seqs: int, dk: int, dv: int, state_bf16: bool):
+    check(L().ti_gdn_step(ctypes.byref(p), num_seqs, dk, dv, int(state_bf16), stream()), "ti_gdn_step")
+
+
+def qkv_prep(p: QkvPrepParams, T: int, D: int):
+    check(L().ti_qkv_prep(ctypes.byref(p), T, D, stream()), "ti_qkv_prep")
+
+
+def attn_paged(p: AttnParams, D: int):
+    check(L().ti_attn_paged(ctypes.byref(p), D, stream()), "ti_attn_paged")
+
+
+def topk(p: TopkParams):
+    check(L().ti_topk(ctypes.byref(p), stream()), "ti_topk")

@@ -1,0 +1,108 @@
+"""Symmetric peer buffers for the fused tensor-parallel kernels.
+
+Each rank owns (a) a packet buffer for the row-parallel all-reduce, laid out
+[2 slots][tp sources][m_cap rows][N/2] 16-byte packet pairs, (b) a packet buffer for the top-k
+candidate exchange [2][tp][m_cap][64] and (c) a step counter and a status word.  The buffers are
+plain cudaMalloc memory; their CUDA-IPC handles travel over torch.distributed and every rank maps
+all of them, so a kernel can store to / poll any rank's buffer over NVLink.  Tags are derived from
+the device step counter (advanced by the embedding kernel once per forward) and the position of the
+collective inside the step, so CUDA-graph replays need no host-side argument changes.
+
+The reference has no counterpart; its communicator is NCCL only (engine/parallel.py:19-200).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import functional as F
+
+
+class PeerComm:
+    def __init__(self, comm, hidden: int, m_cap: int = 64, timeout_s: float = 2.0, device=None):
+        self.comm = comm
+        self.tp, self.rank = comm.world_size, comm.rank
+        self.m_cap = m_cap
+        self.hidden = hidden
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        # step counter + status live in ordinary torch memory (only this rank touches them)
+        self.ctrl = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.step_ptr = self.ctrl.data_ptr()
+        self.status_ptr = self.ctrl.data_ptr() + 4
+        self.ll_bytes = 2 * self.tp * m_cap * (hidden // 2) * 16
+        self.cand_bytes = 2 * self.tp * m_cap * 64 * 16
+        self._local = []
+        self._mapped = []
+        self.ll_ptrs = self._exchange(self.ll_bytes)
+        self.cand_ptrs = self._exchange(self.cand_bytes)
+
+    def _exchange(self, nbytes: int) -> list:
+        lib = F.L()
+        p = ctypes.c_void_p()
+        F.check(lib.ti_symm_alloc(ctypes.byref(p), nbytes), "ti_symm_alloc")
+        self._local.append(p.value)
+        if self.tp == 1:
+            return [p.value]
+        hs = lib.ti_ipc_handle_size()
+        buf = ctypes.create_string_buffer(hs)
+        F.check(lib.ti_ipc_get_handle(p, buf), "ti_ipc_get_handle")
+        import torch.distributed as dist
+        handles = [None] * self.tp
+        dist.all_gather_object(handles, bytes(buf.raw))
+        ptrs = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                ptrs.append(p.value)
+                continue
+            q = ctypes.c_void_p()
+            F.check(lib.ti_ipc_open(ctypes.create_string_buffer(h, hs), ctypes.byref(q)), "ti_ipc_open")
+            self._mapped.append(q.value)
+            ptrs.append(q.value)
+        torch.cuda.synchronize()
+        self.comm.barrier()
+        return ptrs
+
+    def status(self) -> int:
+        """Error bits raised by kernels (1 = a peer wait timed out).  Synchronises."""
+        return int(self.ctrl[1].item())
+
+    def clear_status(self):
+        self.ctrl[1] = 0
+
+    def close(self):
+        lib = F.L()
+        torch.cuda.synchronize()
+        for q in self._mapped:
+            lib.ti_ipc_close(ctypes.c_void_p(q))
+        self._mapped = []
+        if self.tp > 1:
+            self.comm.barrier()
+        for p in self._local:
+            lib.ti_symm_free(ctypes.c_void_p(p))
+        self._local = []
+
+
+class LocalRanks:
+    """Several emulated ranks on ONE GPU (tests): same buffer layout, plain device pointers.  Kernels
+    of all ranks must then run inside a single cooperative launch (`ti_gemv_ranks`)."""
+
+    def __init__(self, tp: int, hidden: int, m_cap: int = 16, timeout_s: float = 1.0, device="cuda"):
+        self.tp, self.m_cap, self.hidden = tp, m_cap, hidden
+        self.timeout_ns = int(timeout_s * 1e9)
+        n = 2 * tp * m_cap * (hidden // 2) * 4     # 16-byte pairs as int32 x4
+        self.bufs = [torch.zeros(n, dtype=torch.int32, device=device) for _ in range(tp)]
+        self.ctrl = torch.zeros(4, dtype=torch.int32, device=device)
+        self.ctrl[0] = 1
+        self.step_ptr = self.ctrl.data_ptr()
+        self.status_ptr = self.ctrl.data_ptr() + 4
+        self.ll_ptrs = [b.data_ptr() for b in self.bufs]
+
+    def view(self, rank: int):
+        class _V:
+            pass
+        v = _V()
+        v.tp, v.rank, v.m_cap = self.tp, rank, self.m_cap
+        v.ll_ptrs, v.step_ptr, v.status_ptr, v.timeout_ns = self.ll_ptrs, self.step_ptr, self.status_ptr, self.timeout_ns
+        return v
