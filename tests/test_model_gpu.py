@@ -83,8 +83,8 @@ def test_prefix_reuse_and_swap_on_gpu():
     st = llm.stats()
     assert st["prefix_hits"] >= 1 and st["prefix_hit_tokens"] >= 48
     _near_greedy(b, shared + _prompt(9, 6), "w8a16")
-    # memory pressure: 4 sequences x (up to 9 blocks) > 40 blocks -> preemption by swapping
-    prompts = [_prompt(100, 10 + i) for i in range(4)]
+    # memory pressure: 4 sequences x (up to 12 blocks) > 40 blocks -> preemption by swapping
+    prompts = [_prompt(150, 10 + i) for i in range(4)]
     outs = llm.generate_token_ids(prompts, SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True))
     st = llm.stats()
     assert st["preemptions"] >= 1 and st["swaps_out"] >= 1 and st["swaps_in"] >= 1

@@ -15,6 +15,7 @@ reference (model/qwen_36.py:710-809, 939-1133).
 """
 from __future__ import annotations
 
+import gc
 import math
 
 import torch
@@ -462,8 +463,17 @@ class _RunMixin:
             self.comm.barrier()
         self._launches = 0
         g.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g.graph, pool=self.graph_pool):
-            body()
+        # objects of an earlier engine (old graphs, tensors) must not be finalised while the stream
+        # captures: collect them now and keep the collector off until the capture ends
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(g.graph, pool=self.graph_pool):
+                body()
+        finally:
+            if gc_was_on:
+                gc.enable()
         g.launches = self._launches
         self.launches_per_decode_step = g.launches
         if self.graph_pool is None:

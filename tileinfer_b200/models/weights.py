@@ -33,6 +33,7 @@ class RandomWeights:
     def __init__(self, cfg: ModelConfig, seed: int = 0, std: float = 0.02, device="cpu"):
         self.cfg, self.seed, self.std = cfg, seed, std
         self.device = torch.device(device)
+        self.cpu_numel_limit = 1 << 24
 
     def _gen(self, name: str) -> torch.Generator:
         h = hashlib.sha256(f"{self.seed}:{name}".encode()).digest()
@@ -83,6 +84,13 @@ class RandomWeights:
             return torch.zeros(shape, dtype=torch.float32, device=self.device)
         if leaf == "norm_w":
             return torch.ones(shape, dtype=torch.float32, device=self.device)
+        numel = 1
+        for d in shape:
+            numel *= d
+        if self.device.type != "cpu" and numel <= self.cpu_numel_limit:
+            # small tensors come from the CPU generator so CPU and GPU runs see identical weights
+            cpu = RandomWeights(self.cfg, self.seed, self.std, "cpu")
+            return cpu.get(name).to(self.device)
         w = torch.empty(shape, dtype=torch.float32, device=self.device)
         w.normal_(0.0, self.std, generator=self._gen(name))
         return w.to(torch.bfloat16).float()
