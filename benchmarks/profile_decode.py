@@ -1,0 +1,54 @@
+"""Decode-step driver for profilers: builds the model, captures the CUDA-graph decode step for one
+batch size and replays it.  Meant to be run as is (prints ms/step) or under
+`ncu --metrics gpu__time_duration.sum --clock-control none` for a per-kernel launch list
+(the reference's counterpart is tests/profile_decode.py, a torch.profiler wrapper).
+
+    python benchmarks/profile_decode.py --model preset:qwen3.6-27b-8l --batch 1 --ctx 256 --steps 3
+"""
+import argparse
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+
+from tileinfer_b200.models.config import get_preset  # noqa: E402
+from tileinfer_b200.models.hybrid_b200 import B200HybridModel  # noqa: E402
+from tileinfer_b200.models.reference_cpu import Batch  # noqa: E402
+from tileinfer_b200.models.weights import RandomWeights  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="preset:qwen3.6-27b-8l")
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--ctx", type=int, default=256)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--quant", default="w8a16")
+    args = ap.parse_args()
+    cfg = get_preset(args.model)
+    torch.cuda.set_device(0)
+    m = B200HybridModel(cfg, RandomWeights(cfg, 0, device="cuda"), quant=args.quant)
+    B = args.batch
+    nblk_seq = args.ctx // 16 + 2
+    m.alloc_cache(B * nblk_seq + 1, 16, B + 1)
+    m.capture_decode_graphs(B, B, args.ctx + 16, B)
+    tables = [list(range(s * nblk_seq, (s + 1) * nblk_seq)) for s in range(B)]
+    pos = args.ctx - 1
+    batch = Batch(torch.randint(0, cfg.vocab_size - 1, (B,)), torch.full((B,), pos), list(range(B + 1)), [pos + 1] * B,
+                  tables, torch.tensor([t[pos // 16] * 16 + pos % 16 for t in tables]), list(range(B)))
+    m._decode_graph_step(batch, 1)
+    torch.cuda.synchronize()
+    g = m.graphs[(m.buckets[-1], 1)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        g.graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    print(f"model={cfg.name} batch={B} ctx={args.ctx} launches/step={g.launches} ms/step={e0.elapsed_time(e1) / args.steps:.4f}")
+
+
+if __name__ == "__main__":
+    main()

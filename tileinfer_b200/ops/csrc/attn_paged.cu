@@ -39,6 +39,8 @@ __global__ void __launch_bounds__(32) qkv_prep_kernel(const __grid_constant__ Qk
   constexpr int E = D / 32;                 // elements per lane
   __shared__ float buf[D];
   const int tok = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+  pdl_trigger();
+  pdl_wait();
   const __nv_bfloat16* row = p.proj + (size_t)tok * p.ld;
   const bool is_q = head < p.hq, is_k = !is_q && head < p.hq + p.hkv;
   const int kvh = is_q ? 0 : (is_k ? head - p.hq : head - p.hq - p.hkv);
@@ -139,6 +141,8 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ AttnP
   __shared__ float MLsm[NSTREAM][16][2];
 
   const int qg = blockIdx.x, kh = blockIdx.y, sp = blockIdx.z;
+  pdl_trigger();
+  pdl_wait();
   const PageRange pr = page_range(p, qg);
   if (pr.ntok == 0) return;
   const int p0 = sp * pr.pps, p1 = min(pr.npages, p0 + pr.pps);
@@ -262,6 +266,8 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ AttnP
 template <int D>
 __global__ void __launch_bounds__(128) attn_merge_kernel(const __grid_constant__ AttnParams p) {
   const int qg = blockIdx.x, kh = blockIdx.y;
+  pdl_trigger();
+  pdl_wait();
   const PageRange pr = page_range(p, qg);
   if (pr.ntok == 0) return;
   const int nact = (pr.npages + pr.pps - 1) / pr.pps;
@@ -297,9 +303,9 @@ int ti_qkv_prep(const ti::QkvPrepParams* p, int T, int D, void* stream) {
   dim3 grid(T, p->hq + 2 * p->hkv);
   cudaStream_t st = (cudaStream_t)stream;
   if (p->rotary_dim > D || (p->rotary_dim & 1)) return -2;
-  if (D == 256) ti::qkv_prep_kernel<256><<<grid, 32, 0, st>>>(*p);
-  else if (D == 128) ti::qkv_prep_kernel<128><<<grid, 32, 0, st>>>(*p);
-  else if (D == 64) ti::qkv_prep_kernel<64><<<grid, 32, 0, st>>>(*p);
+  if (D == 256) ti::launch_kernel(ti::qkv_prep_kernel<256>, grid, dim3(32), 0, st, true, *p);
+  else if (D == 128) ti::launch_kernel(ti::qkv_prep_kernel<128>, grid, dim3(32), 0, st, true, *p);
+  else if (D == 64) ti::launch_kernel(ti::qkv_prep_kernel<64>, grid, dim3(32), 0, st, true, *p);
   else return -3;
   return (int)cudaGetLastError();
 }
@@ -312,14 +318,14 @@ int ti_attn_paged(const ti::AttnParams* p, int D, void* stream) {
   dim3 grid(p->num_qg, p->hkv, p->nsplit), mgrid(p->num_qg, p->hkv);
   cudaStream_t st = (cudaStream_t)stream;
   if (D == 256) {
-    ti::attn_kernel<256, 2><<<grid, 128, 0, st>>>(*p);
-    ti::attn_merge_kernel<256><<<mgrid, 128, 0, st>>>(*p);
+    ti::launch_kernel(ti::attn_kernel<256, 2>, grid, dim3(128), 0, st, true, *p);
+    ti::launch_kernel(ti::attn_merge_kernel<256>, mgrid, dim3(128), 0, st, true, *p);
   } else if (D == 128) {
-    ti::attn_kernel<128, 1><<<grid, 128, 0, st>>>(*p);
-    ti::attn_merge_kernel<128><<<mgrid, 128, 0, st>>>(*p);
+    ti::launch_kernel(ti::attn_kernel<128, 1>, grid, dim3(128), 0, st, true, *p);
+    ti::launch_kernel(ti::attn_merge_kernel<128>, mgrid, dim3(128), 0, st, true, *p);
   } else if (D == 64) {
-    ti::attn_kernel<64, 1><<<grid, 128, 0, st>>>(*p);
-    ti::attn_merge_kernel<64><<<mgrid, 128, 0, st>>>(*p);
+    ti::launch_kernel(ti::attn_kernel<64, 1>, grid, dim3(128), 0, st, true, *p);
+    ti::launch_kernel(ti::attn_merge_kernel<64>, mgrid, dim3(128), 0, st, true, *p);
   } else {
     return -3;
   }

@@ -4,6 +4,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <utility>
 
 #define TI_HOST_DEVICE __host__ __device__ __forceinline__
 #define TI_DEVICE __device__ __forceinline__
@@ -139,6 +141,81 @@ TI_DEVICE bool wait_flag_ge(const uint32_t* flag, uint32_t want, unsigned long l
 }
 TI_DEVICE void store_flag_release(uint32_t* flag, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(flag), "r"(v) : "memory");
+}
+
+
+// ---------------------------------------------------------------- mbarrier + bulk async copy (TMA engine)
+TI_DEVICE uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+TI_DEVICE void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+TI_DEVICE void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
+TI_DEVICE void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+TI_DEVICE void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Linear global -> shared copy by the TMA engine; completion is signalled on `bar` as transferred bytes.
+// Both addresses 16-byte aligned, size a multiple of 16.  Source is this GPU's own memory.
+TI_DEVICE void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+TI_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait on an mbarrier phase.  Returns false (and raises kStatusPeerTimeout) when the budget
+// runs out, so a copy that never lands cannot hang the GPU.
+TI_DEVICE bool mbar_wait(uint32_t bar, uint32_t parity, unsigned long long budget_ns, unsigned* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 255u) == 0u && globaltimer_ns() - t0 > budget_ns) {
+      if (status != nullptr) atomicOr(status, kStatusPeerTimeout);
+      return false;
+    }
+  }
+  return true;
+}
+
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-serialization attribute may start while its predecessor in
+// the stream is still running; it must call pdl_wait() before it touches anything the predecessor
+// writes.  pdl_trigger() lets the successor start.  Kernels use the time before pdl_wait() to prefetch
+// data no earlier kernel of the step writes (weights, recurrent state).
+TI_DEVICE void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+TI_DEVICE void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+inline int& pdl_enabled() {
+  static int flag = [] {
+    const char* e = getenv("TI_PDL");
+    return e == nullptr ? 1 : atoi(e);
+  }();
+  return flag;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                 bool pdl, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = (pdl && pdl_enabled()) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 }  // namespace ti

@@ -57,6 +57,8 @@ __global__ void __launch_bounds__(DV * 4) gdn_kernel(const __grid_constant__ Gdn
   const int c = tid >> 2, dg = tid & 3;
   const int vh = blockIdx.x, s = blockIdx.y;
   const int kh = vh / (p.hv / p.hk);
+  // cu / slots are written by host copies that precede every kernel of the step; the recurrent state
+  // and conv history were last written one step ago: all of this may be read before pdl_wait()
   const int t0 = p.cu ? p.cu[s] : s, t1 = p.cu ? p.cu[s + 1] : s + 1;
   const int slot = p.slots[s];
 
@@ -85,6 +87,8 @@ __global__ void __launch_bounds__(DV * 4) gdn_kernel(const __grid_constant__ Gdn
   const float neg_a = p.neg_a_exp[vh], dtb = p.dt_bias[vh];
   const float nw = p.norm_w[c];
   const float qscale = rsqrtf((float)DK);
+  pdl_trigger();
+  pdl_wait();                                    // `proj` comes from the preceding projection kernel
 
   for (int tok = t0; tok < t1; ++tok) {
     const __nv_bfloat16* row = p.proj + (size_t)tok * p.ld;
@@ -173,11 +177,11 @@ int ti_gdn_step(const ti::GdnParams* p, int num_seqs, int dk, int dv, int state_
   dim3 grid(p->hv, num_seqs);
   cudaStream_t st = (cudaStream_t)stream;
   if (dk == 128 && dv == 128) {
-    if (state_bf16) ti::gdn_kernel<128, 128, __nv_bfloat16><<<grid, 512, 0, st>>>(*p);
-    else ti::gdn_kernel<128, 128, float><<<grid, 512, 0, st>>>(*p);
+    if (state_bf16) ti::launch_kernel(ti::gdn_kernel<128, 128, __nv_bfloat16>, grid, dim3(512), 0, st, true, *p);
+    else ti::launch_kernel(ti::gdn_kernel<128, 128, float>, grid, dim3(512), 0, st, true, *p);
   } else if (dk == 64 && dv == 64) {
-    if (state_bf16) ti::gdn_kernel<64, 64, __nv_bfloat16><<<grid, 256, 0, st>>>(*p);
-    else ti::gdn_kernel<64, 64, float><<<grid, 256, 0, st>>>(*p);
+    if (state_bf16) ti::launch_kernel(ti::gdn_kernel<64, 64, __nv_bfloat16>, grid, dim3(256), 0, st, true, *p);
+    else ti::launch_kernel(ti::gdn_kernel<64, 64, float>, grid, dim3(256), 0, st, true, *p);
   } else {
     return -3;
   }

@@ -74,6 +74,8 @@ __global__ void __launch_bounds__(256) topk_stage1_kernel(const __grid_constant_
   constexpr int EPT = 16;
   __shared__ Best sm[8];
   const int m = blockIdx.x, c = blockIdx.y;
+  pdl_trigger();
+  pdl_wait();
   const int lo = c * p.chunk_size, hi = min(p.V, lo + p.chunk_size);
   float val[EPT];
   int idx[EPT];
@@ -94,6 +96,8 @@ __global__ void __launch_bounds__(256) topk_stage2_kernel(const __grid_constant_
   __shared__ float fin_v[64];
   __shared__ int fin_i[64];
   const int m = blockIdx.x;
+  pdl_trigger();
+  pdl_wait();
   const int nc = p.chunks * p.k;
   float val[EPT];
   int idx[EPT];
@@ -148,8 +152,8 @@ int ti_topk(const ti::TopkParams* p, void* stream) {
   if ((long long)p->chunks * p->chunk_size < p->V) return -3;
   if (p->tp > ti::kMaxRanks || (p->tp > 1 && p->M > p->m_cap)) return -5;
   cudaStream_t st = (cudaStream_t)stream;
-  ti::topk_stage1_kernel<<<dim3(p->M, p->chunks), 256, 0, st>>>(*p);
-  ti::topk_stage2_kernel<<<p->M, 256, 0, st>>>(*p);
+  ti::launch_kernel(ti::topk_stage1_kernel, dim3(p->M, p->chunks), dim3(256), 0, st, true, *p);
+  ti::launch_kernel(ti::topk_stage2_kernel, dim3(p->M), dim3(256), 0, st, true, *p);
   return (int)cudaGetLastError();
 }
 

@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 
@@ -19,7 +20,10 @@ XGLOBAL, XNORM = 0, 1
 EPI_STORE, EPI_SWIGLU, EPI_ROWPAR, EPI_F32 = 0, 1, 2, 3
 W_INT8, W_BF16 = 0, 1
 NUM_SMS = 148
-GEMV_WARPS = 16
+GEMV_WARPS = 8
+GEMV_TPS = int(os.environ.get("TI_GEMV_TPS", "4"))            # 512-byte tiles per ring stage
+GEMV_MAX_STAGES = int(os.environ.get("TI_GEMV_STAGES", "6"))
+GEMV_UNITS_PER_WARP = int(os.environ.get("TI_GEMV_UPW", "4"))
 
 
 class GdnParams(ctypes.Structure):
@@ -120,13 +124,54 @@ class LinearW:
         return self.tiles.numel() * self.tiles.element_size()
 
 
-def plan_split(n_tiles: int, KB: int, ncta: int = NUM_SMS, min_kb: int = 4):
-    """(S, kb_per_split): enough (row-tile, k-range) units to occupy every warp about twice."""
+def _limb_stride(kslice: int) -> int:
+    return kslice + ((64 - (kslice % 128)) + 128) % 128
+
+
+def x_smem_bytes(wt: int, xmode: int, M: int, K: int, kslice: int) -> int:
+    """Shared memory the staged activations take (must mirror x_smem_bytes_impl in gemv_w8a16.cu)."""
+    b = 0
+    if wt == W_INT8:
+        b = 2 * M * _limb_stride(kslice)
+    elif xmode == XNORM:
+        b = (16 if M > 8 else 8) * (K + 8) * 2
+    return (b + 2048 + 127) // 128 * 128
+
+
+def plan_gemv(wt: int, xmode: int, M: int, n_tiles: int, KB: int, ncta: int = NUM_SMS, x_budget: int = 120 * 1024):
+    """(S, kb_per_split, J, stages).  About four (row-tile, k-range) units per warp, k-ranges in whole
+    2 KB ring stages; J CTA groups so that the int8 limb planes of one k-slice fit in `x_budget` bytes;
+    the ring takes what is left of the 227 KB."""
+    tk = 64 if wt == W_INT8 else 32
     warps = ncta * GEMV_WARPS
-    S = max(1, min(math.ceil(2 * warps / n_tiles), KB // min_kb if KB >= min_kb else 1))
-    kbps = math.ceil(KB / S)
-    S = math.ceil(KB / kbps)
-    return S, kbps
+    S = max(1, min(math.ceil(GEMV_UNITS_PER_WARP * warps / n_tiles), KB // 4 if KB >= 4 else 1))
+    J = 1
+    if wt == W_INT8:
+        J = max(1, math.ceil(2 * M * (KB * tk + 64) / x_budget))
+        S = math.ceil(S / J) * J
+    tps = GEMV_TPS
+    kbps = -(-math.ceil(KB / S) // tps) * tps
+    if J == 1:
+        S = math.ceil(KB / kbps)
+    kslice = min(KB, (S // J) * kbps) * tk
+    xb = x_smem_bytes(wt, xmode, M, KB * tk, kslice)
+    per_stage = GEMV_WARPS * (tps * 512 + 8)
+    # two CTAs per SM (this kernel's and the next kernel's, which prefetches under programmatic
+    # dependent launch) when the activations are small; the whole SM otherwise
+    budget = 113 * 1024 if xb <= 48 * 1024 else 227 * 1024
+    stages = int(max(1, min(GEMV_MAX_STAGES, (budget - xb - GEMV_WARPS * 64) // per_stage)))
+    return S, kbps, J, stages
+
+
+_STATUS = None
+
+
+def status_ptr() -> int:
+    """A process-wide device word that kernels OR error bits into when no communicator supplies one."""
+    global _STATUS
+    if _STATUS is None:
+        _STATUS = torch.zeros(4, dtype=torch.int32, device="cuda")
+    return _STATUS.data_ptr()
 
 
 class GemvWorkspace:
@@ -135,7 +180,18 @@ class GemvWorkspace:
     def __init__(self, device="cuda", max_units: int = 1 << 16, max_tiles: int = 1 << 16):
         self.ws = torch.empty(max_units * 128, dtype=torch.float32, device=device)
         self.counters = torch.zeros(max_tiles, dtype=torch.int32, device=device)
+        self.sched = torch.zeros(64, dtype=torch.int32, device=device)     # dynamic unit scheduling state
         self.max_units, self.max_tiles = max_units, max_tiles
+
+
+_DEFAULT_WS = None
+
+
+def default_workspace():
+    global _DEFAULT_WS
+    if _DEFAULT_WS is None:
+        _DEFAULT_WS = GemvWorkspace()
+    return _DEFAULT_WS
 
 
 def make_gemv_params(W: LinearW, x, out, M, *, xmode=XGLOBAL, epi=EPI_STORE, norm_w=None, resid=None, ws=None,
@@ -143,14 +199,21 @@ def make_gemv_params(W: LinearW, x, out, M, *, xmode=XGLOBAL, epi=EPI_STORE, nor
     p = GemvParams()
     p.w, p.scale, p.x, p.norm_w = ptr(W.tiles), ptr(W.scale), ptr(x), ptr(norm_w)
     p.out, p.resid = ptr(out), ptr(resid)
-    S, kbps = plan_split(W.n_tiles, W.KB, ncta)
+    S, kbps, J, stages = plan_gemv(W.wt, xmode, M, W.n_tiles, W.KB, ncta)
+    if ws is None:
+        ws = default_workspace()
     if S > 1:
-        assert ws is not None and W.n_tiles * S <= ws.max_units and W.n_tiles <= ws.max_tiles
+        assert W.n_tiles * S <= ws.max_units and W.n_tiles <= ws.max_tiles
         p.ws, p.counters = ptr(ws.ws), ptr(ws.counters)
     p.M, p.N, p.n_tiles, p.K, p.KB, p.S, p.kb_per_split = M, W.N, W.n_tiles, W.K, W.KB, S, kbps
     p.ldx = ldx if ldx is not None else (x.stride(0) if x.dim() > 1 else W.K)
     p.ldo = ldo if ldo is not None else (out.stride(0) if out.dim() > 1 else W.N)
     p.eps = eps
+    p.stages, p.J, p.tps = stages, J, GEMV_TPS
+    if ws is None:
+        ws = default_workspace()
+    p.sched = ptr(ws.sched)
+    p.status = status_ptr()
     p.tp, p.rank, p.order, p.m_cap = 1, 0, order, 0
     if comm is not None and comm.tp > 1:
         p.tp, p.rank, p.m_cap = comm.tp, comm.rank, comm.m_cap
