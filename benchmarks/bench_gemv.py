@@ -63,7 +63,7 @@ def main():
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1e3 / args.iters
         p0 = ps[0]
-        print(f"{name:10s} N={N:6d} K={K:6d} M={M} S={p0.S} kbps={p0.kb_per_split} J={p0.J} stages={p0.stages} "
+        print(f"{name:10s} N={N:6d} K={K:6d} M={M} R={p0.R} tps={p0.tps} stages={p0.stages} "
               f"{us:7.2f} us  {N * K / us / 1e3:7.1f} GB/s")
         if args.timeline:
             t = dbg.view(148, 8).cpu().double()

@@ -76,7 +76,7 @@ def test_gemv_rowpar_allreduce_emulated_ranks(tp):
     all-reduce in the GEMV epilogue must equal the sum of the per-rank partial products."""
     import ctypes
     F = _F()
-    from tileinfer_b200.ops.lib import GemvParams
+    from tileinfer_b200.ops.lib import ChainParams
     from tileinfer_b200.parallel.symm_mem import LocalRanks
     N, Kfull, M = 5120, 2048, 3
     K = Kfull // tp
@@ -93,10 +93,13 @@ def test_gemv_rowpar_allreduce_emulated_ranks(tp):
         ws = F.GemvWorkspace()
         p = F.make_gemv_params(W, xr, out, M, epi=F.EPI_ROWPAR, resid=resid, ws=ws, comm=ranks.view(r), order=0, ncta=ncta)
         Ws.append(W); outs.append(out); params.append(p); keep.append((xr, ws))
-    size = ctypes.sizeof(GemvParams)
-    blob = b"".join(bytes(p) for p in params)
+    size = ctypes.sizeof(ChainParams)
+    chains = [F.make_chain([p]) for p in params]
+    for c in chains:
+        assert F.L().ti_gemv_chain_prepare(ctypes.byref(c), F.W_INT8, ncta) == 0
+    blob = b"".join(bytes(c) for c in chains)
     dev_params = torch.frombuffer(bytearray(blob), dtype=torch.uint8).cuda()
-    rc = F.L().ti_gemv_ranks(ctypes.byref(params[0]), dev_params.data_ptr(), tp, F.W_INT8, F.XGLOBAL, F.EPI_ROWPAR, ncta,
+    rc = F.L().ti_gemv_ranks(ctypes.byref(chains[0]), dev_params.data_ptr(), tp, ncta,
                              torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     torch.cuda.synchronize()
@@ -108,6 +111,45 @@ def test_gemv_rowpar_allreduce_emulated_ranks(tp):
         torch.testing.assert_close(outs[r].float(), ref, rtol=2e-2, atol=3e-2)
         assert torch.equal(outs[r], outs[0]), "every rank must hold bit-identical results"
     assert size * tp == dev_params.numel()
+
+
+def test_gemv_chain_of_four_matches_separate_launches():
+    """out_proj -> gate_up(SwiGLU) -> down -> in_proj in ONE launch (grid barriers in between) must equal the
+    same four products launched one by one."""
+    F = _F()
+    H, I, KO, NI, M = 1024, 2048, 768, 1536, 3
+    Wo, Wgu = F.LinearW(_rand_w(H, KO, 11), True), F.LinearW(_rand_w(2 * I, H, 12), True)
+    Wd, Wi = F.LinearW(_rand_w(H, I, 13), True), F.LinearW(_rand_w(NI, H, 14), True)
+    x = torch.randn(M, KO, device="cuda").to(BF16)
+    h0 = torch.randn(M, H, device="cuda").to(BF16)
+    n1 = (torch.randn(H, device="cuda") * 0.1).to(BF16)
+    n2 = (torch.randn(H, device="cuda") * 0.1).to(BF16)
+
+    def run(chained):
+        ws = F.GemvWorkspace()
+        h1, h2 = torch.zeros_like(h0), torch.zeros_like(h0)
+        act = torch.zeros(M, I, dtype=BF16, device="cuda")
+        proj = torch.zeros(M, NI, dtype=BF16, device="cuda")
+        ps = [F.make_gemv_params(Wo, x, h1, M, xmode=F.XGLOBAL, epi=F.EPI_ROWPAR, resid=h0, ws=ws),
+              F.make_gemv_params(Wgu, h1, act, M, xmode=F.XNORM, epi=F.EPI_SWIGLU, norm_w=n1, ws=ws),
+              F.make_gemv_params(Wd, act, h2, M, xmode=F.XGLOBAL, epi=F.EPI_ROWPAR, resid=h1, ws=ws),
+              F.make_gemv_params(Wi, h2, proj, M, xmode=F.XNORM, epi=F.EPI_STORE, norm_w=n2, ws=ws)]
+        if chained:
+            F.gemv_chain_launch(ps, F.W_INT8)
+        else:
+            for p in ps:
+                F.gemv_launch(p, F.W_INT8)
+        torch.cuda.synchronize()
+        assert int(ws.sched[2]) == 0 and int(ws.sched[8:72].abs().sum()) == 0 and int(ws.counters.abs().sum()) == 0
+        return h1, act, h2, proj
+    a, b = run(False), run(True)
+    for u, v in zip(a, b):
+        assert torch.equal(u, v)
+    ref_h1 = h0.float() + x.float() @ Wo.dense().float().t()
+    torch.testing.assert_close(a[0].float(), ref_h1, rtol=2e-2, atol=3e-2)
+    for _ in range(3):                      # replays keep working (tickets and barrier counter reset themselves)
+        c = run(True)
+        assert all(torch.equal(u, v) for u, v in zip(b, c))
 
 
 def test_bounded_wait_reports_timeout_and_context_survives():

@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import gc
 import math
+import os
 
 import torch
 
@@ -112,6 +113,8 @@ class _ModelBase:
         self.mix_cols = max(self.hv * self.dv, self.hq * self.D)
         self.launches_per_decode_step = 0
         self._launches = 0
+        self._pending, self._pending_wt = [], 0
+        self.chain = os.environ.get("TI_GEMV_CHAIN", "1") != "0"
 
     # ------------------------------------------------------------------ caches
     def weight_bytes(self) -> int:
@@ -208,8 +211,9 @@ class _StepMixin:
     # ------------------------------------------------------------------ launches
     def _gemv(self, W: LinearW, x, out, M, *, xmode, epi, norm_w=None, resid=None, ldo=None):
         """y = x W^T in row chunks of 16; counts launches; assigns collective order numbers."""
-        for m0 in range(0, M, 16):
-            m = min(16, M - m0)
+        step = F.max_rows(W.wt, xmode, W.K)
+        for m0 in range(0, M, step):
+            m = min(step, M - m0)
             order = 0
             if epi == EPI_ROWPAR:
                 order = self._order
@@ -219,8 +223,21 @@ class _StepMixin:
                 resid=None if resid is None else resid[m0:m0 + m], ws=self.ws, eps=self.cfg.rms_eps,
                 ldx=x.stride(0), ldo=out.stride(0) if ldo is None else ldo,
                 comm=self.peer if epi == EPI_ROWPAR else None, order=order)
-            F.gemv_launch(p, W.wt, xmode, epi)
+            if M <= step and self.chain:
+                # dependent products are collected and launched together (up to four per launch)
+                if self._pending and (self._pending_wt != W.wt or len(self._pending) >= F.MAX_CHAIN):
+                    self._flush()
+                self._pending.append(p)
+                self._pending_wt = W.wt
+            else:
+                F.gemv_launch(p, W.wt, xmode, epi)
+                self._launches += 1
+
+    def _flush(self):
+        if self._pending:
+            F.gemv_chain_launch(self._pending, self._pending_wt)
             self._launches += 1
+            self._pending = []
 
     def _rowpar(self, W: LinearW, x, resid, out, M):
         """Row-parallel projection + all-reduce + residual add -> out."""
@@ -230,6 +247,7 @@ class _StepMixin:
         # baseline: partial sums in bf16, NCCL all-reduce, separate residual add (the reference's structure)
         part = torch.empty(M, W.N, dtype=BF16, device=self.dev)
         self._gemv(W, x, part, M, xmode=XGLOBAL, epi=EPI_STORE)
+        self._flush()
         self.comm.all_reduce(part)
         torch.add(resid[:M], part, out=out[:M])
         self._launches += 2
@@ -253,6 +271,7 @@ class _StepMixin:
                 if x.snap_rel is not None:
                     p.snap_rel, p.num_snap = ptr(x.snap_rel), x.num_snap
                     p.snap_state, p.snap_conv = ptr(x.snap_state[ig]), ptr(x.snap_conv[ig])
+                self._flush()
                 F.gdn_step(p, S, self.dk, self.dv, self.state_bf16)
                 self._launches += 1
                 # the kernel writes [T, hv*dv] densely
@@ -267,6 +286,7 @@ class _StepMixin:
                 q.kcache, q.vcache = ptr(self.kv[ia, 0]), ptr(self.kv[ia, 1])
                 q.ld, q.hq, q.hkv, q.rotary_dim = x.proj.stride(0), self.hq, self.hkv, c.rotary_dim
                 q.eps, q.log2_theta = eps, math.log2(c.rope_theta)
+                self._flush()
                 F.qkv_prep(q, T, self.D)
                 a = AttnParams()
                 a.q, a.kcache, a.vcache = ptr(x.qbuf), ptr(self.kv[ia, 0]), ptr(self.kv[ia, 1])
@@ -286,6 +306,7 @@ class _StepMixin:
             self._gemv(L.gate_up, cur, x.act, T, xmode=XNORM, epi=EPI_SWIGLU, norm_w=L.post_norm)
             self._rowpar(L.down, x.act, cur, nxt, T)
             cur, nxt = nxt, cur
+        self._flush()
         return cur
 
 
@@ -325,6 +346,7 @@ class _RunMixin:
 
     def _lm_head(self, hidden, logits, n):
         self._gemv(self.lm_head, hidden, logits, n, xmode=XNORM, epi=EPI_F32, norm_w=self.final_norm)
+        self._flush()
 
     def _topk_rows(self, logits, n, k):
         """Per-rank top-k (+ fused candidate exchange); rows in chunks of the peer buffer capacity."""

@@ -55,6 +55,18 @@ struct GemvParams {
   unsigned long long* dbg;       // optional [ncta][8] globaltimer stamps of warp 0 (profiling aid)
   int* sched;                    // dynamic scheduling state: [0] launches finished, [1] CTAs finished, [8 + 3*16] tickets
   int tps;                       // 512-byte tiles per ring stage (4, 8 or 16)
+  int xmode, epi;                // XGLOBAL | XNORM ; EPI_*
+  int R;                         // row tiles (of 8 weight rows) per unit: 1 or 2
+};
+
+// Up to four dependent products run back to back in one launch (e.g. out_proj -> gate_up -> down -> the
+// next layer's in_proj): a grid barrier separates them, the weight streams of the warps run ahead into the
+// next product while the barrier and the activation staging take place, so HBM never drains between them.
+constexpr int kMaxChain = 4;
+struct ChainParams {
+  int n_ops;
+  int x_bytes;                   // shared memory reserved for staged activations (max over the ops)
+  GemvParams op[kMaxChain];
 };
 
 // Shared-memory footprint of the staged activations (+ 2 KB of reduction scratch).
@@ -71,11 +83,13 @@ enum { XGLOBAL = 0, XNORM = 1 };
 enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ROWPAR = 2, EPI_F32 = 3 };
 enum { W_INT8 = 0, W_BF16 = 1 };
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 512;
 constexpr int kMaxTilesPerStage = 16;
-constexpr int kQueue = 16;                 // per-warp queue of fetched unit indices
+constexpr int kWarps = kThreads / 32;
+constexpr int kCQ = 32;                    // CTA queue of scheduled units
+constexpr int kLook = 6;                   // units the scheduler keeps queued ahead of the consumer
+constexpr int kMaxR = 2;                   // row tiles per unit
 
-template <int EPI>
 TI_DEVICE void epilogue(const GemvParams& p, int nt, int g, int t, const float (&acc)[4]) {
   const int n = nt * 8 + 2 * t;
   if (n >= p.N) return;
@@ -89,13 +103,13 @@ TI_DEVICE void epilogue(const GemvParams& p, int nt, int g, int t, const float (
     const int m = g + half * 8;
     if (m >= p.M) continue;
     float v0 = acc[half * 2] * s0, v1 = acc[half * 2 + 1] * s1;
-    if (EPI == EPI_STORE) {
+    if (p.epi == EPI_STORE) {
       uint32_t* o = reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + n);
       *o = pack_bf16(v0, v1);
-    } else if (EPI == EPI_F32) {
+    } else if (p.epi == EPI_F32) {
       float2* o = reinterpret_cast<float2*>(static_cast<float*>(p.out) + (size_t)m * p.ldo + n);
       *o = make_float2(v0, v1);
-    } else if (EPI == EPI_SWIGLU) {
+    } else if (p.epi == EPI_SWIGLU) {
       // rows come interleaved (gate, up); both are rounded to bf16 first, as a separate activation
       // kernel reading bf16 projections would see them
       const float gate = round_bf16(v0), up = round_bf16(v1);
@@ -122,13 +136,17 @@ TI_DEVICE void epilogue(const GemvParams& p, int nt, int g, int t, const float (
           sum1 += b;
         }
       }
-      const uint32_t rw = *reinterpret_cast<const uint32_t*>(p.resid + (size_t)m * p.N + n);
+      const uint32_t rw = __ldcg(reinterpret_cast<const uint32_t*>(p.resid + (size_t)m * p.N + n));
       uint32_t* o = reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.N + n);
       *o = pack_bf16(bf16lo(rw) + sum0, bf16hi(rw) + sum1);
     }
   }
 }
 
+
+// Activations may have been written earlier in the SAME launch by another SM (chained products): read them
+// through L2, never through the non-coherent path.
+TI_DEVICE uint4 ld_x16(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
 
 // ---------------------------------------------------------------- integer tensor-core MMAs
 TI_DEVICE void imma_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -144,97 +162,8 @@ TI_DEVICE void imma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uin
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// ---------------------------------------------------------------- work decomposition
-// A unit is (row tile nt, k-split ks).  CTAs form J groups (group j = CTAs with cta % J == j); group j
-// owns the k-splits [j*S/J, (j+1)*S/J) and stages only that slice of x.  Inside a group the units are
-// dealt round-robin to the warps.
-struct Group {
-  int j, ssub, widx, wcount, units, kbs0, kbs1;
-};
-TI_DEVICE Group make_group(const GemvParams& p, int cta, int ncta, int warp, int nwarps) {
-  Group gr;
-  gr.j = cta % p.J;
-  gr.ssub = p.S / p.J;
-  gr.widx = (cta / p.J) * nwarps + warp;
-  gr.wcount = ((ncta - gr.j + p.J - 1) / p.J) * nwarps;
-  gr.units = p.n_tiles * gr.ssub;
-  gr.kbs0 = min(p.KB, gr.j * gr.ssub * p.kb_per_split);
-  gr.kbs1 = min(p.KB, gr.kbs0 + gr.ssub * p.kb_per_split);
-  return gr;
-}
-struct Unit { int nt, ks, kb0, nkb; };
-TI_DEVICE Unit unit_of(const GemvParams& p, const Group& gr, int ul) {
-  Unit u;
-  u.nt = ul / gr.ssub;
-  u.ks = gr.j * gr.ssub + (ul - u.nt * gr.ssub);
-  u.kb0 = u.ks * p.kb_per_split;
-  u.nkb = max(0, min(p.KB, u.kb0 + p.kb_per_split) - u.kb0);
-  return u;
-}
-
-// Cursor of the warp-private weight stream (used by lane 0 only).  Units are handed out dynamically:
-// a ticket counter per CTA group is advanced with atomicAdd, so a warp that falls behind (slow HBM
-// channel, long epilogue wait) simply takes fewer units.  Fetched unit indices go through a small
-// queue so that the consuming side sees them in the same order; each unit is cut into chunks of at
-// most `tps` consecutive 512-byte tiles that the TMA engine copies into the ring, stage after stage.
-struct IssueCursor {
-  int ul, tile, nkb, idx, wr, rd, pre;
-  bool done, can_fetch;
-  size_t base;
-  // The first unit of every warp is assigned statically (unit = warp index in its group), so its
-  // weights can be requested before the kernel is allowed to look at any mutable state; tickets then
-  // number the remaining units from gr.wcount on.
-  TI_DEVICE void take_static(const GemvParams& p, const Group& gr, volatile int* q) {
-    ul = -1;
-    if (gr.widx >= gr.units) return;
-    q[wr++ % kQueue] = gr.widx;
-    const Unit un = unit_of(p, gr, gr.widx);
-    if (un.nkb > 0) {
-      ul = gr.widx;
-      nkb = un.nkb;
-      base = ((size_t)un.nt * p.KB + un.kb0) * 512;
-      tile = 0;
-    }
-  }
-  TI_DEVICE void fetch(const GemvParams& p, const Group& gr, int* ticket, volatile int* q) {
-    ul = -1;
-    while (!done && wr - rd < kQueue - 1) {
-      const int u = gr.wcount + pre;     // ticket drawn one unit ago: its latency is already paid
-      pre = atomicAdd(ticket, 1);
-      if (u >= gr.units) {
-        q[wr++ % kQueue] = -1;
-        done = true;
-        return;
-      }
-      q[wr++ % kQueue] = u;
-      const Unit un = unit_of(p, gr, u);
-      if (un.nkb > 0) {
-        ul = u;
-        nkb = un.nkb;
-        base = ((size_t)un.nt * p.KB + un.kb0) * 512;
-        tile = 0;
-        return;
-      }
-    }
-  }
-  TI_DEVICE void next(const GemvParams& p, const Group& gr, int* ticket, volatile int* q, uint32_t ring_u32,
-                      uint32_t bar0, int stages) {
-    if (ul < 0 && can_fetch) fetch(p, gr, ticket, q);
-    if (ul < 0) return;
-    const int ntile = min(p.tps, nkb - tile);
-    const uint32_t st = (uint32_t)idx % (uint32_t)stages;
-    const uint32_t bytes = (uint32_t)ntile * 512u;
-    mbar_expect_tx(bar0 + st * 8, bytes);
-    bulk_g2s(ring_u32 + st * (uint32_t)p.tps * 512u, p.w + base + (size_t)tile * 512, bytes, bar0 + st * 8);
-    ++idx;
-    tile += ntile;
-    if (tile >= nkb) ul = -1;
-  }
-};
-
 // ---------------------------------------------------------------- activation staging
 // Per-row statistics scratch: red[nwarps][16] then rowv[16] (rrms), rows[16] (limb scale 2^(e-14)).
-template <int XMODE>
 TI_DEVICE void block_row_reduce(float (&v)[16], int M, float* red, float* out, int tid, bool is_max) {
   const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
   for (int m = 0; m < M; ++m) {
@@ -252,7 +181,6 @@ TI_DEVICE void block_row_reduce(float (&v)[16], int M, float* red, float* out, i
 
 // Stages the k-slice [k_lo, k_hi) of up to 16 rows as two int8 limb planes.  XNORM: the rows are first
 // RMS-normalised with (1+w) (statistics over the full row) and rounded to bf16.
-template <int XMODE>
 TI_DEVICE void stage_limbs(const GemvParams& p, int k_lo, int k_hi, int8_t* xh, uint8_t* xl, int stride, float* scratch) {
   const int tid = threadIdx.x;
   float* red = scratch;            // [16 warps][16]
@@ -261,7 +189,7 @@ TI_DEVICE void stage_limbs(const GemvParams& p, int k_lo, int k_hi, int8_t* xh, 
   float* inv = scratch + 288;      // [16]  2^(e-14): value of one fixed-point unit
   const int nthreads = blockDim.x;
   // ---- single-row fast path (batch-1 decode): the row lives in registers, read from memory once
-  if (p.M == 1 && (k_hi - k_lo) <= 40 * nthreads && (XMODE != XNORM || (k_lo == 0 && k_hi == p.K))) {
+  if (p.M == 1 && (k_hi - k_lo) <= 40 * nthreads && (p.xmode != XNORM || (k_lo == 0 && k_hi == p.K))) {
     const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
     const int c_lo = k_lo >> 3, c_hi = k_hi >> 3;
     float v[5][8];
@@ -270,7 +198,7 @@ TI_DEVICE void stage_limbs(const GemvParams& p, int k_lo, int k_hi, int8_t* xh, 
     for (int j = 0; j < 5; ++j) {
       const int c = c_lo + tid + j * nthreads;
       uint4 q = make_uint4(0, 0, 0, 0);
-      if (c < c_hi) q = ldg_cached16(p.x + (size_t)c * 8);
+      if (c < c_hi) q = ld_x16(p.x + (size_t)c * 8);
       const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -279,7 +207,7 @@ TI_DEVICE void stage_limbs(const GemvParams& p, int k_lo, int k_hi, int8_t* xh, 
         ss += v[j][2 * i] * v[j][2 * i] + v[j][2 * i + 1] * v[j][2 * i + 1];
       }
     }
-    if (XMODE == XNORM) {
+    if (p.xmode == XNORM) {
       ss = warp_sum(ss);
       if (lane == 0) red[warp] = ss;
       __syncthreads();
@@ -333,20 +261,20 @@ TI_DEVICE void stage_limbs(const GemvParams& p, int k_lo, int k_hi, int8_t* xh, 
     return;
   }
   float acc[16];
-  if (XMODE == XNORM) {
+  if (p.xmode == XNORM) {
 #pragma unroll
     for (int m = 0; m < 16; ++m) acc[m] = 0.f;
     for (int c = tid; c < (p.K >> 3); c += blockDim.x) {
 #pragma unroll
       for (int m = 0; m < 16; ++m) {
         if (m >= p.M) break;
-        const uint4 v = ldg_cached16(p.x + (size_t)m * p.ldx + c * 8);
+        const uint4 v = ld_x16(p.x + (size_t)m * p.ldx + c * 8);
         const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[m] += bf16lo(w4[i]) * bf16lo(w4[i]) + bf16hi(w4[i]) * bf16hi(w4[i]);
       }
     }
-    block_row_reduce<XMODE>(acc, p.M, red, rrms, tid, false);
+    block_row_reduce(acc, p.M, red, rrms, tid, false);
     if (tid < p.M) rrms[tid] = rsqrtf(rrms[tid] / (float)p.K + p.eps);
     __syncthreads();
   }
@@ -356,18 +284,18 @@ TI_DEVICE void stage_limbs(const GemvParams& p, int k_lo, int k_hi, int8_t* xh, 
   const int c_lo = k_lo >> 3, c_hi = k_hi >> 3;
   for (int c = c_lo + tid; c < c_hi; c += blockDim.x) {
     uint4 nw = make_uint4(0, 0, 0, 0);
-    if (XMODE == XNORM) nw = ldg_cached16(p.norm_w + c * 8);
+    if (p.xmode == XNORM) nw = ldg_cached16(p.norm_w + c * 8);
     const uint32_t n4[4] = {nw.x, nw.y, nw.z, nw.w};
 #pragma unroll
     for (int m = 0; m < 16; ++m) {
       if (m >= p.M) break;
-      const uint4 v = ldg_cached16(p.x + (size_t)m * p.ldx + c * 8);
+      const uint4 v = ld_x16(p.x + (size_t)m * p.ldx + c * 8);
       const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
-      const float rr = XMODE == XNORM ? rrms[m] : 1.f;
+      const float rr = p.xmode == XNORM ? rrms[m] : 1.f;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float a = bf16lo(w4[i]), b = bf16hi(w4[i]);
-        if (XMODE == XNORM) {
+        if (p.xmode == XNORM) {
           a = round_bf16(a * rr * (1.f + bf16lo(n4[i])));
           b = round_bf16(b * rr * (1.f + bf16hi(n4[i])));
         }
@@ -375,7 +303,7 @@ TI_DEVICE void stage_limbs(const GemvParams& p, int k_lo, int k_hi, int8_t* xh, 
       }
     }
   }
-  block_row_reduce<XMODE>(acc, p.M, red, amax, tid, true);
+  block_row_reduce(acc, p.M, red, amax, tid, true);
   if (tid < p.M) {
     const float a = amax[tid];
     int e = (int)((__float_as_uint(a) >> 23) & 0xffu) - 127;
@@ -388,19 +316,19 @@ TI_DEVICE void stage_limbs(const GemvParams& p, int k_lo, int k_hi, int8_t* xh, 
   // pass B: quantise and store the limb planes
   for (int c = c_lo + tid; c < c_hi; c += blockDim.x) {
     uint4 nw = make_uint4(0, 0, 0, 0);
-    if (XMODE == XNORM) nw = ldg_cached16(p.norm_w + c * 8);
+    if (p.xmode == XNORM) nw = ldg_cached16(p.norm_w + c * 8);
     const uint32_t n4[4] = {nw.x, nw.y, nw.z, nw.w};
 #pragma unroll
     for (int m = 0; m < 16; ++m) {
       if (m >= p.M) break;
-      const uint4 v = ldg_cached16(p.x + (size_t)m * p.ldx + c * 8);
+      const uint4 v = ld_x16(p.x + (size_t)m * p.ldx + c * 8);
       const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
-      const float rr = XMODE == XNORM ? rrms[m] : 1.f, qs = amax[m];
+      const float rr = p.xmode == XNORM ? rrms[m] : 1.f, qs = amax[m];
       uint32_t hw[2] = {0, 0}, lw[2] = {0, 0};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float a = bf16lo(w4[i]), b = bf16hi(w4[i]);
-        if (XMODE == XNORM) {
+        if (p.xmode == XNORM) {
           a = round_bf16(a * rr * (1.f + bf16lo(n4[i])));
           b = round_bf16(b * rr * (1.f + bf16hi(n4[i])));
         }
@@ -434,13 +362,13 @@ TI_DEVICE void stage_bf16_norm(const GemvParams& p, __nv_bfloat16* xs, int xs_st
 #pragma unroll
     for (int m = 0; m < 16; ++m) {
       if (m >= p.M) break;
-      const uint4 v = ldg_cached16(p.x + (size_t)m * p.ldx + c * 8);
+      const uint4 v = ld_x16(p.x + (size_t)m * p.ldx + c * 8);
       const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[m] += bf16lo(w4[i]) * bf16lo(w4[i]) + bf16hi(w4[i]) * bf16hi(w4[i]);
     }
   }
-  block_row_reduce<XNORM>(acc, p.M, red, rrms, tid, false);
+  block_row_reduce(acc, p.M, red, rrms, tid, false);
   if (tid < p.M) rrms[tid] = rsqrtf(rrms[tid] / (float)p.K + p.eps);
   __syncthreads();
   for (int c = tid; c < chunks; c += blockDim.x) {
@@ -449,7 +377,7 @@ TI_DEVICE void stage_bf16_norm(const GemvParams& p, __nv_bfloat16* xs, int xs_st
     for (int m = 0; m < rows; ++m) {
       uint4 o = make_uint4(0, 0, 0, 0);
       if (m < p.M) {
-        const uint4 v = ldg_cached16(p.x + (size_t)m * p.ldx + c * 8);
+        const uint4 v = ld_x16(p.x + (size_t)m * p.ldx + c * 8);
         const uint32_t a4[4] = {v.x, v.y, v.z, v.w};
         const float rr = rrms[m];
         uint32_t r4[4];
@@ -464,231 +392,399 @@ TI_DEVICE void stage_bf16_norm(const GemvParams& p, __nv_bfloat16* xs, int xs_st
   __syncthreads();
 }
 
-// ---------------------------------------------------------------- split-k bookkeeping
-// The warp that brings a row tile's arrival counter to S sums the S partials in a fixed order
-// (deterministic) and runs the epilogue.
-TI_DEVICE int splitk_announce(const GemvParams& p, int pend_nt, unsigned& tk_val, int lane) {
-  if (pend_nt < 0) return -1;
-  __threadfence();
-  __syncwarp();
-  if (lane == 0) tk_val = atomicAdd(p.counters + pend_nt, 1u);
-  return pend_nt;
-}
-template <int EPI>
-TI_DEVICE void splitk_settle(const GemvParams& p, int tk_nt, unsigned tk_val, int g, int t, int lane) {
-  if (tk_nt < 0) return;
-  const unsigned prev = __shfl_sync(0xffffffffu, tk_val, 0);
-  if (prev != (unsigned)p.S - 1u) return;
-  __threadfence();
-  float sum[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int s = 0; s < p.S; ++s) {
-    const float4 v = __ldcg(reinterpret_cast<const float4*>(p.ws + ((size_t)tk_nt * p.S + s) * 128 + lane * 4));
-    sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
+// ---------------------------------------------------------------- work decomposition
+// A unit is R consecutive row tiles (8 weight rows each) over the WHOLE k range; the 16 warps of a CTA
+// split k evenly and meet in shared memory, so no partial sum ever leaves the SM and nothing is fenced
+// or counted in global memory.  Units are dealt to CTAs: the first one statically (unit = CTA index),
+// the rest through one ticket counter per product, drawn a unit ahead by a scheduler thread (warp 0,
+// lane 0) that keeps a CTA-wide queue of the next units.  Every warp runs a private weight stream
+// (TMA bulk copies into its ring) along that queue, as far ahead as its ring allows, also across the
+// products of a chain.
+TI_DEVICE int num_units(const GemvParams& p) { return (p.n_tiles + p.R - 1) / p.R; }
+#define TI_UNIT_END (-1)
+TI_DEVICE int pack_unit(int op, int unit) { return (op << 26) | unit; }
+
+// Units k*ncta + cta for k < num_static are assigned statically (no atomics: they can be queued before the
+// kernel may look at mutable state and they fill the look-ahead at once); the second half of a product's
+// units is handed out through the ticket counter, which evens out CTAs that fell behind.
+TI_DEVICE int num_static(const GemvParams& p, int ncta) { return max(1, num_units(p) / (2 * ncta)); }
+
+struct Scheduler {            // registers of warp 0 / lane 0; queue storage in shared memory
+  int op, pre, sk;
+  bool pre_valid, done, can_ticket;
+  TI_DEVICE void push(volatile int* cq, volatile int* wr, int e) {
+    const int w = *wr;
+    cq[w % kCQ] = e;
+    __threadfence_block();
+    *wr = w + 1;
   }
-  if (lane == 0) p.counters[tk_nt] = 0u;
-  epilogue<EPI>(p, tk_nt, g, t, sum);
+  TI_DEVICE void fill(const ChainParams& c, int cta, int ncta, volatile int* cq, volatile int* wr, int upto) {
+    while (!done && *wr < upto) {
+      const GemvParams& p = c.op[op];
+      const int U = num_units(p), ns = num_static(p, ncta);
+      if (sk < ns) {
+        const int u = sk * ncta + cta;
+        ++sk;
+        if (u < U) push(cq, wr, pack_unit(op, u));
+        continue;
+      }
+      if (!can_ticket) return;
+      int* ticket = p.sched + 8 + op * 16;
+      if (!pre_valid) {
+        pre = atomicAdd(ticket, 1);
+        pre_valid = true;
+      }
+      const int u = ns * ncta + pre;
+      if (u >= U) {
+        sk = 0;
+        pre_valid = false;
+        if (++op >= c.n_ops) {
+          push(cq, wr, TI_UNIT_END);
+          done = true;
+        }
+        continue;
+      }
+      pre = atomicAdd(ticket, 1);          // next ticket, used one unit from now
+      push(cq, wr, pack_unit(op, u));
+    }
+  }
+  // draw the first ticket of the current product early so that its latency is hidden
+  TI_DEVICE void warm(const ChainParams& c) {
+    if (!done && can_ticket && !pre_valid) {
+      pre = atomicAdd(c.op[op].sched + 8 + op * 16, 1);
+      pre_valid = true;
+    }
+  }
+};
+
+struct WarpCursor {           // registers of lane 0 of each warp
+  int seq, r, rn, tile, nkb, idx;
+  bool have, done;
+  size_t base, rstride;
+  const uint8_t* w;
+  TI_DEVICE bool load(const ChainParams& c, int warp, volatile int* cq, volatile int* wr) {
+    while (!done && seq < *wr) {
+      const int e = cq[seq % kCQ];
+      if (e == TI_UNIT_END) {
+        done = true;
+        return false;
+      }
+      const GemvParams& p = c.op[e >> 26];
+      const int unit = e & ((1 << 26) - 1);
+      const int kb_lo = (warp * p.KB) / kWarps, kb_hi = ((warp + 1) * p.KB) / kWarps;
+      nkb = kb_hi - kb_lo;
+      if (nkb <= 0) {                      // fewer k tiles than warps: nothing to stream for this unit
+        ++seq;
+        continue;
+      }
+      rn = min(p.R, p.n_tiles - unit * p.R);
+      r = 0;
+      tile = 0;
+      w = p.w;
+      rstride = (size_t)p.KB * 512;
+      base = ((size_t)unit * p.R * p.KB + kb_lo) * 512;
+      have = true;
+      return true;
+    }
+    return false;
+  }
+  TI_DEVICE void next(const ChainParams& c, int warp, volatile int* cq, volatile int* wr, uint32_t ring_u32,
+                      uint32_t bar0, int stages, int tps) {
+    if (!have && !load(c, warp, cq, wr)) return;
+    const int ntile = min(tps, nkb - tile);
+    const uint32_t st = (uint32_t)idx % (uint32_t)stages;
+    const uint32_t bytes = (uint32_t)ntile * 512u;
+    mbar_expect_tx(bar0 + st * 8, bytes);
+    bulk_g2s(ring_u32 + st * (uint32_t)tps * 512u, w + base + (size_t)r * rstride + (size_t)tile * 512, bytes,
+             bar0 + st * 8);
+    ++idx;
+    tile += ntile;
+    if (tile >= nkb) {
+      tile = 0;
+      if (++r >= rn) {
+        have = false;
+        ++seq;
+      }
+    }
+  }
+};
+
+// Grid-wide barrier between chained products.  All CTAs of the launch are resident (one per SM), the
+// counter is reset by the last CTA of the launch.  The wait is bounded like every other wait here.
+TI_DEVICE void grid_barrier(int* counter, int target, unsigned* status) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(counter, 1);
+    const unsigned long long t0 = globaltimer_ns();
+    unsigned spins = 0;
+    while (true) {
+      int v;
+      asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(counter) : "memory");
+      if (v >= target) break;
+      if ((++spins & 63u) == 0u && globaltimer_ns() - t0 > 2000000000ull) {
+        if (status != nullptr) atomicOr(status, kStatusPeerTimeout);
+        break;
+      }
+    }
+    __threadfence();
+  }
+  __syncthreads();
 }
 
 // ---------------------------------------------------------------- main body
-template <int WT, int XMODE, int EPI>
-TI_DEVICE void gemv_body(const GemvParams& p, int cta, int ncta, uint8_t* smem) {
+template <int WT>
+TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int nwarps = blockDim.x >> 5;
-  const bool hi = p.M > 8;
-  const Group gr = make_group(p, cta, ncta, warp, nwarps);
-  const bool stamp = p.dbg != nullptr && tid == 0;
-  if (stamp) p.dbg[cta * 8 + 0] = globaltimer_ns();
-  const int kslice = (gr.kbs1 - gr.kbs0) * (WT == W_INT8 ? 64 : 32);
-  const int kslice_max = min(p.KB, (p.S / p.J) * p.kb_per_split) * (WT == W_INT8 ? 64 : 32);
-  const size_t x_bytes = x_smem_bytes_impl(WT, XMODE, p.M, p.K, kslice_max);
+  const GemvParams& p0 = c.op[0];
+  const bool stamp = p0.dbg != nullptr && tid == 0;
+  if (stamp) p0.dbg[cta * 8 + 0] = globaltimer_ns();
+  const size_t x_bytes = (size_t)c.x_bytes;
 
-  // ---- weight stream first: the ring fills while the activations are being staged
-  const int stages = p.stages;
-  const int stage_bytes = p.tps * 512;
-  uint8_t* ring = smem + x_bytes + (size_t)warp * stages * stage_bytes;
+  // ---- shared memory: [staged x | per-warp partial sums (2 buffers) | rings | mbarriers | unit queue]
+  const int stages = p0.stages, tps = p0.tps;
+  const int stage_bytes = tps * 512;
+  float* part = reinterpret_cast<float*>(smem + x_bytes);                        // [2][kWarps][kMaxR][128]
+  uint8_t* ring0 = smem + x_bytes + 2 * kWarps * kMaxR * 512;
+  uint8_t* ring = ring0 + (size_t)warp * stages * stage_bytes;
   const uint32_t ring_u32 = smem_u32(ring);
-  uint8_t* after_ring = smem + x_bytes + (size_t)nwarps * stages * stage_bytes;
+  uint8_t* after_ring = ring0 + (size_t)kWarps * stages * stage_bytes;
   const uint32_t bar0 = smem_u32(after_ring) + warp * stages * 8;
-  volatile int* queue = reinterpret_cast<volatile int*>(after_ring + nwarps * stages * 8) + warp * kQueue;
-  IssueCursor issue;
-  issue.ul = -1;
-  issue.idx = issue.wr = issue.rd = 0;
-  issue.nkb = issue.tile = 0;
-  issue.base = 0;
-  issue.done = false;
-  issue.can_fetch = false;
-  issue.pre = 0;
+  volatile int* cq = reinterpret_cast<volatile int*>(after_ring + kWarps * stages * 8);
+  volatile int* cq_wr = cq + kCQ;
+
+  Scheduler sch;
+  sch.op = sch.pre = sch.sk = 0;
+  sch.pre_valid = sch.done = sch.can_ticket = false;
+  if (tid == 0) {
+    *cq_wr = 0;
+    sch.fill(c, cta, ncta, cq, cq_wr, kLook);      // static units of the first product only (no tickets yet)
+  }
+  __syncthreads();
+  WarpCursor cur;
+  cur.seq = cur.r = cur.rn = cur.tile = cur.nkb = cur.idx = 0;
+  cur.have = cur.done = false;
+  cur.base = cur.rstride = 0;
+  cur.w = nullptr;
   if (lane == 0) {
     for (int s = 0; s < stages; ++s) mbar_init(bar0 + s * 8, 1);
     fence_mbar_init();
-    issue.take_static(p, gr, queue);
-    for (int s = 0; s < stages; ++s) issue.next(p, gr, nullptr, queue, ring_u32, bar0, stages);
+    for (int s = 0; s < stages; ++s) cur.next(c, warp, cq, cq_wr, ring_u32, bar0, stages, tps);
   }
   __syncwarp();
   // Everything above touched only weights and this CTA's shared memory.  Let the next kernel of the
   // stream start its own prefetch, then wait until the previous kernel (which produced x and may still
-  // be using the split-k workspace, the arrival counters and the tickets) has completed.
+  // be using the tickets) has completed.
   pdl_trigger();
   pdl_wait();
-  if (stamp) p.dbg[cta * 8 + 1] = globaltimer_ns();
-  // ticket counters rotate over three slots: this launch uses slot (launches finished) % 3, which the
-  // previous launch zeroed, and zeroes the slot of the next launch
-  const int seq = *reinterpret_cast<volatile int*>(p.sched);
-  int* ticket = p.sched + 8 + (seq % 3) * 16 + gr.j;
-  if (cta == 0 && tid < 16) p.sched[8 + ((seq + 1) % 3) * 16 + tid] = 0;
-  if (lane == 0) {
-    issue.pre = atomicAdd(ticket, 1);
-    issue.can_fetch = true;
+  if (stamp) p0.dbg[cta * 8 + 1] = globaltimer_ns();
+  if (tid == 0) {
+    sch.can_ticket = true;
+    sch.warm(c);
   }
 
-  // ---- activations
-  float* scratch = reinterpret_cast<float*>(smem + x_bytes - 2048);
-  const int lstride = limb_stride(kslice_max);
-  int8_t* xh = reinterpret_cast<int8_t*>(smem);
-  uint8_t* xl = smem + (size_t)p.M * lstride;
-  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);
-  const int xs_stride = p.K + 8;
-  if (WT == W_INT8) {
-    stage_limbs<XMODE>(p, gr.kbs0 * 64, gr.kbs0 * 64 + kslice, xh, xl, lstride, scratch);
-  } else if (XMODE == XNORM) {
-    stage_bf16_norm(p, xs, xs_stride, scratch);
-  }
-  float inv0 = 0.f, inv1 = 0.f;                 // value of one fixed-point unit for rows g and g+8
-  if (WT == W_INT8) {
-    inv0 = g < p.M ? scratch[288 + g] : 0.f;
-    inv1 = g + 8 < p.M ? scratch[288 + g + 8] : 0.f;
-  }
-
-  if (stamp) p.dbg[cta * 8 + 2] = globaltimer_ns();
-  if (lane == 0)                                // top the ring up if the static unit was a short one
-    for (int s = issue.idx; s < stages; ++s) issue.next(p, gr, ticket, queue, ring_u32, bar0, stages);
   unsigned cidx = 0;                            // chunks consumed by this warp so far
   bool alive = true;
-  int pend_nt = -1, tk_nt = -1;                 // split-k: partial written / arrival in flight
-  unsigned tk_val = 0;
-  while (true) {
-    int ul = 0;
+  float* scratch = reinterpret_cast<float*>(smem + x_bytes - 2048);
+  int cur_op = -1;
+  float inv0 = 0.f, inv1 = 0.f;                 // value of one fixed-point unit for rows g and g+8
+  int lstride = 0;
+  int8_t* xh = reinterpret_cast<int8_t*>(smem);
+  uint8_t* xl = smem;
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);
+
+  for (int cseq = 0;; ++cseq) {
+    // ---- next unit of this CTA
+    if (tid == 0) sch.fill(c, cta, ncta, cq, cq_wr, cseq + kLook);
+    int e = 0;
     if (lane == 0) {
-      if (issue.rd == issue.wr) issue.fetch(p, gr, ticket, queue);   // queue drained by empty units
-      ul = queue[issue.rd++ % kQueue];
-    }
-    ul = __shfl_sync(0xffffffffu, ul, 0);
-    if (ul < 0) break;
-    const Unit un = unit_of(p, gr, ul);
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    int ah[4] = {0, 0, 0, 0}, al[4] = {0, 0, 0, 0};
-    for (int tile0 = 0; tile0 < un.nkb; tile0 += p.tps) {
-      const int ntile = min(p.tps, un.nkb - tile0);
-      const unsigned st = cidx % (unsigned)stages;
-      if (alive) alive = mbar_wait(bar0 + st * 8, (cidx / (unsigned)stages) & 1u, 2000000000ull, p.status);
-      if (stamp && cidx == 0) p.dbg[cta * 8 + 3] = globaltimer_ns();
-      const uint8_t* sbuf = ring + (size_t)st * stage_bytes + lane * 16;
-#pragma unroll 4
-      for (int u = 0; u < kMaxTilesPerStage; ++u) {
-        if (u >= ntile) break;
-        const uint4 wv = *reinterpret_cast<const uint4*>(sbuf + u * 512);
-        const int kb = un.kb0 + tile0 + u;
-        if (WT == W_INT8) {
-          const size_t xo = (size_t)(kb - gr.kbs0) * 64 + t * 16;
-          const uint4 z = make_uint4(0, 0, 0, 0);
-          const uint4 h0 = g < p.M ? *reinterpret_cast<const uint4*>(xh + (size_t)g * lstride + xo) : z;
-          const uint4 l0 = g < p.M ? *reinterpret_cast<const uint4*>(xl + (size_t)g * lstride + xo) : z;
-          const uint4 h1 = (hi && g + 8 < p.M) ? *reinterpret_cast<const uint4*>(xh + (size_t)(g + 8) * lstride + xo) : z;
-          const uint4 l1 = (hi && g + 8 < p.M) ? *reinterpret_cast<const uint4*>(xl + (size_t)(g + 8) * lstride + xo) : z;
-          imma_s8s8(ah, h0.x, h1.x, h0.y, h1.y, wv.x, wv.y);
-          imma_s8s8(ah, h0.z, h1.z, h0.w, h1.w, wv.z, wv.w);
-          imma_u8s8(al, l0.x, l1.x, l0.y, l1.y, wv.x, wv.y);
-          imma_u8s8(al, l0.z, l1.z, l0.w, l1.w, wv.z, wv.w);
-        } else {
-          const int k0 = kb * 32 + t * 8;
-          uint4 xv, yv;
-          if (XMODE == XNORM) {
-            xv = *reinterpret_cast<const uint4*>(xs + (size_t)g * xs_stride + k0);
-            yv = hi ? *reinterpret_cast<const uint4*>(xs + (size_t)(g + 8) * xs_stride + k0) : make_uint4(0, 0, 0, 0);
-          } else {
-            xv = (g < p.M) ? ldg_cached16(p.x + (size_t)g * p.ldx + k0) : make_uint4(0, 0, 0, 0);
-            yv = (g + 8 < p.M) ? ldg_cached16(p.x + (size_t)(g + 8) * p.ldx + k0) : make_uint4(0, 0, 0, 0);
-          }
-          mma_bf16_16816(acc, xv.x, yv.x, xv.y, yv.y, wv.x, wv.y);
-          mma_bf16_16816(acc, xv.z, yv.z, xv.w, yv.w, wv.z, wv.w);
+      const unsigned long long t0 = globaltimer_ns();
+      unsigned spins = 0;
+      while (*cq_wr <= cseq) {                   // only until the scheduler thread has published it
+        if ((++spins & 1023u) == 0u && globaltimer_ns() - t0 > 2000000000ull) {
+          if (p0.status != nullptr) atomicOr(p0.status, kStatusPeerTimeout);
+          break;
         }
       }
-      __syncwarp();                              // every lane is done with the stage before it is refilled
-      ++cidx;
-      if (lane == 0) issue.next(p, gr, ticket, queue, ring_u32, bar0, stages);
+      e = *cq_wr <= cseq ? TI_UNIT_END : cq[cseq % kCQ];
     }
-    if (WT == W_INT8) {
-      acc[0] = ((float)ah[0] * 256.f + (float)al[0]) * inv0;
-      acc[1] = ((float)ah[1] * 256.f + (float)al[1]) * inv0;
-      acc[2] = ((float)ah[2] * 256.f + (float)al[2]) * inv1;
-      acc[3] = ((float)ah[3] * 256.f + (float)al[3]) * inv1;
+    e = __shfl_sync(0xffffffffu, e, 0);
+    if (e == TI_UNIT_END) break;
+    const int op = e >> 26, unit = e & ((1 << 26) - 1);
+    const GemvParams& p = c.op[op];
+    if (op != cur_op) {
+      // ---- product boundary: everyone is done with the previous product; stage the new activations
+      if (op > 0) grid_barrier(p0.sched + 2, op * ncta, p0.status);
+      else __syncthreads();
+      cur_op = op;
+      lstride = limb_stride(p.K);
+      xl = smem + (size_t)p.M * lstride;
+      if (WT == W_INT8) stage_limbs(p, 0, p.K, xh, xl, lstride, scratch);
+      else if (p.xmode == XNORM) stage_bf16_norm(p, xs, p.K + 8, scratch);
+      if (WT == W_INT8) {
+        inv0 = g < p.M ? scratch[288 + g] : 0.f;
+        inv1 = g + 8 < p.M ? scratch[288 + g + 8] : 0.f;
+      }
+      if (stamp && op == 0) p0.dbg[cta * 8 + 2] = globaltimer_ns();
     }
-    if (p.S == 1) {
-      epilogue<EPI>(p, un.nt, g, t, acc);
-    } else {
-      // split-k: arrivals are deferred so that neither the fence nor the counter round trip stalls the
-      // stream: (a) settle the arrival issued one unit ago, (b) announce the partial written one unit
-      // ago (its store has long landed, the fence is cheap), (c) write this unit's partial
-      splitk_settle<EPI>(p, tk_nt, tk_val, g, t, lane);
-      tk_nt = splitk_announce(p, pend_nt, tk_val, lane);
-      *reinterpret_cast<float4*>(p.ws + ((size_t)un.nt * p.S + un.ks) * 128 + lane * 4) =
-          make_float4(acc[0], acc[1], acc[2], acc[3]);
-      pend_nt = un.nt;
+    if (lane == 0)                                // keep the ring full (it may have been starved of queue entries)
+      for (int s = cur.idx - (int)cidx; s < stages; ++s) cur.next(c, warp, cq, cq_wr, ring_u32, bar0, stages, tps);
+
+    const bool hi = p.M > 8;
+    const int kb_lo = (warp * p.KB) / kWarps, kb_hi = ((warp + 1) * p.KB) / kWarps;
+    const int nkb = kb_hi - kb_lo;
+    const int rn = min(p.R, p.n_tiles - unit * p.R);
+    float* mypart = part + ((size_t)(cseq & 1) * kWarps + warp) * kMaxR * 128 + lane * 4;
+    for (int r = 0; r < rn; ++r) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      int ah[2][4], al[2][4];                    // two accumulator sets: consecutive tiles do not chain
+#pragma unroll
+      for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) ah[a][b] = al[a][b] = 0;
+      for (int tile0 = 0; tile0 < nkb; tile0 += tps) {
+        const int ntile = min(tps, nkb - tile0);
+        const unsigned st = cidx % (unsigned)stages;
+        if (alive) alive = mbar_wait(bar0 + st * 8, (cidx / (unsigned)stages) & 1u, 2000000000ull, p.status);
+        if (stamp && cidx == 0) p0.dbg[cta * 8 + 3] = globaltimer_ns();
+        const uint8_t* sbuf = ring + (size_t)st * stage_bytes + lane * 16;
+#pragma unroll
+        for (int u = 0; u < kMaxTilesPerStage; ++u) {
+          if (u >= ntile) break;
+          const uint4 wv = *reinterpret_cast<const uint4*>(sbuf + u * 512);
+          const int kb = kb_lo + tile0 + u;
+          if (WT == W_INT8) {
+            const size_t xo = (size_t)kb * 64 + t * 16;
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            const uint4 h0 = g < p.M ? *reinterpret_cast<const uint4*>(xh + (size_t)g * lstride + xo) : z;
+            const uint4 l0 = g < p.M ? *reinterpret_cast<const uint4*>(xl + (size_t)g * lstride + xo) : z;
+            const uint4 h1 = (hi && g + 8 < p.M) ? *reinterpret_cast<const uint4*>(xh + (size_t)(g + 8) * lstride + xo) : z;
+            const uint4 l1 = (hi && g + 8 < p.M) ? *reinterpret_cast<const uint4*>(xl + (size_t)(g + 8) * lstride + xo) : z;
+            imma_s8s8(ah[u & 1], h0.x, h1.x, h0.y, h1.y, wv.x, wv.y);
+            imma_u8s8(al[u & 1], l0.x, l1.x, l0.y, l1.y, wv.x, wv.y);
+            imma_s8s8(ah[u & 1], h0.z, h1.z, h0.w, h1.w, wv.z, wv.w);
+            imma_u8s8(al[u & 1], l0.z, l1.z, l0.w, l1.w, wv.z, wv.w);
+          } else {
+            const int k0 = kb * 32 + t * 8;
+            uint4 xv, yv;
+            if (p.xmode == XNORM) {
+              xv = *reinterpret_cast<const uint4*>(xs + (size_t)g * (p.K + 8) + k0);
+              yv = hi ? *reinterpret_cast<const uint4*>(xs + (size_t)(g + 8) * (p.K + 8) + k0) : make_uint4(0, 0, 0, 0);
+            } else {
+              xv = (g < p.M) ? ld_x16(p.x + (size_t)g * p.ldx + k0) : make_uint4(0, 0, 0, 0);
+              yv = (g + 8 < p.M) ? ld_x16(p.x + (size_t)(g + 8) * p.ldx + k0) : make_uint4(0, 0, 0, 0);
+            }
+            mma_bf16_16816(acc, xv.x, yv.x, xv.y, yv.y, wv.x, wv.y);
+            mma_bf16_16816(acc, xv.z, yv.z, xv.w, yv.w, wv.z, wv.w);
+          }
+        }
+        __syncwarp();                            // every lane is done with the stage before it is refilled
+        ++cidx;
+        if (lane == 0) cur.next(c, warp, cq, cq_wr, ring_u32, bar0, stages, tps);
+      }
+      if (WT == W_INT8) {
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          acc[b] = ((float)(ah[0][b] + ah[1][b]) * 256.f + (float)(al[0][b] + al[1][b])) * (b < 2 ? inv0 : inv1);
+      }
+      *reinterpret_cast<float4*>(mypart + r * 128) = make_float4(acc[0], acc[1], acc[2], acc[3]);
     }
-    if (stamp) p.dbg[cta * 8 + 4] = globaltimer_ns();
+    __syncthreads();                             // the k slices of all 16 warps are in shared memory
+    if (warp == (cseq & (kWarps - 1))) {         // one warp (rotating) reduces in a fixed order and finishes the rows
+      const float* pb = part + (size_t)(cseq & 1) * kWarps * kMaxR * 128 + lane * 4;
+      for (int r = 0; r < rn; ++r) {
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          const float4 v = *reinterpret_cast<const float4*>(pb + ((size_t)w * kMaxR + r) * 128);
+          sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
+        }
+        epilogue(p, unit * p.R + r, g, t, sum);
+      }
+    }
+    if (stamp) p0.dbg[cta * 8 + 4] = globaltimer_ns();
   }
-  if (p.S > 1) {                                 // drain the deferred arrivals
-    splitk_settle<EPI>(p, tk_nt, tk_val, g, t, lane);
-    tk_nt = splitk_announce(p, pend_nt, tk_val, lane);
-    splitk_settle<EPI>(p, tk_nt, tk_val, g, t, lane);
-  }
-  if (stamp) p.dbg[cta * 8 + 5] = globaltimer_ns();
-  // the last CTA to finish advances the launch sequence number (monotonic, never reset)
+  if (stamp) p0.dbg[cta * 8 + 5] = globaltimer_ns();
+  // the last CTA of the launch resets the tickets and the barrier counter for the next launch
   __syncthreads();
   if (tid == 0) {
     __threadfence();
-    const int fin = atomicAdd(p.sched + 1, 1);
-    if ((fin + 1) % ncta == 0) atomicAdd(p.sched, 1);
+    const int fin = atomicAdd(p0.sched + 1, 1);
+    if ((fin + 1) % ncta == 0) {
+      for (int i = 0; i < kMaxChain * 16; ++i) p0.sched[8 + i] = 0;
+      p0.sched[2] = 0;
+      __threadfence();
+    }
   }
 }
 
-template <int WT, int XMODE, int EPI>
-__global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const __grid_constant__ GemvParams p) {
+template <int WT>
+__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant__ ChainParams c) {
   extern __shared__ __align__(128) uint8_t smem[];
-  gemv_body<WT, XMODE, EPI>(p, blockIdx.x, gridDim.x, smem);
+  gemv_body<WT>(c, blockIdx.x, gridDim.x, smem);
 }
 
 // All emulated ranks of a tensor-parallel group in ONE cooperative launch on one GPU: block b
 // works for rank b / ctas_per_rank.  Used by tests where fewer GPUs than ranks are available;
 // separate launches that wait on one another must never share a GPU.
-template <int WT, int XMODE, int EPI>
-__global__ void __launch_bounds__(kThreads, 2) gemv_kernel_ranks(const GemvParams* plist, int ctas_per_rank) {
+template <int WT>
+__global__ void __launch_bounds__(kThreads, 1) gemv_kernel_ranks(const ChainParams* clist, int ctas_per_rank) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int r = blockIdx.x / ctas_per_rank;
-  gemv_body<WT, XMODE, EPI>(plist[r], blockIdx.x - r * ctas_per_rank, ctas_per_rank, smem);
+  gemv_body<WT>(clist[r], blockIdx.x - r * ctas_per_rank, ctas_per_rank, smem);
 }
 
-static size_t smem_bytes(const GemvParams& p, int wt, int xmode) {
+static int op_x_bytes(const GemvParams& p, int wt) { return (int)x_smem_bytes_impl(wt, p.xmode, p.M, p.K, p.K); }
+
+static size_t smem_bytes(const ChainParams& c) {
+  const GemvParams& p = c.op[0];
+  return (size_t)c.x_bytes + 2 * kWarps * kMaxR * 512 + (size_t)kWarps * p.stages * (p.tps * 512 + 8) + (kCQ + 4) * 4;
+}
+
+static int check(const GemvParams& p, int wt) {
   const int tk = wt == W_INT8 ? 64 : 32;
-  const int kslice = std::min(p.KB, (p.S / p.J) * p.kb_per_split) * tk;
-  return x_smem_bytes_impl(wt, xmode, p.M, p.K, kslice) + (size_t)(kThreads / 32) * (p.stages * (p.tps * 512 + 8) + kQueue * 4);
+  if (p.M < 1 || p.M > 16 || p.N < 2 || (p.N & 1) || p.K % tk || p.KB * tk != p.K) return -2;
+  if (p.R < 1 || p.R > kMaxR || p.n_tiles < 1 || p.n_tiles >= (1 << 26)) return -3;
+  if (p.tps != 4 && p.tps != 8 && p.tps != 16) return -7;
+  if (p.sched == nullptr || p.stages < 1 || p.stages > 8) return -7;
+  if (p.xmode < 0 || p.xmode > 1 || p.epi < 0 || p.epi > 3) return -8;
+  if (p.K % 8 || p.ldx % 8) return -4;
+  if (p.tp > kMaxRanks || (p.tp > 1 && p.M > p.m_cap)) return -5;
+  return 0;
 }
 
-template <int WT, int XMODE, int EPI>
-static int launch(const GemvParams& p, int ncta, cudaStream_t st, const GemvParams* dev_list, int nranks) {
-  const size_t sm = smem_bytes(p, WT, XMODE);
+static int prepare(ChainParams& c, int wt) {
+  if (c.n_ops < 1 || c.n_ops > kMaxChain) return -9;
+  int xb = 0;
+  for (int i = 0; i < c.n_ops; ++i) {
+    const int rc = check(c.op[i], wt);
+    if (rc) return rc;
+    if (c.op[i].sched != c.op[0].sched || c.op[i].stages != c.op[0].stages || c.op[i].tps != c.op[0].tps) return -9;
+    xb = std::max(xb, op_x_bytes(c.op[i], wt));
+  }
+  c.x_bytes = xb;
+  if (smem_bytes(c) > 227 * 1024) return -4;
+  return 0;
+}
+
+template <int WT>
+static int launch(const ChainParams& c, int ncta, cudaStream_t st, const ChainParams* dev_list, int nranks) {
+  const size_t sm = smem_bytes(c);
+  static bool configured = false, configured_ranks = false;
   if (dev_list == nullptr) {
-    auto k = gemv_kernel<WT, XMODE, EPI>;
-    static size_t configured = 0;
-    if (sm > configured) {
+    auto k = gemv_kernel<WT>;
+    if (!configured) {
       cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-      configured = 227 * 1024;
+      configured = true;
     }
-    cudaError_t e = launch_kernel(k, dim3(ncta), dim3(kThreads), sm, st, true, p);
+    cudaError_t e = launch_kernel(k, dim3(ncta), dim3(kThreads), sm, st, true, c);
     if (e != cudaSuccess) return (int)e;
   } else {
-    auto k = gemv_kernel_ranks<WT, XMODE, EPI>;
-    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    auto k = gemv_kernel_ranks<WT>;
+    if (!configured_ranks) {
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      configured_ranks = true;
+    }
     void* args[] = {(void*)&dev_list, (void*)&ncta};
     cudaError_t e = cudaLaunchCooperativeKernel((void*)k, dim3(ncta * nranks), dim3(kThreads), args, sm, st);
     if (e != cudaSuccess) return (int)e;
@@ -696,59 +792,31 @@ static int launch(const GemvParams& p, int ncta, cudaStream_t st, const GemvPara
   return (int)cudaGetLastError();
 }
 
-template <int WT, int XMODE>
-static int dispatch_epi(const GemvParams& p, int epi, int ncta, cudaStream_t st, const GemvParams* dl, int nr) {
-  switch (epi) {
-    case EPI_STORE: return launch<WT, XMODE, EPI_STORE>(p, ncta, st, dl, nr);
-    case EPI_SWIGLU: return launch<WT, XMODE, EPI_SWIGLU>(p, ncta, st, dl, nr);
-    case EPI_ROWPAR: return launch<WT, XMODE, EPI_ROWPAR>(p, ncta, st, dl, nr);
-    case EPI_F32: return launch<WT, XMODE, EPI_F32>(p, ncta, st, dl, nr);
-  }
-  return -1;
-}
-
-static int check(const GemvParams& p, int wt, int xmode, int ncta) {
-  const int tk = wt == W_INT8 ? 64 : 32;
-  if (p.M < 1 || p.M > 16 || p.N < 2 || (p.N & 1) || p.K % tk || p.KB * tk != p.K) return -2;
-  if (p.S < 1 || p.kb_per_split < 1 || (long long)p.S * p.kb_per_split < p.KB) return -3;
-  if (p.J < 1 || p.S % p.J || p.J > ncta || (wt != W_INT8 && p.J != 1)) return -6;
-  if (p.tps != 4 && p.tps != 8 && p.tps != 16) return -7;
-  if (p.sched == nullptr || p.J > 16) return -7;
-  if (p.stages < 1 || p.stages > 8 || smem_bytes(p, wt, xmode) > 227 * 1024) return -4;
-  if (p.K % 8 || p.ldx % 8) return -4;
-  if (p.tp > kMaxRanks || (p.tp > 1 && p.M > p.m_cap)) return -5;
-  return 0;
-}
-
 }  // namespace ti
 
 extern "C" {
 
-// Launches y = x W^T with the selected weight type, x source and epilogue on `stream`.
-// Returns 0 or a CUDA / argument error code.
-int ti_gemv(const ti::GemvParams* p, int wt, int xmode, int epi, int ncta, void* stream) {
-  int rc = ti::check(*p, wt, xmode, ncta);
-  if (rc) return rc;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (wt == ti::W_INT8)
-    return xmode == ti::XNORM ? ti::dispatch_epi<ti::W_INT8, ti::XNORM>(*p, epi, ncta, st, nullptr, 1)
-                              : ti::dispatch_epi<ti::W_INT8, ti::XGLOBAL>(*p, epi, ncta, st, nullptr, 1);
-  return xmode == ti::XNORM ? ti::dispatch_epi<ti::W_BF16, ti::XNORM>(*p, epi, ncta, st, nullptr, 1)
-                            : ti::dispatch_epi<ti::W_BF16, ti::XGLOBAL>(*p, epi, ncta, st, nullptr, 1);
-}
-
-// One cooperative launch that runs `nranks` emulated ranks (parameter blocks in device memory at
-// `dev_params`, a host copy of rank 0's block in `p0` for validation) with `ncta` blocks each.
-int ti_gemv_ranks(const ti::GemvParams* p0, const ti::GemvParams* dev_params, int nranks, int wt, int xmode, int epi,
-                  int ncta, void* stream) {
-  int rc = ti::check(*p0, wt, xmode, ncta);
-  if (rc) return rc;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (wt != ti::W_INT8) return -6;
-  return xmode == ti::XNORM ? ti::dispatch_epi<ti::W_INT8, ti::XNORM>(*p0, epi, ncta, st, dev_params, nranks)
-                            : ti::dispatch_epi<ti::W_INT8, ti::XGLOBAL>(*p0, epi, ncta, st, dev_params, nranks);
-}
-
 int ti_gemv_params_size() { return (int)sizeof(ti::GemvParams); }
+int ti_chain_params_size() { return (int)sizeof(ti::ChainParams); }
+
+// Runs c->n_ops dependent products (y_i = x_i W_i^T with their prologues / epilogues) in one launch.
+// `c` is modified (x_bytes is filled in).  Returns 0 or a CUDA / argument error code.
+int ti_gemv_chain(ti::ChainParams* c, int wt, int ncta, void* stream) {
+  const int rc = ti::prepare(*c, wt);
+  if (rc) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return wt == ti::W_INT8 ? ti::launch<ti::W_INT8>(*c, ncta, st, nullptr, 1) : ti::launch<ti::W_BF16>(*c, ncta, st, nullptr, 1);
+}
+
+// Size `c` exactly as ti_gemv_chain would (validation + x_bytes) without launching.
+int ti_gemv_chain_prepare(ti::ChainParams* c, int wt, int ncta) { return ti::prepare(*c, wt); }
+
+// One cooperative launch that runs `nranks` emulated ranks (prepared chain blocks in device memory at
+// `dev_chains`, a host copy of rank 0's block in `c0`) with `ncta` blocks each.  int8 weights only.
+int ti_gemv_ranks(ti::ChainParams* c0, const ti::ChainParams* dev_chains, int nranks, int ncta, void* stream) {
+  const int rc = ti::prepare(*c0, ti::W_INT8);
+  if (rc) return rc;
+  return ti::launch<ti::W_INT8>(*c0, ncta, static_cast<cudaStream_t>(stream), dev_chains, nranks);
+}
 
 }  // extern "C"

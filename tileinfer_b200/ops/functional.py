@@ -12,7 +12,7 @@ import os
 import torch
 
 from . import lib as _l
-from .lib import GemvParams, MAX_RANKS, check, ptr, stream
+from .lib import ChainParams, GemvParams, MAX_CHAIN, MAX_RANKS, check, ptr, stream
 
 _I, _P, _F = ctypes.c_int, ctypes.c_void_p, ctypes.c_float
 
@@ -20,8 +20,8 @@ XGLOBAL, XNORM = 0, 1
 EPI_STORE, EPI_SWIGLU, EPI_ROWPAR, EPI_F32 = 0, 1, 2, 3
 W_INT8, W_BF16 = 0, 1
 NUM_SMS = 148
-GEMV_WARPS = 8
-GEMV_TPS = int(os.environ.get("TI_GEMV_TPS", "4"))            # 512-byte tiles per ring stage
+GEMV_WARPS = 16
+GEMV_TPS = int(os.environ.get("TI_GEMV_TPS", "8"))            # 512-byte tiles per ring stage
 GEMV_MAX_STAGES = int(os.environ.get("TI_GEMV_STAGES", "6"))
 GEMV_UNITS_PER_WARP = int(os.environ.get("TI_GEMV_UPW", "4"))
 
@@ -138,29 +138,33 @@ def x_smem_bytes(wt: int, xmode: int, M: int, K: int, kslice: int) -> int:
     return (b + 2048 + 127) // 128 * 128
 
 
-def plan_gemv(wt: int, xmode: int, M: int, n_tiles: int, KB: int, ncta: int = NUM_SMS, x_budget: int = 120 * 1024):
-    """(S, kb_per_split, J, stages).  About four (row-tile, k-range) units per warp, k-ranges in whole
-    2 KB ring stages; J CTA groups so that the int8 limb planes of one k-slice fit in `x_budget` bytes;
-    the ring takes what is left of the 227 KB."""
+PART_BYTES = 2 * GEMV_WARPS * 2 * 512          # per-warp partial sums, two buffers, up to two row tiles
+_RING_CHOICES = ((8, 3), (8, 2), (4, 3), (4, 2), (4, 1))
+
+
+def plan_gemv(wt: int, xmode: int, M: int, n_tiles: int, KB: int, ncta: int = NUM_SMS):
+    """(R, tps, stages) or None when M rows of this K do not fit in shared memory.
+    R: row tiles per unit; (tps, stages): geometry of the per-warp weight ring that fits beside the staged
+    activations and the partial-sum buffers in 227 KB."""
     tk = 64 if wt == W_INT8 else 32
-    warps = ncta * GEMV_WARPS
-    S = max(1, min(math.ceil(GEMV_UNITS_PER_WARP * warps / n_tiles), KB // 4 if KB >= 4 else 1))
-    J = 1
-    if wt == W_INT8:
-        J = max(1, math.ceil(2 * M * (KB * tk + 64) / x_budget))
-        S = math.ceil(S / J) * J
-    tps = GEMV_TPS
-    kbps = -(-math.ceil(KB / S) // tps) * tps
-    if J == 1:
-        S = math.ceil(KB / kbps)
-    kslice = min(KB, (S // J) * kbps) * tk
-    xb = x_smem_bytes(wt, xmode, M, KB * tk, kslice)
-    per_stage = GEMV_WARPS * (tps * 512 + 8)
-    # two CTAs per SM (this kernel's and the next kernel's, which prefetches under programmatic
-    # dependent launch) when the activations are small; the whole SM otherwise
-    budget = 113 * 1024 if xb <= 48 * 1024 else 227 * 1024
-    stages = int(max(1, min(GEMV_MAX_STAGES, (budget - xb - GEMV_WARPS * 64) // per_stage)))
-    return S, kbps, J, stages
+    xb = x_smem_bytes(wt, xmode, M, KB * tk, KB * tk)
+    R = 2 if n_tiles >= 8 * ncta else 1
+    forced = os.environ.get("TI_GEMV_TPS")
+    for tps, stages in _RING_CHOICES:
+        if forced and int(forced) != tps:
+            continue
+        if xb + PART_BYTES + GEMV_WARPS * stages * (tps * 512 + 8) + 256 <= 227 * 1024:
+            return R, tps, stages
+    return None
+
+
+def max_rows(wt: int, xmode: int, K: int) -> int:
+    """Largest row count (<= 16) one launch can take for this K."""
+    tk = 64 if wt == W_INT8 else 32
+    for m in (16, 12, 8, 6, 4, 3, 2, 1):
+        if plan_gemv(wt, xmode, m, 1024, K // tk) is not None:
+            return m
+    raise ValueError(f"K={K} does not fit in shared memory even for one row")
 
 
 _STATUS = None
@@ -180,7 +184,7 @@ class GemvWorkspace:
     def __init__(self, device="cuda", max_units: int = 1 << 16, max_tiles: int = 1 << 16):
         self.ws = torch.empty(max_units * 128, dtype=torch.float32, device=device)
         self.counters = torch.zeros(max_tiles, dtype=torch.int32, device=device)
-        self.sched = torch.zeros(64, dtype=torch.int32, device=device)     # dynamic unit scheduling state
+        self.sched = torch.zeros(128, dtype=torch.int32, device=device)     # dynamic unit scheduling state
         self.max_units, self.max_tiles = max_units, max_tiles
 
 
@@ -199,17 +203,18 @@ def make_gemv_params(W: LinearW, x, out, M, *, xmode=XGLOBAL, epi=EPI_STORE, nor
     p = GemvParams()
     p.w, p.scale, p.x, p.norm_w = ptr(W.tiles), ptr(W.scale), ptr(x), ptr(norm_w)
     p.out, p.resid = ptr(out), ptr(resid)
-    S, kbps, J, stages = plan_gemv(W.wt, xmode, M, W.n_tiles, W.KB, ncta)
+    plan = plan_gemv(W.wt, xmode, M, W.n_tiles, W.KB, ncta)
+    if plan is None:
+        raise ValueError(f"{M} rows of K={W.K} do not fit in shared memory; split the rows (max_rows)")
+    R, tps, stages = plan
     if ws is None:
         ws = default_workspace()
-    if S > 1:
-        assert W.n_tiles * S <= ws.max_units and W.n_tiles <= ws.max_tiles
-        p.ws, p.counters = ptr(ws.ws), ptr(ws.counters)
-    p.M, p.N, p.n_tiles, p.K, p.KB, p.S, p.kb_per_split = M, W.N, W.n_tiles, W.K, W.KB, S, kbps
+    p.M, p.N, p.n_tiles, p.K, p.KB, p.S, p.kb_per_split = M, W.N, W.n_tiles, W.K, W.KB, 1, W.KB
     p.ldx = ldx if ldx is not None else (x.stride(0) if x.dim() > 1 else W.K)
     p.ldo = ldo if ldo is not None else (out.stride(0) if out.dim() > 1 else W.N)
     p.eps = eps
-    p.stages, p.J, p.tps = stages, J, GEMV_TPS
+    p.stages, p.J, p.tps, p.R = stages, 1, tps, R
+    p.xmode, p.epi = xmode, epi
     if ws is None:
         ws = default_workspace()
     p.sched = ptr(ws.sched)
@@ -223,20 +228,43 @@ def make_gemv_params(W: LinearW, x, out, M, *, xmode=XGLOBAL, epi=EPI_STORE, nor
     return p
 
 
-def gemv_launch(p: GemvParams, wt: int, xmode: int, epi: int, ncta: int = NUM_SMS):
-    check(L().ti_gemv(ctypes.byref(p), wt, xmode, epi, ncta, stream()), "ti_gemv")
+def make_chain(params: list) -> ChainParams:
+    """Up to MAX_CHAIN dependent products for one launch; the ring depth is the smallest of the ops'."""
+    assert 1 <= len(params) <= MAX_CHAIN
+    c = ChainParams()
+    c.n_ops = len(params)
+    # one ring geometry per launch: the one of the op that has the least room
+    tps, stages = min((p.tps * p.stages, p.tps, p.stages) for p in params)[1:]
+    for i, p in enumerate(params):
+        p.tps, p.stages = tps, stages
+        c.op[i] = p
+    return c
+
+
+def gemv_chain_launch(params: list, wt: int, ncta: int = NUM_SMS):
+    c = make_chain(params)
+    check(L().ti_gemv_chain(ctypes.byref(c), wt, ncta, stream()), "ti_gemv_chain")
+
+
+def gemv_launch(p: GemvParams, wt: int, xmode: int = None, epi: int = None, ncta: int = NUM_SMS):
+    if xmode is not None:
+        p.xmode = xmode
+    if epi is not None:
+        p.epi = epi
+    gemv_chain_launch([p], wt, ncta)
 
 
 def gemv(W: LinearW, x: torch.Tensor, *, out=None, xmode=XGLOBAL, epi=EPI_STORE, norm_w=None, resid=None, ws=None,
          eps=1e-6, comm=None, order=0) -> torch.Tensor:
-    """Convenience form (allocates `out`); loops over chunks of 16 rows."""
+    """Convenience form (allocates `out`); loops over row chunks that fit in shared memory."""
     M = x.shape[0]
+    step = max_rows(W.wt, xmode, W.K)
     if out is None:
         cols = W.N // 2 if epi == EPI_SWIGLU else W.N
         dt = torch.float32 if epi == EPI_F32 else torch.bfloat16
         out = torch.empty(M, cols, dtype=dt, device=x.device)
-    for m0 in range(0, M, 16):
-        m = min(16, M - m0)
+    for m0 in range(0, M, step):
+        m = min(step, M - m0)
         p = make_gemv_params(W, x[m0:m0 + m], out[m0:m0 + m], m, xmode=xmode, epi=epi, norm_w=norm_w,
                              resid=None if resid is None else resid[m0:m0 + m], ws=ws, eps=eps,
                              ldx=x.stride(0), ldo=out.stride(0), comm=comm, order=order)

@@ -26,8 +26,15 @@ class GemvParams(ctypes.Structure):
         ("KB", ctypes.c_int), ("S", ctypes.c_int), ("kb_per_split", ctypes.c_int),
         ("ldx", ctypes.c_int), ("ldo", ctypes.c_int),
         ("tp", ctypes.c_int), ("rank", ctypes.c_int), ("order", ctypes.c_int), ("m_cap", ctypes.c_int),
-        ("eps", ctypes.c_float), ("stages", ctypes.c_int), ("J", ctypes.c_int), ("dbg", ctypes.c_void_p), ("sched", ctypes.c_void_p), ("tps", ctypes.c_int),
+        ("eps", ctypes.c_float), ("stages", ctypes.c_int), ("J", ctypes.c_int), ("dbg", ctypes.c_void_p), ("sched", ctypes.c_void_p), ("tps", ctypes.c_int), ("xmode", ctypes.c_int), ("epi", ctypes.c_int), ("R", ctypes.c_int),
     ]
+
+
+MAX_CHAIN = 4
+
+
+class ChainParams(ctypes.Structure):
+    _fields_ = [("n_ops", ctypes.c_int), ("x_bytes", ctypes.c_int), ("op", GemvParams * MAX_CHAIN)]
 
 
 def lib() -> ctypes.CDLL:
@@ -43,8 +50,9 @@ def lib() -> ctypes.CDLL:
                 if fn is None:
                     raise RuntimeError(f"{path} lacks symbol {name}; rebuild with python -m tileinfer_b200.ops.build --force")
                 fn.restype, fn.argtypes = getattr(_Sigs, name)
-        if _LIB.ti_gemv_params_size() != ctypes.sizeof(GemvParams):
-            raise RuntimeError("GemvParams layout mismatch between Python and CUDA")
+        if _LIB.ti_gemv_params_size() != ctypes.sizeof(GemvParams) or \
+                _LIB.ti_chain_params_size() != ctypes.sizeof(ChainParams):
+            raise RuntimeError("GemvParams / ChainParams layout mismatch between Python and CUDA")
     return _LIB
 
 
@@ -52,9 +60,11 @@ _I, _P, _F, _U64 = ctypes.c_int, ctypes.c_void_p, ctypes.c_float, ctypes.c_uint6
 
 
 class _Sigs:
-    ti_gemv = (_I, [ctypes.POINTER(GemvParams), _I, _I, _I, _I, _P])
-    ti_gemv_ranks = (_I, [ctypes.POINTER(GemvParams), _P, _I, _I, _I, _I, _I, _P])
+    ti_gemv_chain = (_I, [ctypes.POINTER(ChainParams), _I, _I, _P])
+    ti_gemv_chain_prepare = (_I, [ctypes.POINTER(ChainParams), _I, _I])
+    ti_gemv_ranks = (_I, [ctypes.POINTER(ChainParams), _P, _I, _I, _P])
     ti_gemv_params_size = (_I, [])
+    ti_chain_params_size = (_I, [])
 
 
 def register(name: str, restype, argtypes):
