@@ -56,6 +56,24 @@ def test_gemv_norm_prologue_and_swiglu(M):
     torch.testing.assert_close(act.float(), ref, rtol=3e-2, atol=0.25)
 
 
+@pytest.mark.parametrize("M", [1, 9, 12, 16])
+@pytest.mark.parametrize("K", [384, 5120])
+def test_gemv_bf16_weights_norm_prologue(M, K):
+    F = _F()
+    N = 1024
+    W = F.LinearW(_rand_w(N, K, seed=21), False)
+    h = (torch.randn(M, K, device="cuda") * 2).to(BF16)
+    nw = (torch.randn(K, device="cuda") * 0.1).to(BF16)
+    y = F.gemv(W, h, xmode=F.XNORM, epi=F.EPI_F32, norm_w=nw)
+    hf = h.float()
+    xn = (hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + nw.float())).to(BF16).float()
+    torch.testing.assert_close(y, xn @ W.dense().float().t(), rtol=1e-2, atol=2e-2)
+    x = torch.randn(M, K, device="cuda").to(BF16)
+    r = torch.randn(M, N, device="cuda").to(BF16)
+    out = F.gemv(W, x, epi=F.EPI_ROWPAR, resid=r)
+    torch.testing.assert_close(out.float(), r.float() + x.float() @ W.dense().float().t(), rtol=2e-2, atol=3e-2)
+
+
 def test_gemv_rowpar_residual_tp1_and_f32():
     F = _F()
     N, K, M = 5120, 768, 4
@@ -113,13 +131,15 @@ def test_gemv_rowpar_allreduce_emulated_ranks(tp):
     assert size * tp == dev_params.numel()
 
 
-def test_gemv_chain_of_four_matches_separate_launches():
+@pytest.mark.parametrize("quant,M,H", [(True, 3, 1024), (False, 12, 384), (True, 12, 384), (False, 1, 1024)])
+def test_gemv_chain_of_four_matches_separate_launches(quant, M, H):
     """out_proj -> gate_up(SwiGLU) -> down -> in_proj in ONE launch (grid barriers in between) must equal the
     same four products launched one by one."""
     F = _F()
-    H, I, KO, NI, M = 1024, 2048, 768, 1536, 3
-    Wo, Wgu = F.LinearW(_rand_w(H, KO, 11), True), F.LinearW(_rand_w(2 * I, H, 12), True)
-    Wd, Wi = F.LinearW(_rand_w(H, I, 13), True), F.LinearW(_rand_w(NI, H, 14), True)
+    I, KO, NI = 2048, 768, 1536
+    wt = F.W_INT8 if quant else F.W_BF16
+    Wo, Wgu = F.LinearW(_rand_w(H, KO, 11), quant), F.LinearW(_rand_w(2 * I, H, 12), quant)
+    Wd, Wi = F.LinearW(_rand_w(H, I, 13), quant), F.LinearW(_rand_w(NI, H, 14), quant)
     x = torch.randn(M, KO, device="cuda").to(BF16)
     h0 = torch.randn(M, H, device="cuda").to(BF16)
     n1 = (torch.randn(H, device="cuda") * 0.1).to(BF16)
@@ -135,16 +155,16 @@ def test_gemv_chain_of_four_matches_separate_launches():
               F.make_gemv_params(Wd, act, h2, M, xmode=F.XGLOBAL, epi=F.EPI_ROWPAR, resid=h1, ws=ws),
               F.make_gemv_params(Wi, h2, proj, M, xmode=F.XNORM, epi=F.EPI_STORE, norm_w=n2, ws=ws)]
         if chained:
-            F.gemv_chain_launch(ps, F.W_INT8)
+            F.gemv_chain_launch(ps, wt)
         else:
             for p in ps:
-                F.gemv_launch(p, F.W_INT8)
+                F.gemv_launch(p, wt)
         torch.cuda.synchronize()
         assert int(ws.sched[2]) == 0 and int(ws.sched[8:72].abs().sum()) == 0 and int(ws.counters.abs().sum()) == 0
         return h1, act, h2, proj
     a, b = run(False), run(True)
-    for u, v in zip(a, b):
-        assert torch.equal(u, v)
+    for name, u, v in zip(("h1", "act", "h2", "proj"), a, b):
+        assert torch.equal(u, v), f"{name}: max diff {(u.float() - v.float()).abs().max().item()}"
     ref_h1 = h0.float() + x.float() @ Wo.dense().float().t()
     torch.testing.assert_close(a[0].float(), ref_h1, rtol=2e-2, atol=3e-2)
     for _ in range(3):                      # replays keep working (tickets and barrier counter reset themselves)

@@ -403,6 +403,10 @@ TI_DEVICE void stage_bf16_norm(const GemvParams& p, __nv_bfloat16* xs, int xs_st
 TI_DEVICE int num_units(const GemvParams& p) { return (p.n_tiles + p.R - 1) / p.R; }
 #define TI_UNIT_END (-1)
 TI_DEVICE int pack_unit(int op, int unit) { return (op << 26) | unit; }
+constexpr int kUnitMask = (1 << 26) - 1;
+// queue entry that opens product `op`: every CTA sees it (and takes part in the grid barrier and the
+// activation staging of that product) whether or not it gets any unit of the product
+TI_DEVICE int pack_begin(int op) { return (op << 26) | kUnitMask; }
 
 // Units k*ncta + cta for k < num_static are assigned statically (no atomics: they can be queued before the
 // kernel may look at mutable state and they fill the look-ahead at once); the second half of a product's
@@ -411,7 +415,7 @@ TI_DEVICE int num_static(const GemvParams& p, int ncta) { return max(1, num_unit
 
 struct Scheduler {            // registers of warp 0 / lane 0; queue storage in shared memory
   int op, pre, sk;
-  bool pre_valid, done, can_ticket;
+  bool pre_valid, done, can_ticket, opened;
   TI_DEVICE void push(volatile int* cq, volatile int* wr, int e) {
     const int w = *wr;
     cq[w % kCQ] = e;
@@ -422,6 +426,11 @@ struct Scheduler {            // registers of warp 0 / lane 0; queue storage in 
     while (!done && *wr < upto) {
       const GemvParams& p = c.op[op];
       const int U = num_units(p), ns = num_static(p, ncta);
+      if (!opened) {
+        opened = true;
+        push(cq, wr, pack_begin(op));
+        continue;
+      }
       if (sk < ns) {
         const int u = sk * ncta + cta;
         ++sk;
@@ -437,7 +446,7 @@ struct Scheduler {            // registers of warp 0 / lane 0; queue storage in 
       const int u = ns * ncta + pre;
       if (u >= U) {
         sk = 0;
-        pre_valid = false;
+        pre_valid = opened = false;
         if (++op >= c.n_ops) {
           push(cq, wr, TI_UNIT_END);
           done = true;
@@ -470,10 +479,10 @@ struct WarpCursor {           // registers of lane 0 of each warp
         return false;
       }
       const GemvParams& p = c.op[e >> 26];
-      const int unit = e & ((1 << 26) - 1);
+      const int unit = e & kUnitMask;
       const int kb_lo = (warp * p.KB) / kWarps, kb_hi = ((warp + 1) * p.KB) / kWarps;
       nkb = kb_hi - kb_lo;
-      if (nkb <= 0) {                      // fewer k tiles than warps: nothing to stream for this unit
+      if (unit == kUnitMask || nkb <= 0) { // a product marker, or fewer k tiles than warps: nothing to stream
         ++seq;
         continue;
       }
@@ -555,7 +564,7 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
 
   Scheduler sch;
   sch.op = sch.pre = sch.sk = 0;
-  sch.pre_valid = sch.done = sch.can_ticket = false;
+  sch.pre_valid = sch.done = sch.can_ticket = sch.opened = false;
   if (tid == 0) {
     *cq_wr = 0;
     sch.fill(c, cta, ncta, cq, cq_wr, kLook);      // static units of the first product only (no tickets yet)
@@ -610,9 +619,9 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
     }
     e = __shfl_sync(0xffffffffu, e, 0);
     if (e == TI_UNIT_END) break;
-    const int op = e >> 26, unit = e & ((1 << 26) - 1);
+    const int op = e >> 26, unit = e & kUnitMask;
     const GemvParams& p = c.op[op];
-    if (op != cur_op) {
+    if (unit == kUnitMask) {
       // ---- product boundary: everyone is done with the previous product; stage the new activations
       if (op > 0) grid_barrier(p0.sched + 2, op * ncta, p0.status);
       else __syncthreads();
@@ -626,6 +635,7 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
         inv1 = g + 8 < p.M ? scratch[288 + g + 8] : 0.f;
       }
       if (stamp && op == 0) p0.dbg[cta * 8 + 2] = globaltimer_ns();
+      continue;
     }
     if (lane == 0)                                // keep the ring full (it may have been starved of queue entries)
       for (int s = cur.idx - (int)cidx; s < stages; ++s) cur.next(c, warp, cq, cq_wr, ring_u32, bar0, stages, tps);
