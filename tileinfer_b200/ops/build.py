@@ -20,7 +20,8 @@ LIB = os.path.join(HERE, "libtileinfer_b200.so")
 STAMP = os.path.join(BUILD, "stamp.txt")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+              "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+              "-DTI_GEMV_WARPS=" + os.environ.get("TI_GEMV_WARPS", "16")]
 
 
 def _nvcc() -> str:

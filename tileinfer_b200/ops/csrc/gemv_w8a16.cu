@@ -83,12 +83,16 @@ enum { XGLOBAL = 0, XNORM = 1 };
 enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ROWPAR = 2, EPI_F32 = 3 };
 enum { W_INT8 = 0, W_BF16 = 1 };
 
-constexpr int kThreads = 512;
+#ifndef TI_GEMV_WARPS
+#define TI_GEMV_WARPS 16
+#endif
+constexpr int kThreads = TI_GEMV_WARPS * 32;
+constexpr int kTPS = 8;                    // 512-byte tiles per ring stage (4 KB)
 constexpr int kMaxTilesPerStage = 16;
 constexpr int kWarps = kThreads / 32;
-constexpr int kCQ = 32;                    // CTA queue of scheduled units
-constexpr int kLook = 6;                   // units the scheduler keeps queued ahead of the consumer
-constexpr int kMaxR = 2;                   // row tiles per unit
+constexpr int kCQ = 16;                    // per-warp queue of scheduled units
+constexpr int kLook = 6;                   // entries a warp keeps queued ahead of its consumer side
+constexpr int kMaxR = 4;                   // row tiles per unit
 
 TI_DEVICE void epilogue(const GemvParams& p, int nt, int g, int t, const float (&acc)[4]) {
   const int n = nt * 8 + 2 * t;
@@ -147,6 +151,12 @@ TI_DEVICE void epilogue(const GemvParams& p, int nt, int g, int t, const float (
 // Activations may have been written earlier in the SAME launch by another SM (chained products): read them
 // through L2, never through the non-coherent path.
 TI_DEVICE uint4 ld_x16(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
+
+TI_DEVICE uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
 
 // ---------------------------------------------------------------- integer tensor-core MMAs
 TI_DEVICE void imma_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -393,48 +403,51 @@ TI_DEVICE void stage_bf16_norm(const GemvParams& p, __nv_bfloat16* xs, int xs_st
 }
 
 // ---------------------------------------------------------------- work decomposition
-// A unit is R consecutive row tiles (8 weight rows each) over the WHOLE k range; the 16 warps of a CTA
-// split k evenly and meet in shared memory, so no partial sum ever leaves the SM and nothing is fenced
-// or counted in global memory.  Units are dealt to CTAs: the first one statically (unit = CTA index),
-// the rest through one ticket counter per product, drawn a unit ahead by a scheduler thread (warp 0,
-// lane 0) that keeps a CTA-wide queue of the next units.  Every warp runs a private weight stream
-// (TMA bulk copies into its ring) along that queue, as far ahead as its ring allows, also across the
-// products of a chain.
+// A unit is R consecutive row tiles (8 weight rows each) over the WHOLE k range, owned by ONE warp: no
+// partial sum ever leaves the warp, nothing is reduced, fenced or counted anywhere.  A warp streams its
+// unit through a private ring of shared memory filled by TMA bulk copies (the tiles of a row tile are
+// contiguous), deep enough to cover HBM latency at that warp's share of the bandwidth, and keeps
+// streaming across units and across the products of a chain.  Units are dealt to warps: the first ones
+// statically (spread over the SMs first), the rest through one ticket counter per product, drawn one
+// unit ahead.  A per-warp queue in shared memory carries the unit sequence from the issuing side (lane 0
+// runs ahead with the copies) to the consuming side.
 TI_DEVICE int num_units(const GemvParams& p) { return (p.n_tiles + p.R - 1) / p.R; }
 #define TI_UNIT_END (-1)
-TI_DEVICE int pack_unit(int op, int unit) { return (op << 26) | unit; }
 constexpr int kUnitMask = (1 << 26) - 1;
-// queue entry that opens product `op`: every CTA sees it (and takes part in the grid barrier and the
+TI_DEVICE int pack_unit(int op, int unit) { return (op << 26) | unit; }
+// queue entry that opens product `op`: every warp sees it (and takes part in the grid barrier and the
 // activation staging of that product) whether or not it gets any unit of the product
 TI_DEVICE int pack_begin(int op) { return (op << 26) | kUnitMask; }
+// Units k*W + widx for k < num_static are assigned statically (no atomics: they can be queued before the
+// kernel may look at mutable state); the rest of a product's units go through the ticket counter, which
+// evens out warps that fell behind.
+TI_DEVICE int num_static(const GemvParams& p, int W) { return max(1, num_units(p) / (2 * W)); }
 
-// Units k*ncta + cta for k < num_static are assigned statically (no atomics: they can be queued before the
-// kernel may look at mutable state and they fill the look-ahead at once); the second half of a product's
-// units is handed out through the ticket counter, which evens out CTAs that fell behind.
-TI_DEVICE int num_static(const GemvParams& p, int ncta) { return max(1, num_units(p) / (2 * ncta)); }
+struct WarpStream {           // registers of lane 0 of each warp; queue storage in shared memory
+  // scheduling side
+  int op, pre, sk, wr, rd;
+  bool pre_valid, sdone, can_ticket, opened;
+  // copy side
+  int cs, idx, left, row_left, kb_row;
+  uint32_t ist;
+  bool have, cdone;
+  const uint8_t* gptr;
 
-struct Scheduler {            // registers of warp 0 / lane 0; queue storage in shared memory
-  int op, pre, sk;
-  bool pre_valid, done, can_ticket, opened;
-  TI_DEVICE void push(volatile int* cq, volatile int* wr, int e) {
-    const int w = *wr;
-    cq[w % kCQ] = e;
-    __threadfence_block();
-    *wr = w + 1;
-  }
-  TI_DEVICE void fill(const ChainParams& c, int cta, int ncta, volatile int* cq, volatile int* wr, int upto) {
-    while (!done && *wr < upto) {
+  TI_DEVICE void push(volatile int* q, int e) { q[wr++ % kCQ] = e; }
+  // queue the next entries of this warp's unit sequence, at most up to `ahead` entries beyond `rd`
+  TI_DEVICE void schedule(const ChainParams& c, int widx, int W, volatile int* q, int ahead) {
+    while (!sdone && wr - rd < ahead) {
       const GemvParams& p = c.op[op];
-      const int U = num_units(p), ns = num_static(p, ncta);
+      const int U = num_units(p), ns = num_static(p, W);
       if (!opened) {
         opened = true;
-        push(cq, wr, pack_begin(op));
+        push(q, pack_begin(op));
         continue;
       }
       if (sk < ns) {
-        const int u = sk * ncta + cta;
+        const int u = sk * W + widx;
         ++sk;
-        if (u < U) push(cq, wr, pack_unit(op, u));
+        if (u < U) push(q, pack_unit(op, u));
         continue;
       }
       if (!can_ticket) return;
@@ -443,77 +456,63 @@ struct Scheduler {            // registers of warp 0 / lane 0; queue storage in 
         pre = atomicAdd(ticket, 1);
         pre_valid = true;
       }
-      const int u = ns * ncta + pre;
+      const int u = ns * W + pre;
       if (u >= U) {
         sk = 0;
         pre_valid = opened = false;
         if (++op >= c.n_ops) {
-          push(cq, wr, TI_UNIT_END);
-          done = true;
+          push(q, TI_UNIT_END);
+          sdone = true;
         }
         continue;
       }
       pre = atomicAdd(ticket, 1);          // next ticket, used one unit from now
-      push(cq, wr, pack_unit(op, u));
+      push(q, pack_unit(op, u));
     }
   }
-  // draw the first ticket of the current product early so that its latency is hidden
-  TI_DEVICE void warm(const ChainParams& c) {
-    if (!done && can_ticket && !pre_valid) {
-      pre = atomicAdd(c.op[op].sched + 8 + op * 16, 1);
-      pre_valid = true;
-    }
-  }
-};
-
-struct WarpCursor {           // registers of lane 0 of each warp
-  int seq, r, rn, tile, nkb, idx;
-  bool have, done;
-  size_t base, rstride;
-  const uint8_t* w;
-  TI_DEVICE bool load(const ChainParams& c, int warp, volatile int* cq, volatile int* wr) {
-    while (!done && seq < *wr) {
-      const int e = cq[seq % kCQ];
+  TI_DEVICE bool load(const ChainParams& c, int widx, int W, volatile int* q) {
+    while (!cdone) {
+      if (cs >= wr) schedule(c, widx, W, q, kLook);
+      if (cs >= wr) return false;
+      const int e = q[cs % kCQ];
       if (e == TI_UNIT_END) {
-        done = true;
+        cdone = true;
         return false;
       }
-      const GemvParams& p = c.op[e >> 26];
       const int unit = e & kUnitMask;
-      const int kb_lo = (warp * p.KB) / kWarps, kb_hi = ((warp + 1) * p.KB) / kWarps;
-      nkb = kb_hi - kb_lo;
-      if (unit == kUnitMask || nkb <= 0) { // a product marker, or fewer k tiles than warps: nothing to stream
-        ++seq;
+      if (unit == kUnitMask) {             // product marker: nothing to stream
+        ++cs;
         continue;
       }
-      rn = min(p.R, p.n_tiles - unit * p.R);
-      r = 0;
-      tile = 0;
-      w = p.w;
-      rstride = (size_t)p.KB * 512;
-      base = ((size_t)unit * p.R * p.KB + kb_lo) * 512;
+      const GemvParams& p = c.op[e >> 26];
+      // the R row tiles of a unit are adjacent in memory: one contiguous run of rn * KB tiles
+      const int rn = min(p.R, p.n_tiles - unit * p.R);
+      left = rn * p.KB;
+      row_left = p.KB;
+      kb_row = p.KB;
+      gptr = p.w + (size_t)unit * p.R * p.KB * 512;
       have = true;
       return true;
     }
     return false;
   }
-  TI_DEVICE void next(const ChainParams& c, int warp, volatile int* cq, volatile int* wr, uint32_t ring_u32,
-                      uint32_t bar0, int stages, int tps) {
-    if (!have && !load(c, warp, cq, wr)) return;
-    const int ntile = min(tps, nkb - tile);
-    const uint32_t st = (uint32_t)idx % (uint32_t)stages;
+  // hands the next chunk (<= kTPS tiles, never across a row tile) to the TMA engine
+  TI_DEVICE void next(const ChainParams& c, int widx, int W, volatile int* q, uint32_t ring_u32, uint32_t bar0,
+                      int stages) {
+    if (!have && !load(c, widx, W, q)) return;
+    const int ntile = min(kTPS, row_left);
     const uint32_t bytes = (uint32_t)ntile * 512u;
-    mbar_expect_tx(bar0 + st * 8, bytes);
-    bulk_g2s(ring_u32 + st * (uint32_t)tps * 512u, w + base + (size_t)r * rstride + (size_t)tile * 512, bytes,
-             bar0 + st * 8);
+    mbar_expect_tx(bar0 + ist * 8, bytes);
+    bulk_g2s(ring_u32 + ist * (kTPS * 512u), gptr, bytes, bar0 + ist * 8);
+    ist = ist + 1 == (uint32_t)stages ? 0u : ist + 1;
     ++idx;
-    tile += ntile;
-    if (tile >= nkb) {
-      tile = 0;
-      if (++r >= rn) {
-        have = false;
-        ++seq;
-      }
+    gptr += bytes;
+    left -= ntile;
+    row_left -= ntile;
+    if (row_left == 0) row_left = kb_row;
+    if (left == 0) {
+      have = false;
+      ++cs;
     }
   }
 };
@@ -549,36 +548,29 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
   const bool stamp = p0.dbg != nullptr && tid == 0;
   if (stamp) p0.dbg[cta * 8 + 0] = globaltimer_ns();
   const size_t x_bytes = (size_t)c.x_bytes;
+  const int W = ncta * kWarps, widx = warp * ncta + cta;      // consecutive units land on different SMs
 
-  // ---- shared memory: [staged x | per-warp partial sums (2 buffers) | rings | mbarriers | unit queue]
-  const int stages = p0.stages, tps = p0.tps;
-  const int stage_bytes = tps * 512;
-  float* part = reinterpret_cast<float*>(smem + x_bytes);                        // [2][kWarps][kMaxR][128]
-  uint8_t* ring0 = smem + x_bytes + 2 * kWarps * kMaxR * 512;
+  // ---- shared memory: [staged x | rings | mbarriers | unit queues]
+  const int stages = p0.stages;
+  const int stage_bytes = kTPS * 512;
+  uint8_t* ring0 = smem + x_bytes;
   uint8_t* ring = ring0 + (size_t)warp * stages * stage_bytes;
   const uint32_t ring_u32 = smem_u32(ring);
   uint8_t* after_ring = ring0 + (size_t)kWarps * stages * stage_bytes;
   const uint32_t bar0 = smem_u32(after_ring) + warp * stages * 8;
-  volatile int* cq = reinterpret_cast<volatile int*>(after_ring + kWarps * stages * 8);
-  volatile int* cq_wr = cq + kCQ;
+  volatile int* q = reinterpret_cast<volatile int*>(after_ring + kWarps * stages * 8) + warp * kCQ;
 
-  Scheduler sch;
-  sch.op = sch.pre = sch.sk = 0;
-  sch.pre_valid = sch.done = sch.can_ticket = sch.opened = false;
-  if (tid == 0) {
-    *cq_wr = 0;
-    sch.fill(c, cta, ncta, cq, cq_wr, kLook);      // static units of the first product only (no tickets yet)
-  }
-  __syncthreads();
-  WarpCursor cur;
-  cur.seq = cur.r = cur.rn = cur.tile = cur.nkb = cur.idx = 0;
-  cur.have = cur.done = false;
-  cur.base = cur.rstride = 0;
-  cur.w = nullptr;
+  WarpStream ws;
+  ws.op = ws.pre = ws.sk = ws.wr = ws.rd = 0;
+  ws.pre_valid = ws.sdone = ws.can_ticket = ws.opened = false;
+  ws.cs = ws.idx = ws.left = ws.row_left = ws.kb_row = 0;
+  ws.ist = 0;
+  ws.have = ws.cdone = false;
+  ws.gptr = nullptr;
   if (lane == 0) {
     for (int s = 0; s < stages; ++s) mbar_init(bar0 + s * 8, 1);
     fence_mbar_init();
-    for (int s = 0; s < stages; ++s) cur.next(c, warp, cq, cq_wr, ring_u32, bar0, stages, tps);
+    for (int s = 0; s < stages; ++s) ws.next(c, widx, W, q, ring_u32, bar0, stages);   // static units only
   }
   __syncwarp();
   // Everything above touched only weights and this CTA's shared memory.  Let the next kernel of the
@@ -587,45 +579,34 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
   pdl_trigger();
   pdl_wait();
   if (stamp) p0.dbg[cta * 8 + 1] = globaltimer_ns();
-  if (tid == 0) {
-    sch.can_ticket = true;
-    sch.warm(c);
-  }
+  if (lane == 0) ws.can_ticket = true;
 
   unsigned cidx = 0;                            // chunks consumed by this warp so far
+  uint32_t cst = 0, cpar = 0;                   // ring stage / mbarrier phase of the next chunk to consume
   bool alive = true;
   float* scratch = reinterpret_cast<float*>(smem + x_bytes - 2048);
-  int cur_op = -1;
   float inv0 = 0.f, inv1 = 0.f;                 // value of one fixed-point unit for rows g and g+8
   int lstride = 0;
   int8_t* xh = reinterpret_cast<int8_t*>(smem);
   uint8_t* xl = smem;
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem);
 
-  for (int cseq = 0;; ++cseq) {
-    // ---- next unit of this CTA
-    if (tid == 0) sch.fill(c, cta, ncta, cq, cq_wr, cseq + kLook);
+  while (true) {
+    // ---- next entry of this warp's sequence
     int e = 0;
     if (lane == 0) {
-      const unsigned long long t0 = globaltimer_ns();
-      unsigned spins = 0;
-      while (*cq_wr <= cseq) {                   // only until the scheduler thread has published it
-        if ((++spins & 1023u) == 0u && globaltimer_ns() - t0 > 2000000000ull) {
-          if (p0.status != nullptr) atomicOr(p0.status, kStatusPeerTimeout);
-          break;
-        }
-      }
-      e = *cq_wr <= cseq ? TI_UNIT_END : cq[cseq % kCQ];
+      if (ws.rd >= ws.wr) ws.schedule(c, widx, W, q, kLook);
+      e = ws.rd >= ws.wr ? TI_UNIT_END : q[ws.rd % kCQ];
+      ++ws.rd;
     }
     e = __shfl_sync(0xffffffffu, e, 0);
     if (e == TI_UNIT_END) break;
     const int op = e >> 26, unit = e & kUnitMask;
     const GemvParams& p = c.op[op];
     if (unit == kUnitMask) {
-      // ---- product boundary: everyone is done with the previous product; stage the new activations
+      // ---- product boundary: every warp of every CTA is done with the previous product
       if (op > 0) grid_barrier(p0.sched + 2, op * ncta, p0.status);
       else __syncthreads();
-      cur_op = op;
       lstride = limb_stride(p.K);
       xl = smem + (size_t)p.M * lstride;
       if (WT == W_INT8) stage_limbs(p, 0, p.K, xh, xl, lstride, scratch);
@@ -637,14 +618,17 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
       if (stamp && op == 0) p0.dbg[cta * 8 + 2] = globaltimer_ns();
       continue;
     }
-    if (lane == 0)                                // keep the ring full (it may have been starved of queue entries)
-      for (int s = cur.idx - (int)cidx; s < stages; ++s) cur.next(c, warp, cq, cq_wr, ring_u32, bar0, stages, tps);
+    if (lane == 0)                                // keep the ring full
+      for (int s = ws.idx - (int)cidx; s < stages; ++s) ws.next(c, widx, W, q, ring_u32, bar0, stages);
 
     const bool hi = p.M > 8;
-    const int kb_lo = (warp * p.KB) / kWarps, kb_hi = ((warp + 1) * p.KB) / kWarps;
-    const int nkb = kb_hi - kb_lo;
     const int rn = min(p.R, p.n_tiles - unit * p.R);
-    float* mypart = part + ((size_t)(cseq & 1) * kWarps + warp) * kMaxR * 128 + lane * 4;
+    // rows of the staged activations this lane feeds to the MMA (rows >= M are clamped: their results
+    // are never written)
+    const uint32_t xrow0 = (uint32_t)min(g, p.M - 1), xrow1 = (uint32_t)min(g + 8, p.M - 1);
+    const uint32_t xh0 = smem_u32(xh) + xrow0 * (uint32_t)lstride + t * 16, xl0 = smem_u32(xl) + xrow0 * (uint32_t)lstride + t * 16;
+    const uint32_t xh1 = smem_u32(xh) + xrow1 * (uint32_t)lstride + t * 16, xl1 = smem_u32(xl) + xrow1 * (uint32_t)lstride + t * 16;
+    const uint32_t xs0 = smem_u32(xs) + (xrow0 * (uint32_t)(p.K + 8) + t * 8) * 2, xs1 = smem_u32(xs) + (xrow1 * (uint32_t)(p.K + 8) + t * 8) * 2;
     for (int r = 0; r < rn; ++r) {
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       int ah[2][4], al[2][4];                    // two accumulator sets: consecutive tiles do not chain
@@ -652,65 +636,69 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
       for (int a = 0; a < 2; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) ah[a][b] = al[a][b] = 0;
-      for (int tile0 = 0; tile0 < nkb; tile0 += tps) {
-        const int ntile = min(tps, nkb - tile0);
-        const unsigned st = cidx % (unsigned)stages;
-        if (alive) alive = mbar_wait(bar0 + st * 8, (cidx / (unsigned)stages) & 1u, 2000000000ull, p.status);
-        if (stamp && cidx == 0) p0.dbg[cta * 8 + 3] = globaltimer_ns();
-        const uint8_t* sbuf = ring + (size_t)st * stage_bytes + lane * 16;
+      for (int tile0 = 0; tile0 < p.KB; tile0 += kTPS) {
+        const int ntile = min(kTPS, p.KB - tile0);
+        if (alive) alive = mbar_wait(bar0 + cst * 8, cpar, 2000000000ull, p.status);
+        const uint32_t sbuf = ring_u32 + cst * (kTPS * 512u) + lane * 16;
+        if (WT == W_INT8) {
+          const uint32_t o = (uint32_t)tile0 * 64u;
+          if (!hi) {
 #pragma unroll
-        for (int u = 0; u < kMaxTilesPerStage; ++u) {
-          if (u >= ntile) break;
-          const uint4 wv = *reinterpret_cast<const uint4*>(sbuf + u * 512);
-          const int kb = kb_lo + tile0 + u;
-          if (WT == W_INT8) {
-            const size_t xo = (size_t)kb * 64 + t * 16;
-            const uint4 z = make_uint4(0, 0, 0, 0);
-            const uint4 h0 = g < p.M ? *reinterpret_cast<const uint4*>(xh + (size_t)g * lstride + xo) : z;
-            const uint4 l0 = g < p.M ? *reinterpret_cast<const uint4*>(xl + (size_t)g * lstride + xo) : z;
-            const uint4 h1 = (hi && g + 8 < p.M) ? *reinterpret_cast<const uint4*>(xh + (size_t)(g + 8) * lstride + xo) : z;
-            const uint4 l1 = (hi && g + 8 < p.M) ? *reinterpret_cast<const uint4*>(xl + (size_t)(g + 8) * lstride + xo) : z;
-            imma_s8s8(ah[u & 1], h0.x, h1.x, h0.y, h1.y, wv.x, wv.y);
-            imma_u8s8(al[u & 1], l0.x, l1.x, l0.y, l1.y, wv.x, wv.y);
-            imma_s8s8(ah[u & 1], h0.z, h1.z, h0.w, h1.w, wv.z, wv.w);
-            imma_u8s8(al[u & 1], l0.z, l1.z, l0.w, l1.w, wv.z, wv.w);
-          } else {
-            const int k0 = kb * 32 + t * 8;
-            uint4 xv, yv;
-            if (p.xmode == XNORM) {
-              xv = *reinterpret_cast<const uint4*>(xs + (size_t)g * (p.K + 8) + k0);
-              yv = hi ? *reinterpret_cast<const uint4*>(xs + (size_t)(g + 8) * (p.K + 8) + k0) : make_uint4(0, 0, 0, 0);
-            } else {
-              xv = (g < p.M) ? ld_x16(p.x + (size_t)g * p.ldx + k0) : make_uint4(0, 0, 0, 0);
-              yv = (g + 8 < p.M) ? ld_x16(p.x + (size_t)(g + 8) * p.ldx + k0) : make_uint4(0, 0, 0, 0);
+            for (int u = 0; u < kTPS; ++u) {
+              if (u < ntile) {
+                const uint4 wv = lds128(sbuf + u * 512), h0 = lds128(xh0 + o + u * 64), l0 = lds128(xl0 + o + u * 64);
+                imma_s8s8(ah[u & 1], h0.x, 0u, h0.y, 0u, wv.x, wv.y);
+                imma_u8s8(al[u & 1], l0.x, 0u, l0.y, 0u, wv.x, wv.y);
+                imma_s8s8(ah[u & 1], h0.z, 0u, h0.w, 0u, wv.z, wv.w);
+                imma_u8s8(al[u & 1], l0.z, 0u, l0.w, 0u, wv.z, wv.w);
+              }
             }
-            mma_bf16_16816(acc, xv.x, yv.x, xv.y, yv.y, wv.x, wv.y);
-            mma_bf16_16816(acc, xv.z, yv.z, xv.w, yv.w, wv.z, wv.w);
+          } else {
+#pragma unroll
+            for (int u = 0; u < kTPS; ++u) {
+              if (u < ntile) {
+                const uint4 wv = lds128(sbuf + u * 512), h0 = lds128(xh0 + o + u * 64), l0 = lds128(xl0 + o + u * 64);
+                const uint4 h1 = lds128(xh1 + o + u * 64), l1 = lds128(xl1 + o + u * 64);
+                imma_s8s8(ah[u & 1], h0.x, h1.x, h0.y, h1.y, wv.x, wv.y);
+                imma_u8s8(al[u & 1], l0.x, l1.x, l0.y, l1.y, wv.x, wv.y);
+                imma_s8s8(ah[u & 1], h0.z, h1.z, h0.w, h1.w, wv.z, wv.w);
+                imma_u8s8(al[u & 1], l0.z, l1.z, l0.w, l1.w, wv.z, wv.w);
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int u = 0; u < kTPS; ++u) {
+            if (u < ntile) {
+              const uint4 wv = lds128(sbuf + u * 512);
+              const int k0 = (tile0 + u) * 32;
+              uint4 xv, yv = make_uint4(0, 0, 0, 0);
+              if (p.xmode == XNORM) {
+                xv = lds128(xs0 + k0 * 2);
+                if (hi) yv = lds128(xs1 + k0 * 2);
+              } else {
+                xv = ld_x16(p.x + (size_t)xrow0 * p.ldx + k0 + t * 8);
+                if (hi) yv = ld_x16(p.x + (size_t)xrow1 * p.ldx + k0 + t * 8);
+              }
+              mma_bf16_16816(acc, xv.x, yv.x, xv.y, yv.y, wv.x, wv.y);
+              mma_bf16_16816(acc, xv.z, yv.z, xv.w, yv.w, wv.z, wv.w);
+            }
           }
         }
         __syncwarp();                            // every lane is done with the stage before it is refilled
         ++cidx;
-        if (lane == 0) cur.next(c, warp, cq, cq_wr, ring_u32, bar0, stages, tps);
+        if (++cst == (uint32_t)stages) {
+          cst = 0;
+          cpar ^= 1u;
+        }
+        if (lane == 0) ws.next(c, widx, W, q, ring_u32, bar0, stages);
       }
       if (WT == W_INT8) {
 #pragma unroll
         for (int b = 0; b < 4; ++b)
           acc[b] = ((float)(ah[0][b] + ah[1][b]) * 256.f + (float)(al[0][b] + al[1][b])) * (b < 2 ? inv0 : inv1);
       }
-      *reinterpret_cast<float4*>(mypart + r * 128) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    }
-    __syncthreads();                             // the k slices of all 16 warps are in shared memory
-    if (warp == (cseq & (kWarps - 1))) {         // one warp (rotating) reduces in a fixed order and finishes the rows
-      const float* pb = part + (size_t)(cseq & 1) * kWarps * kMaxR * 128 + lane * 4;
-      for (int r = 0; r < rn; ++r) {
-        float sum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-          const float4 v = *reinterpret_cast<const float4*>(pb + ((size_t)w * kMaxR + r) * 128);
-          sum[0] += v.x; sum[1] += v.y; sum[2] += v.z; sum[3] += v.w;
-        }
-        epilogue(p, unit * p.R + r, g, t, sum);
-      }
+      epilogue(p, unit * p.R + r, g, t, acc);
     }
     if (stamp) p0.dbg[cta * 8 + 4] = globaltimer_ns();
   }
@@ -748,14 +736,14 @@ static int op_x_bytes(const GemvParams& p, int wt) { return (int)x_smem_bytes_im
 
 static size_t smem_bytes(const ChainParams& c) {
   const GemvParams& p = c.op[0];
-  return (size_t)c.x_bytes + 2 * kWarps * kMaxR * 512 + (size_t)kWarps * p.stages * (p.tps * 512 + 8) + (kCQ + 4) * 4;
+  return (size_t)c.x_bytes + (size_t)kWarps * (p.stages * (p.tps * 512 + 8) + kCQ * 4);
 }
 
 static int check(const GemvParams& p, int wt) {
   const int tk = wt == W_INT8 ? 64 : 32;
   if (p.M < 1 || p.M > 16 || p.N < 2 || (p.N & 1) || p.K % tk || p.KB * tk != p.K) return -2;
   if (p.R < 1 || p.R > kMaxR || p.n_tiles < 1 || p.n_tiles >= (1 << 26)) return -3;
-  if (p.tps != 4 && p.tps != 8 && p.tps != 16) return -7;
+  if (p.tps != kTPS) return -7;
   if (p.sched == nullptr || p.stages < 1 || p.stages > 8) return -7;
   if (p.xmode < 0 || p.xmode > 1 || p.epi < 0 || p.epi > 3) return -8;
   if (p.K % 8 || p.ldx % 8) return -4;

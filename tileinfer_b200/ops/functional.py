@@ -20,7 +20,7 @@ XGLOBAL, XNORM = 0, 1
 EPI_STORE, EPI_SWIGLU, EPI_ROWPAR, EPI_F32 = 0, 1, 2, 3
 W_INT8, W_BF16 = 0, 1
 NUM_SMS = 148
-GEMV_WARPS = 16
+GEMV_WARPS = int(os.environ.get("TI_GEMV_WARPS", "16"))   # must match the -DTI_GEMV_WARPS the library was built with
 GEMV_TPS = int(os.environ.get("TI_GEMV_TPS", "8"))            # 512-byte tiles per ring stage
 GEMV_MAX_STAGES = int(os.environ.get("TI_GEMV_STAGES", "6"))
 GEMV_UNITS_PER_WARP = int(os.environ.get("TI_GEMV_UPW", "4"))
@@ -138,8 +138,8 @@ def x_smem_bytes(wt: int, xmode: int, M: int, K: int, kslice: int) -> int:
     return (b + 2048 + 127) // 128 * 128
 
 
-PART_BYTES = 2 * GEMV_WARPS * 2 * 512          # per-warp partial sums, two buffers, up to two row tiles
-_RING_CHOICES = ((8, 3), (8, 2), (4, 3), (4, 2), (4, 1))
+PART_BYTES = 0
+_RING_CHOICES = ((8, 6), (8, 5), (8, 4), (8, 3), (8, 2), (8, 1))
 
 
 def plan_gemv(wt: int, xmode: int, M: int, n_tiles: int, KB: int, ncta: int = NUM_SMS):
@@ -148,12 +148,9 @@ def plan_gemv(wt: int, xmode: int, M: int, n_tiles: int, KB: int, ncta: int = NU
     activations and the partial-sum buffers in 227 KB."""
     tk = 64 if wt == W_INT8 else 32
     xb = x_smem_bytes(wt, xmode, M, KB * tk, KB * tk)
-    R = 2 if n_tiles >= 8 * ncta else 1
-    forced = os.environ.get("TI_GEMV_TPS")
+    R = 2 if n_tiles >= 8 * ncta * GEMV_WARPS else 1
     for tps, stages in _RING_CHOICES:
-        if forced and int(forced) != tps:
-            continue
-        if xb + PART_BYTES + GEMV_WARPS * stages * (tps * 512 + 8) + 256 <= 227 * 1024:
+        if xb + PART_BYTES + GEMV_WARPS * (stages * (tps * 512 + 8) + 64) <= 227 * 1024:
             return R, tps, stages
     return None
 
