@@ -119,34 +119,46 @@ TI_DEVICE void epilogue(const GemvParams& p, int nt, int g, int t, const float (
       const float gate = round_bf16(v0), up = round_bf16(v1);
       static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] = __float2bfloat16_rn(silu_f(gate) * up);
     } else {  // EPI_ROWPAR
-      float sum0 = v0, sum1 = v1;
       if (p.tp > 1) {
+        // Send only: the partial goes, tagged, into the packet buffer of EVERY rank (this one included).
+        // Nothing is awaited here, so ranks whose warps take the row tiles in a different order can never
+        // wait on each other in a cycle; rowpar_reduce() collects the packets once the product is done.
         const unsigned tag = (*p.step_ptr) * 65536u + (unsigned)p.order + 1u;
         const int slot = p.order & 1;
-        const size_t pairs = (size_t)(p.N >> 1);
-        const size_t mine = (((size_t)slot * p.tp + p.rank) * p.m_cap + m) * pairs + (n >> 1);
-        for (int q = 0; q < p.tp; ++q)
-          if (q != p.rank) ll_store2(reinterpret_cast<uint8_t*>(p.peer_ll[q]) + mine * 16, v0, v1, tag);
-        sum0 = 0.f;
-        sum1 = 0.f;
-        const uint8_t* local = reinterpret_cast<const uint8_t*>(p.peer_ll[p.rank]);
-        for (int r = 0; r < p.tp; ++r) {   // fixed rank order: every rank gets the same bits
-          float a = v0, b = v1;
-          if (r != p.rank) {
-            const size_t idx = (((size_t)slot * p.tp + r) * p.m_cap + m) * pairs + (n >> 1);
-            ll_wait2(local + idx * 16, tag, a, b, p.timeout_ns, p.status);
-          }
-          sum0 += a;
-          sum1 += b;
-        }
+        const size_t mine = ((((size_t)slot * p.tp + p.rank) * p.m_cap + m) * (size_t)(p.N >> 1) + (n >> 1)) * 16;
+        for (int q = 0; q < p.tp; ++q) ll_store2(reinterpret_cast<uint8_t*>(p.peer_ll[q]) + mine, v0, v1, tag);
+      } else {
+        const uint32_t rw = __ldcg(reinterpret_cast<const uint32_t*>(p.resid + (size_t)m * p.N + n));
+        uint32_t* o = reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.N + n);
+        *o = pack_bf16(bf16lo(rw) + v0, bf16hi(rw) + v1);
       }
-      const uint32_t rw = __ldcg(reinterpret_cast<const uint32_t*>(p.resid + (size_t)m * p.N + n));
-      uint32_t* o = reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.N + n);
-      *o = pack_bf16(bf16lo(rw) + sum0, bf16hi(rw) + sum1);
     }
   }
 }
 
+// Second half of the fused all-reduce of a row-parallel product (tp > 1): every thread of the grid takes
+// some (row, column pair) positions, waits (bounded) for the tagged packets of all ranks, adds them in rank
+// order (so every rank computes bit-identical sums) and adds the residual.
+TI_DEVICE void rowpar_reduce(const GemvParams& p, int cta, int ncta) {
+  const unsigned tag = (*p.step_ptr) * 65536u + (unsigned)p.order + 1u;
+  const int slot = p.order & 1;
+  const int pairs = p.N >> 1;
+  const uint8_t* local = reinterpret_cast<const uint8_t*>(p.peer_ll[p.rank]);
+  for (int i = cta * blockDim.x + threadIdx.x; i < p.M * pairs; i += ncta * blockDim.x) {
+    const int m = i / pairs, pr = i - m * pairs;
+    float s0 = 0.f, s1 = 0.f;
+    for (int r = 0; r < p.tp; ++r) {
+      float a, b;
+      ll_wait2(local + ((((size_t)slot * p.tp + r) * p.m_cap + m) * (size_t)pairs + pr) * 16, tag, a, b, p.timeout_ns,
+               p.status);
+      s0 += a;
+      s1 += b;
+    }
+    const uint32_t rw = __ldcg(reinterpret_cast<const uint32_t*>(p.resid + (size_t)m * p.N + 2 * pr));
+    uint32_t* o = reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.N + 2 * pr);
+    *o = pack_bf16(bf16lo(rw) + s0, bf16hi(rw) + s1);
+  }
+}
 
 // Activations may have been written earlier in the SAME launch by another SM (chained products): read them
 // through L2, never through the non-coherent path.
@@ -583,6 +595,7 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
 
   unsigned cidx = 0;                            // chunks consumed by this warp so far
   uint32_t cst = 0, cpar = 0;                   // ring stage / mbarrier phase of the next chunk to consume
+  int cur_op = -1;
   bool alive = true;
   float* scratch = reinterpret_cast<float*>(smem + x_bytes - 2048);
   float inv0 = 0.f, inv1 = 0.f;                 // value of one fixed-point unit for rows g and g+8
@@ -600,10 +613,15 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
       ++ws.rd;
     }
     e = __shfl_sync(0xffffffffu, e, 0);
+    if (e == TI_UNIT_END || (e & kUnitMask) == kUnitMask) {
+      // this warp has sent everything it owns of the previous product: collect the all-reduce
+      if (cur_op >= 0 && c.op[cur_op].epi == EPI_ROWPAR && c.op[cur_op].tp > 1) rowpar_reduce(c.op[cur_op], cta, ncta);
+    }
     if (e == TI_UNIT_END) break;
     const int op = e >> 26, unit = e & kUnitMask;
     const GemvParams& p = c.op[op];
     if (unit == kUnitMask) {
+      cur_op = op;
       // ---- product boundary: every warp of every CTA is done with the previous product
       if (op > 0) grid_barrier(p0.sched + 2, op * ncta, p0.status);
       else __syncthreads();
