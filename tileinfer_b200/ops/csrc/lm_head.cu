@@ -12,6 +12,7 @@
 // same way, then (tp > 1) stores its k winners as tagged packets into every peer's buffer and waits,
 // bounded, for the peers' packets.
 #include "common.cuh"
+#include "topk_static.h"
 
 namespace ti {
 
@@ -154,6 +155,82 @@ int ti_topk(const ti::TopkParams* p, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   ti::launch_kernel(ti::topk_stage1_kernel, dim3(p->M, p->chunks), dim3(256), 0, st, true, *p);
   ti::launch_kernel(ti::topk_stage2_kernel, dim3(p->M), dim3(256), 0, st, true, *p);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------ allocation-free entry point
+// Same two kernels as ti_topk(); the per-chunk candidate workspace is a file-scope device array, so the
+// call allocates nothing.  See topk_static.h for who this is for, the limits and the sharing rules.
+namespace ti {
+static __device__ __align__(256) float g_topk_static_val[TI_TOPK_STATIC_MAX_ENTRIES];
+static __device__ __align__(256) int g_topk_static_idx[TI_TOPK_STATIC_MAX_ENTRIES];
+constexpr int kMaxDevices = 64;
+static float* g_static_val_ptr[kMaxDevices];
+static int* g_static_idx_ptr[kMaxDevices];
+static bool g_static_ready[kMaxDevices];
+}  // namespace ti
+
+extern "C" {
+
+const char* ti_topk_static_error(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case -1: return "rows must be in [1, 16]: the static scratch holds 16 rows";
+    case -2: return "k must be in [1, 64]";
+    case -3: return "vocab must be in [1, 524288] and ld >= vocab";
+    case -4: return "null pointer argument";
+    case -5: return "more than 64 CUDA devices are not supported";
+    default: return code > 0 ? "CUDA error (value is a cudaError_t)" : "unknown error";
+  }
+}
+
+int ti_topk_static(const float* logits, int rows, int vocab, int ld, int k, int vocab_start, float* out_val,
+                   int* out_idx, void* stream) {
+  if (logits == nullptr || out_val == nullptr || out_idx == nullptr) return -4;
+  if (rows < 1 || rows > TI_TOPK_STATIC_MAX_ROWS) return -1;
+  if (k < 1 || k > 64) return -2;
+  if (vocab < 1 || vocab > 128 * 4096 || ld < vocab) return -3;
+  // chunk geometry: at most 128 chunks and 8192 candidates per row, chunks of a multiple of 256 columns
+  const int max_chunks = 8192 / k < 128 ? 8192 / k : 128;
+  int cs = (vocab + max_chunks - 1) / max_chunks;
+  cs = ((cs + 255) / 256) * 256;
+  if (cs < 256) cs = 256;
+  if (cs > 4096) return -3;
+  const int chunks = (vocab + cs - 1) / cs;
+  // the device address of the scratch: the array's name is only a host-side handle, so it is resolved
+  // once per device, with that device current, and cached
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= ti::kMaxDevices) return -5;
+  if (!ti::g_static_ready[dev]) {
+    e = cudaGetSymbolAddress((void**)&ti::g_static_val_ptr[dev], ti::g_topk_static_val);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaGetSymbolAddress((void**)&ti::g_static_idx_ptr[dev], ti::g_topk_static_idx);
+    if (e != cudaSuccess) return (int)e;
+    ti::g_static_ready[dev] = true;
+  }
+  ti::TopkParams p = {};
+  p.logits = logits;
+  p.ws_val = ti::g_static_val_ptr[dev];
+  p.ws_idx = ti::g_static_idx_ptr[dev];
+  p.out_val = out_val;
+  p.out_idx = out_idx;
+  p.M = rows;
+  p.V = vocab;
+  p.ld = ld;
+  p.k = k;
+  p.chunks = chunks;
+  p.chunk_size = cs;
+  p.vocab_start = vocab_start;
+  p.tp = 1;
+  cudaStream_t st = (cudaStream_t)stream;
+  e = ti::launch_kernel(ti::topk_stage1_kernel, dim3(rows, chunks), dim3(256), 0, st, false, p);
+  if (e != cudaSuccess) return (int)e;
+  e = ti::launch_kernel(ti::topk_stage2_kernel, dim3(rows), dim3(256), 0, st, false, p);
+  if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();
 }
 
