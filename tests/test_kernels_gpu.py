@@ -421,3 +421,33 @@ def test_topk(k):
     torch.testing.assert_close(vals, rv)
     assert int(idx[0, 0]) == 1017
     assert torch.equal(idx[1:].long() - 1000, ri[1:])
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (200, 1552, 384), (64, 5120, 768), (300, 2048, 5120)])
+def test_tcgen05_gemm_w8a16(M, N, K):
+    """TMA-fed tcgen05 kind::i8 GEMM with two-limb activations against fp32 matmul, all three epilogues."""
+    F = _F()
+    W = F.LinearW(_rand_w(N, K, seed=31), True)
+    x = (torch.randn(M, K, device="cuda") * 1.5).to(BF16)
+    limbs = F.quant_rows(x)
+    recon = (limbs.hi.float() * 256 + limbs.lo.float()) * limbs.scale[:, None]
+    torch.testing.assert_close(recon, x.float(), rtol=0, atol=float(x.float().abs().max()) * 2.0 ** -14)
+    y = F.gemm_w8a16(W, limbs)
+    torch.cuda.synchronize()
+    ref = x.float() @ W.dense().float().t()
+    tol = dict(rtol=2e-2, atol=3e-2 if K < 2048 else 8e-2)      # outputs of magnitude ~10: one bf16 ulp is 0.06
+    torch.testing.assert_close(y.float(), ref, **tol)
+    r = torch.randn(M, N, device="cuda").to(BF16)
+    y2 = F.gemm_w8a16(W, limbs, epi=F.GEPI_ROWPAR, resid=r)
+    torch.testing.assert_close(y2.float(), r.float() + ref, rtol=2e-2, atol=tol["atol"] + 1e-2)
+    y3 = F.gemm_w8a16(W, limbs, epi=F.GEPI_SWIGLU)
+    gu = ref.to(BF16).float()
+    torch.testing.assert_close(y3.float(), torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2], rtol=3e-2, atol=0.3)
+    # fused RMSNorm in the limb kernel
+    nw = (torch.randn(K, device="cuda") * 0.1).to(BF16)
+    ln = F.quant_rows(x, norm_w=nw)
+    xf = x.float()
+    xn = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + nw.float())).to(BF16).float()
+    y4 = F.gemm_w8a16(W, ln)
+    torch.testing.assert_close(y4.float(), xn @ W.dense().float().t(), **tol)
+    assert int(torch.zeros(1, device="cuda").item()) == 0

@@ -115,6 +115,7 @@ class _ModelBase:
         self._launches = 0
         self._pending, self._pending_wt = [], 0
         self.chain = os.environ.get("TI_GEMV_CHAIN", "1") != "0"
+        self.gemm_min_rows = int(os.environ.get("TI_GEMM_MIN_ROWS", "16"))   # more rows than this: tcgen05 GEMM
 
     # ------------------------------------------------------------------ caches
     def weight_bytes(self) -> int:
@@ -209,8 +210,18 @@ class _StepMixin:
         return x
 
     # ------------------------------------------------------------------ launches
+    def _gemm(self, W: LinearW, x, out, M, *, epi, norm_w=None, resid=None):
+        """Prefill path (many rows): limb planes of x (RMSNorm fused), then the tcgen05 GEMM."""
+        self._flush()
+        limbs = F.quant_rows(x[:M], norm_w=norm_w, eps=self.cfg.rms_eps)
+        gepi = {EPI_STORE: F.GEPI_STORE, EPI_SWIGLU: F.GEPI_SWIGLU, EPI_ROWPAR: F.GEPI_ROWPAR}[epi]
+        F.gemm_w8a16(W, limbs, out=out[:M], epi=gepi, resid=None if resid is None else resid[:M])
+        self._launches += 2
+
     def _gemv(self, W: LinearW, x, out, M, *, xmode, epi, norm_w=None, resid=None, ldo=None):
         """y = x W^T in row chunks of 16; counts launches; assigns collective order numbers."""
+        if M > self.gemm_min_rows and W.wt == F.W_INT8 and epi != EPI_F32 and not (epi == EPI_ROWPAR and self.tp > 1):
+            return self._gemm(W, x, out, M, epi=epi, norm_w=norm_w if xmode == XNORM else None, resid=resid)
         step = F.max_rows(W.wt, xmode, W.K)
         for m0 in range(0, M, step):
             m = min(step, M - m0)
@@ -241,6 +252,14 @@ class _StepMixin:
 
     def _rowpar(self, W: LinearW, x, resid, out, M):
         """Row-parallel projection + all-reduce + residual add -> out."""
+        if self.tp > 1 and M > self.gemm_min_rows and W.wt == F.W_INT8:
+            # prefill under tensor parallelism: tcgen05 GEMM to a bf16 partial, NCCL all-reduce, residual add
+            part = torch.empty(M, W.N, dtype=BF16, device=self.dev)
+            self._gemm(W, x, part, M, epi=EPI_STORE)
+            self.comm.all_reduce(part)
+            torch.add(resid[:M], part, out=out[:M])
+            self._launches += 2
+            return
         if self.tp == 1 or self.peer is not None:
             self._gemv(W, x, out, M, xmode=XGLOBAL, epi=EPI_ROWPAR, resid=resid)
             return

@@ -74,6 +74,9 @@ _l.register("ti_ipc_close", _I, [_P])
 _l.register("ti_memset_async", _I, [_P, _I, ctypes.c_size_t, _P])
 _l.register("ti_wait_flag_probe", _I, [_P, ctypes.c_uint, ctypes.c_ulonglong, _P, _P, _P])
 
+_l.register("ti_quant_rows", _I, [_P, _I, _P, _F, _I, _I, _P, _P, _P, _P])
+_l.register("ti_gemm_w8a16", _I, [_P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _P, _P])
+
 _checked = False
 
 
@@ -314,3 +317,39 @@ def attn_paged(p: AttnParams, D: int):
 
 def topk(p: TopkParams):
     check(L().ti_topk(ctypes.byref(p), stream()), "ti_topk")
+
+
+# ------------------------------------------------------------------------------------ prefill GEMM (tcgen05)
+GEPI_STORE, GEPI_SWIGLU, GEPI_ROWPAR = 0, 1, 2
+
+
+class Limbs:
+    """Activation rows split into two int8 planes plus the per-row value of one fixed-point unit."""
+
+    def __init__(self, M: int, K: int, device):
+        self.M, self.K = M, K
+        self.hi = torch.empty(M, K, dtype=torch.int8, device=device)
+        self.lo = torch.empty(M, K, dtype=torch.uint8, device=device)
+        self.scale = torch.empty(M, dtype=torch.float32, device=device)
+
+
+def quant_rows(x: torch.Tensor, norm_w=None, eps: float = 1e-6, out: Limbs = None) -> Limbs:
+    """Limb planes of x [M, K] (bf16, row stride x.stride(0)); RMSNorm(1+w) fused when norm_w is given."""
+    M, K = x.shape
+    if out is None:
+        out = Limbs(M, K, x.device)
+    check(L().ti_quant_rows(ptr(x), x.stride(0), ptr(norm_w), eps, M, K, ptr(out.hi), ptr(out.lo), ptr(out.scale),
+                            stream()), "ti_quant_rows")
+    return out
+
+
+def gemm_w8a16(W: "LinearW", limbs: Limbs, *, out=None, epi=GEPI_STORE, resid=None) -> torch.Tensor:
+    """y = x W^T on the tcgen05 tensor cores for int8-tiled W and the limb planes of x (any M)."""
+    assert W.wt == W_INT8 and limbs.K == W.K
+    M = limbs.M
+    if out is None:
+        out = torch.empty(M, W.N // 2 if epi == GEPI_SWIGLU else W.N, dtype=torch.bfloat16, device=limbs.hi.device)
+    check(L().ti_gemm_w8a16(ptr(W.tiles), ptr(W.scale), W.n_tiles, W.N, W.K, ptr(limbs.hi), ptr(limbs.lo),
+                            ptr(limbs.scale), M, ptr(resid), ptr(out), out.stride(0), epi, status_ptr(), stream()),
+          "ti_gemm_w8a16")
+    return out
