@@ -16,9 +16,37 @@ def _unavailable(why: str) -> dict:
     return {"impl": "reference", "unavailable": why.replace("\n", " ")[:300]}
 
 
+def _sm90_dispatch_defect() -> str | None:
+    """The reference picks its warp-specialised prefill attention on compute capability >= 9.0 and calls
+    it with a `num_stages` keyword that the kernel factory does not accept (kernels/gqa_varlen.py:193-196
+    against :376-379), so every prefill raises TypeError there.  Seen on a B200 with the 8-layer
+    configuration; the reference was developed on sm_80, where the other branch runs.  The check reads the
+    installed source as text, so a reference without the defect is run normally."""
+    import re
+    try:
+        import torch
+        if not torch.cuda.is_available() or torch.cuda.get_device_capability(0) < (9, 0):
+            return None
+        src = open(os.path.join(REF, "kernels", "gqa_varlen.py")).read()
+    except OSError:
+        return None
+    sig = re.search(r"def flashattn_ws\((.*?)\):", src, re.S)
+    call = re.search(r"return flashattn_ws\((.*?)\)", src, re.S)
+    if sig and call and "num_stages" in call.group(1) and "num_stages" not in sig.group(1):
+        return ("the unmodified reference cannot prefill on sm_90+: kernels/gqa_varlen.py calls flashattn_ws(num_stages=3) "
+                "but flashattn_ws takes no num_stages (TypeError, observed on B200)")
+    return None
+
+
 def run(args) -> dict:
     if not os.path.isdir(os.path.join(REF, "engine")):
         return _unavailable("baseline/_ref is not installed")
+    import torch
+    if not torch.cuda.is_available():
+        return _unavailable("the reference needs a CUDA device")
+    why = _sm90_dispatch_defect()
+    if why is not None:
+        return _unavailable(why) if int(os.environ.get("RANK", "0")) == 0 else None
     rank = int(os.environ.get("RANK", "0"))
     preset = args.model.split(":", 1)[1] if ":" in args.model else args.model
     ckpt = os.path.join(os.environ.get("TI_REF_CKPT_DIR", "/tmp"), f"ti_ref_ckpt_{preset}")

@@ -40,7 +40,7 @@ def test_fused_tp_matches_oracle_and_all_ranks_agree(tp):
     ranks = res["ranks"]
     assert all(r["status"] == 0 for r in ranks), "a peer wait timed out"
     assert all(r["greedy"] == ranks[0]["greedy"] and r["sampled"] == ranks[0]["sampled"] for r in ranks)
-    assert ranks[0]["graph_launches"] > 0
+    assert ranks[0]["graph_launches"] > 0 and all(r["scrubs"] >= 2 for r in ranks)
     for p, o in zip(res["prompts"], ranks[0]["greedy"]):
         assert len(o) == 12
         _near_greedy(o, p)

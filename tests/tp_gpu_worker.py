@@ -23,11 +23,14 @@ def main():
     tp = int(os.environ["WORLD_SIZE"])
     llm = LLM("preset:tiny-hybrid-tp", quantization="w8a16", tp_size=tp, num_kvcache_blocks=128, max_num_seqs=8,
               max_model_len=512, max_prefill_chunk_tokens=32, fused_collectives=fused, nccl_timeout=120)
+    peer = llm.model_runner.model.peer
+    if peer is not None:
+        peer.SCRUB_PERIOD = 7          # exercise the periodic buffer scrub many times in this short run
     prompts = [prompt(21, 1), prompt(70, 2), prompt(5, 3)]
     greedy = llm.generate_token_ids(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
     sampled = llm.generate_token_ids(prompts[:2], SamplingParams(temperature=0.8, top_k=20, max_tokens=8, ignore_eos=True))
     status = llm.model_runner.model.peer_status()
-    mine = {"greedy": greedy, "sampled": sampled, "status": status,
+    mine = {"greedy": greedy, "sampled": sampled, "status": status, "scrubs": getattr(peer, "scrubs", 0),
             "graph_launches": llm.model_runner.model.launches_per_decode_step}
     box = [None] * tp
     dist.all_gather_object(box, mine)

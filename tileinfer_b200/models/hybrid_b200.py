@@ -274,6 +274,8 @@ class _StepMixin:
     def _run_layers(self, x: _Ctx):
         c, T, S = self.cfg, x.T, x.S
         eps = c.rms_eps
+        if self.peer is not None and not torch.cuda.is_current_stream_capturing():
+            self.peer.tick()
         F.embed(x.ids, self.embed, x.h[0], self.step_ptr)
         self._launches += 1
         self._order = 0
@@ -547,6 +549,8 @@ class _RunMixin:
         x.slots.copy_(h["slots"], non_blocking=True)
         x.block_tables.copy_(bt, non_blocking=True)
         x.qg.copy_(qg, non_blocking=True)
+        if self.peer is not None:
+            self.peer.tick()
         g.graph.replay()
         self.host_steps += 1
         return g.topk.out_val[:n], g.topk.out_idx[:n]

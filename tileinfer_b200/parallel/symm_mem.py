@@ -64,6 +64,29 @@ class PeerComm:
         self.comm.barrier()
         return ptrs
 
+    SCRUB_PERIOD = 1 << 15
+
+    def tick(self, steps: int = 1):
+        """Called once per forward (eager or graph replay), by every rank in lockstep.  A tag is
+        step * 65536 + position, so it recurs after 2^16 steps; a row of a packet buffer that was last
+        written exactly that long ago (a batch size not used since) could then be mistaken for fresh
+        data.  Every 2^15 steps all ranks therefore drain, zero their own buffers and meet again
+        before any of them sends the next packet."""
+        self._steps = getattr(self, "_steps", 0) + steps
+        if self.tp > 1 and self._steps >= self.SCRUB_PERIOD:
+            self._steps = 0
+            self.scrub()
+
+    def scrub(self):
+        lib = F.L()
+        torch.cuda.synchronize()
+        self.comm.barrier()                   # nobody is still sending into anybody's buffer
+        for ptr, n in zip(self._local, (self.ll_bytes, self.cand_bytes)):
+            F.check(lib.ti_memset_async(ctypes.c_void_p(ptr), 0, n, None), "ti_memset_async")
+        torch.cuda.synchronize()
+        self.comm.barrier()                   # nobody sends before every buffer is clean
+        self.scrubs = getattr(self, "scrubs", 0) + 1
+
     def status(self) -> int:
         """Error bits raised by kernels (1 = a peer wait timed out).  Synchronises."""
         return int(self.ctrl[1].item())
