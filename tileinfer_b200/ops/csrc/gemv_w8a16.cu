@@ -423,7 +423,12 @@ TI_DEVICE void stage_bf16_norm(const GemvParams& p, __nv_bfloat16* xs, int xs_st
 // statically (spread over the SMs first), the rest through one ticket counter per product, drawn one
 // unit ahead.  A per-warp queue in shared memory carries the unit sequence from the issuing side (lane 0
 // runs ahead with the copies) to the consuming side.
-TI_DEVICE int num_units(const GemvParams& p) { return (p.n_tiles + p.R - 1) / p.R; }
+// With S > 1 the k range of a row-tile group is cut into S slices of kb_per_split tiles: unit = group * S + slice.
+// The partial sums of a slice go to the workspace (fp32, [row tile][slice][128]); once the whole grid has passed
+// the product's barrier they are added in slice order (deterministic) and handed to the epilogue.  This is for
+// products with few rows (N = 5120: 640 row tiles for 2368 warps), where whole-k units would leave most warps,
+// and with them most of the bytes in flight, idle.
+TI_DEVICE int num_units(const GemvParams& p) { return ((p.n_tiles + p.R - 1) / p.R) * p.S; }
 #define TI_UNIT_END (-1)
 constexpr int kUnitMask = (1 << 26) - 1;
 TI_DEVICE int pack_unit(int op, int unit) { return (op << 26) | unit; }
@@ -441,7 +446,7 @@ struct WarpStream {           // registers of lane 0 of each warp; queue storage
   bool pre_valid, sdone, can_ticket, opened;
   // copy side
   int cs, idx, left, row_left, kb_row;
-  uint32_t ist;
+  uint32_t ist, skip;
   bool have, cdone;
   const uint8_t* gptr;
 
@@ -497,12 +502,15 @@ struct WarpStream {           // registers of lane 0 of each warp; queue storage
         continue;
       }
       const GemvParams& p = c.op[e >> 26];
-      // the R row tiles of a unit are adjacent in memory: one contiguous run of rn * KB tiles
-      const int rn = min(p.R, p.n_tiles - unit * p.R);
-      left = rn * p.KB;
-      row_left = p.KB;
-      kb_row = p.KB;
-      gptr = p.w + (size_t)unit * p.R * p.KB * 512;
+      // one run of tiles per row tile of the unit; with S == 1 the runs are adjacent in memory
+      const int grp = unit / p.S, sl = unit - grp * p.S;
+      const int kt0 = sl * p.kb_per_split, run = min(p.KB, kt0 + p.kb_per_split) - kt0;
+      const int rn = min(p.R, p.n_tiles - grp * p.R);
+      left = rn * run;
+      row_left = run;
+      kb_row = run;
+      skip = (uint32_t)(p.KB - run) * 512u;
+      gptr = p.w + ((size_t)grp * p.R * p.KB + kt0) * 512;
       have = true;
       return true;
     }
@@ -521,13 +529,35 @@ struct WarpStream {           // registers of lane 0 of each warp; queue storage
     gptr += bytes;
     left -= ntile;
     row_left -= ntile;
-    if (row_left == 0) row_left = kb_row;
+    if (row_left == 0) {
+      row_left = kb_row;
+      gptr += skip;
+    }
     if (left == 0) {
       have = false;
       ++cs;
     }
   }
 };
+
+// Adds the S slice partials of every row tile in slice order and runs the epilogue.  One thread per (row tile,
+// fragment lane); the whole grid takes part.  Called after a grid barrier that follows the product.
+TI_DEVICE void split_reduce(const GemvParams& p, int cta, int ncta) {
+  const int total = p.n_tiles * 32;
+  for (int i = cta * blockDim.x + threadIdx.x; i < total; i += ncta * blockDim.x) {
+    const int nt = i >> 5, lane = i & 31;
+    const float4* src = reinterpret_cast<const float4*>(p.ws + (size_t)nt * p.S * 128) + lane;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int sl = 0; sl < p.S; ++sl) {
+      const float4 v = __ldcg(src + sl * 32);
+      acc[0] += v.x;
+      acc[1] += v.y;
+      acc[2] += v.z;
+      acc[3] += v.w;
+    }
+    epilogue(p, nt, lane >> 2, lane & 3, acc);
+  }
+}
 
 // Grid-wide barrier between chained products.  All CTAs of the launch are resident (one per SM), the
 // counter is reset by the last CTA of the launch.  The wait is bounded like every other wait here.
@@ -576,7 +606,7 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
   ws.op = ws.pre = ws.sk = ws.wr = ws.rd = 0;
   ws.pre_valid = ws.sdone = ws.can_ticket = ws.opened = false;
   ws.cs = ws.idx = ws.left = ws.row_left = ws.kb_row = 0;
-  ws.ist = 0;
+  ws.ist = ws.skip = 0;
   ws.have = ws.cdone = false;
   ws.gptr = nullptr;
   if (lane == 0) {
@@ -595,7 +625,7 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
 
   unsigned cidx = 0;                            // chunks consumed by this warp so far
   uint32_t cst = 0, cpar = 0;                   // ring stage / mbarrier phase of the next chunk to consume
-  int cur_op = -1;
+  int cur_op = -1, nbar = 0;                    // nbar: grid barriers passed (the same sequence in every CTA)
   bool alive = true;
   float* scratch = reinterpret_cast<float*>(smem + x_bytes - 2048);
   float inv0 = 0.f, inv1 = 0.f;                 // value of one fixed-point unit for rows g and g+8
@@ -613,9 +643,14 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
       ++ws.rd;
     }
     e = __shfl_sync(0xffffffffu, e, 0);
-    if (e == TI_UNIT_END || (e & kUnitMask) == kUnitMask) {
+    if ((e == TI_UNIT_END || (e & kUnitMask) == kUnitMask) && cur_op >= 0) {
+      const GemvParams& pp = c.op[cur_op];
+      if (pp.S > 1) {                             // every slice partial is in the workspace after this barrier
+        grid_barrier(p0.sched + 2, ++nbar * ncta, p0.status);
+        split_reduce(pp, cta, ncta);
+      }
       // this warp has sent everything it owns of the previous product: collect the all-reduce
-      if (cur_op >= 0 && c.op[cur_op].epi == EPI_ROWPAR && c.op[cur_op].tp > 1) rowpar_reduce(c.op[cur_op], cta, ncta);
+      if (pp.epi == EPI_ROWPAR && pp.tp > 1) rowpar_reduce(pp, cta, ncta);
     }
     if (e == TI_UNIT_END) break;
     const int op = e >> 26, unit = e & kUnitMask;
@@ -623,7 +658,7 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
     if (unit == kUnitMask) {
       cur_op = op;
       // ---- product boundary: every warp of every CTA is done with the previous product
-      if (op > 0) grid_barrier(p0.sched + 2, op * ncta, p0.status);
+      if (op > 0) grid_barrier(p0.sched + 2, ++nbar * ncta, p0.status);
       else __syncthreads();
       lstride = limb_stride(p.K);
       xl = smem + (size_t)p.M * lstride;
@@ -640,7 +675,9 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
       for (int s = ws.idx - (int)cidx; s < stages; ++s) ws.next(c, widx, W, q, ring_u32, bar0, stages);
 
     const bool hi = p.M > 8;
-    const int rn = min(p.R, p.n_tiles - unit * p.R);
+    const int grp = unit / p.S, sl = unit - grp * p.S;
+    const int kt0 = sl * p.kb_per_split, kt1 = min(p.KB, kt0 + p.kb_per_split);
+    const int rn = min(p.R, p.n_tiles - grp * p.R);
     // rows of the staged activations this lane feeds to the MMA (rows >= M are clamped: their results
     // are never written)
     const uint32_t xrow0 = (uint32_t)min(g, p.M - 1), xrow1 = (uint32_t)min(g + 8, p.M - 1);
@@ -654,8 +691,8 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
       for (int a = 0; a < 2; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) ah[a][b] = al[a][b] = 0;
-      for (int tile0 = 0; tile0 < p.KB; tile0 += kTPS) {
-        const int ntile = min(kTPS, p.KB - tile0);
+      for (int tile0 = kt0; tile0 < kt1; tile0 += kTPS) {
+        const int ntile = min(kTPS, kt1 - tile0);
         if (alive) alive = mbar_wait(bar0 + cst * 8, cpar, 2000000000ull, p.status);
         const uint32_t sbuf = ring_u32 + cst * (kTPS * 512u) + lane * 16;
         if (WT == W_INT8) {
@@ -716,7 +753,10 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
         for (int b = 0; b < 4; ++b)
           acc[b] = ((float)(ah[0][b] + ah[1][b]) * 256.f + (float)(al[0][b] + al[1][b])) * (b < 2 ? inv0 : inv1);
       }
-      epilogue(p, unit * p.R + r, g, t, acc);
+      if (p.S > 1)
+        reinterpret_cast<float4*>(p.ws + ((size_t)(grp * p.R + r) * p.S + sl) * 128)[lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      else
+        epilogue(p, grp * p.R + r, g, t, acc);
     }
     if (stamp) p0.dbg[cta * 8 + 4] = globaltimer_ns();
   }
@@ -761,6 +801,10 @@ static int check(const GemvParams& p, int wt) {
   const int tk = wt == W_INT8 ? 64 : 32;
   if (p.M < 1 || p.M > 16 || p.N < 2 || (p.N & 1) || p.K % tk || p.KB * tk != p.K) return -2;
   if (p.R < 1 || p.R > kMaxR || p.n_tiles < 1 || p.n_tiles >= (1 << 26)) return -3;
+  if (p.S < 1 || p.kb_per_split < 1 || (long long)(p.S - 1) * p.kb_per_split >= p.KB ||
+      (long long)p.S * p.kb_per_split < p.KB || (p.S > 1 && p.ws == nullptr))
+    return -6;
+  if ((long long)((p.n_tiles + p.R - 1) / p.R) * p.S >= kUnitMask) return -3;
   if (p.tps != kTPS) return -7;
   if (p.sched == nullptr || p.stages < 1 || p.stages > 8) return -7;
   if (p.xmode < 0 || p.xmode > 1 || p.epi < 0 || p.epi > 3) return -8;

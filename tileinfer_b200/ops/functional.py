@@ -158,6 +158,20 @@ def plan_gemv(wt: int, xmode: int, M: int, n_tiles: int, KB: int, ncta: int = NU
     return None
 
 
+def plan_split(n_tiles: int, KB: int, R: int, split: int | None = None, ncta: int = NUM_SMS):
+    """(S, kb_per_split): cuts the k range of a product into S slices (multiples of 8 tiles, one ring stage) whose
+    partial sums meet in the workspace after a grid barrier.  Off by default (S = 1, whole-k units): on B200 the
+    extra barrier and the reduction pass cost more (about 10 us) than the idle warps of a 640-row-tile product;
+    `split` (or TI_GEMV_S) asks for about that many slices."""
+    if split is None:
+        split = int(os.environ.get("TI_GEMV_S", "1"))
+    if split <= 1 or KB < 16:
+        return 1, KB
+    kbps = min(KB, max(8, -(-KB // split) // 8 * 8))
+    S = -(-KB // kbps)
+    return (S, kbps) if S > 1 else (1, KB)
+
+
 def max_rows(wt: int, xmode: int, K: int) -> int:
     """Largest row count (<= 16) one launch can take for this K."""
     tk = 64 if wt == W_INT8 else 32
@@ -199,7 +213,7 @@ def default_workspace():
 
 
 def make_gemv_params(W: LinearW, x, out, M, *, xmode=XGLOBAL, epi=EPI_STORE, norm_w=None, resid=None, ws=None,
-                     eps=1e-6, ldx=None, ldo=None, comm=None, order=0, ncta=NUM_SMS) -> GemvParams:
+                     eps=1e-6, ldx=None, ldo=None, comm=None, order=0, ncta=NUM_SMS, split=None) -> GemvParams:
     p = GemvParams()
     p.w, p.scale, p.x, p.norm_w = ptr(W.tiles), ptr(W.scale), ptr(x), ptr(norm_w)
     p.out, p.resid = ptr(out), ptr(resid)
@@ -209,7 +223,11 @@ def make_gemv_params(W: LinearW, x, out, M, *, xmode=XGLOBAL, epi=EPI_STORE, nor
     R, tps, stages = plan
     if ws is None:
         ws = default_workspace()
-    p.M, p.N, p.n_tiles, p.K, p.KB, p.S, p.kb_per_split = M, W.N, W.n_tiles, W.K, W.KB, 1, W.KB
+    S, kbps = plan_split(W.n_tiles, W.KB, R, split, ncta)
+    if S > 1 and W.n_tiles * S > ws.max_units:
+        S, kbps = 1, W.KB
+    p.M, p.N, p.n_tiles, p.K, p.KB, p.S, p.kb_per_split = M, W.N, W.n_tiles, W.K, W.KB, S, kbps
+    p.ws = ptr(ws.ws)
     p.ldx = ldx if ldx is not None else (x.stride(0) if x.dim() > 1 else W.K)
     p.ldo = ldo if ldo is not None else (out.stride(0) if out.dim() > 1 else W.N)
     p.eps = eps
@@ -255,7 +273,7 @@ def gemv_launch(p: GemvParams, wt: int, xmode: int = None, epi: int = None, ncta
 
 
 def gemv(W: LinearW, x: torch.Tensor, *, out=None, xmode=XGLOBAL, epi=EPI_STORE, norm_w=None, resid=None, ws=None,
-         eps=1e-6, comm=None, order=0) -> torch.Tensor:
+         eps=1e-6, comm=None, order=0, split=None) -> torch.Tensor:
     """Convenience form (allocates `out`); loops over row chunks that fit in shared memory."""
     M = x.shape[0]
     step = max_rows(W.wt, xmode, W.K)
@@ -267,7 +285,7 @@ def gemv(W: LinearW, x: torch.Tensor, *, out=None, xmode=XGLOBAL, epi=EPI_STORE,
         m = min(step, M - m0)
         p = make_gemv_params(W, x[m0:m0 + m], out[m0:m0 + m], m, xmode=xmode, epi=epi, norm_w=norm_w,
                              resid=None if resid is None else resid[m0:m0 + m], ws=ws, eps=eps,
-                             ldx=x.stride(0), ldo=out.stride(0), comm=comm, order=order)
+                             ldx=x.stride(0), ldo=out.stride(0), comm=comm, order=order, split=split)
         gemv_launch(p, W.wt, xmode, epi)
     return out
 
