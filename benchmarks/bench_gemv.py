@@ -2,7 +2,10 @@
 timeline (globaltimer stamps written by the kernel).  Weights are rotated over several copies so
 that every launch streams from HBM, not from the 126 MB L2.
 
-    python benchmarks/bench_gemv.py [--timeline]
+    python benchmarks/bench_gemv.py [--timeline] [--chain]
+
+--chain times the four dependent products of a decoder layer (out_proj -> gate_up+SwiGLU -> down -> next
+in_proj, 27B shapes) in ONE launch, as the decode step runs them.
 """
 import argparse
 import os
@@ -25,13 +28,76 @@ SHAPES = {   # name: (N, K, xmode, epi)
 }
 
 
+def _print_timeline(dbg, n_ops):
+    t = dbg.view(148, 32).cpu().double()
+    t0 = t[:, 0].min()
+
+    def row(nm, j):
+        c = (t[:, j] - t0) / 1e3
+        print(f"      {nm:22s} min {c.min():7.2f}  mean {c.mean():7.2f}  max {c.max():7.2f} us")
+    row("start", 0)
+    row("ring primed", 1)
+    for op in range(n_ops):
+        for k, nm in enumerate(("marker reached", "barrier passed", "x staged", "last unit done")):
+            row(f"op{op} {nm}", 8 + 4 * op + k)
+    row("end", 5)
+
+
+def bench_chain(args):
+    """One launch = out_proj, gate_up, down, in_proj of the 27B layer; weights rotate over copies > L2."""
+    M, H, I, KO, NI = args.M, 5120, 17408, 6144, 16480
+    ws = F.GemvWorkspace()
+    ncopy = 3
+    mk = lambda n, k: F.LinearW(torch.randn(n, k, device="cuda") * 0.05, True)
+    sets = [(mk(H, KO), mk(2 * I, H), mk(H, I), mk(NI, H)) for _ in range(ncopy)]
+    x = torch.randn(M, KO, device="cuda").to(torch.bfloat16)
+    h0 = torch.randn(M, H, device="cuda").to(torch.bfloat16)
+    h1, h2 = torch.zeros_like(h0), torch.zeros_like(h0)
+    act = torch.zeros(M, I, dtype=torch.bfloat16, device="cuda")
+    proj = torch.zeros(M, NI, dtype=torch.bfloat16, device="cuda")
+    nw = torch.zeros(H, dtype=torch.bfloat16, device="cuda")
+    dbg = torch.zeros(148 * 32, dtype=torch.int64, device="cuda")
+    chains = []
+    for Wo, Wgu, Wd, Wi in sets:
+        ps = [F.make_gemv_params(Wo, x, h1, M, xmode=F.XGLOBAL, epi=F.EPI_ROWPAR, resid=h0, ws=ws),
+              F.make_gemv_params(Wgu, h1, act, M, xmode=F.XNORM, epi=F.EPI_SWIGLU, norm_w=nw, ws=ws),
+              F.make_gemv_params(Wd, act, h2, M, xmode=F.XGLOBAL, epi=F.EPI_ROWPAR, resid=h1, ws=ws),
+              F.make_gemv_params(Wi, h2, proj, M, xmode=F.XNORM, epi=F.EPI_STORE, norm_w=nw, ws=ws)]
+        if args.timeline:
+            ps[0].dbg = dbg.data_ptr()
+        chains.append(ps)
+    for i in range(4):
+        F.gemv_chain_launch(chains[i % ncopy], F.W_INT8)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(args.iters):
+            F.gemv_chain_launch(chains[i % ncopy], F.W_INT8)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.iters
+    nbytes = sum(W.nbytes() for W in sets[0])
+    print(f"chain of 4 (27B layer) M={M} stages={chains[0][0].stages}: {us:7.2f} us  {nbytes / us / 1e3:7.1f} GB/s "
+          f"({nbytes / 1e6:.0f} MB)")
+    if args.timeline:
+        _print_timeline(dbg, 4)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--timeline", action="store_true")
+    ap.add_argument("--chain", action="store_true")
     ap.add_argument("--M", type=int, default=1)
     ap.add_argument("--iters", type=int, default=40)
     args = ap.parse_args()
     M = args.M
+    if args.chain:
+        return bench_chain(args)
     ws = F.GemvWorkspace()
     for name, (N, K, xmode, epi) in SHAPES.items():
         ncopy = max(2, int(400e6 // (N * K)) + 1)
@@ -40,7 +106,7 @@ def main():
         nw = torch.zeros(K, dtype=torch.bfloat16, device="cuda")
         resid = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
         out = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
-        dbg = torch.zeros(148 * 8, dtype=torch.int64, device="cuda")
+        dbg = torch.zeros(148 * 32, dtype=torch.int64, device="cuda")
         ps = []
         for W in Ws:
             p = F.make_gemv_params(W, x, out, M, xmode=xmode, epi=epi, norm_w=nw, resid=resid, ws=ws)
@@ -66,12 +132,7 @@ def main():
         print(f"{name:10s} N={N:6d} K={K:6d} M={M} R={p0.R} tps={p0.tps} stages={p0.stages} "
               f"{us:7.2f} us  {N * K / us / 1e3:7.1f} GB/s")
         if args.timeline:
-            t = dbg.view(148, 8).cpu().double()
-            t0 = t[:, 0].min()
-            names = ["start", "ring primed", "x staged", "first chunk", "last unit", "end"]
-            for j, nm in enumerate(names):
-                c = (t[:, j] - t0) / 1e3
-                print(f"      {nm:12s} min {c.min():7.2f}  mean {c.mean():7.2f}  max {c.max():7.2f} us")
+            _print_timeline(dbg, 1)
 
 
 if __name__ == "__main__":

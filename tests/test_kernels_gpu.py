@@ -36,10 +36,11 @@ def test_gemv_store(M, N, K, quant):
     assert int(ws.counters.abs().sum()) == 0
     y2 = F.gemv(W, x, ws=ws)
     assert torch.equal(y, y2), "deterministic across launches"
-    # k range cut into slices whose partial sums meet in the workspace
-    y3 = F.gemv(W, x, ws=ws, split=3)
-    torch.testing.assert_close(y3.float(), ref, rtol=2e-2, atol=2e-2)
-    assert torch.equal(y3, F.gemv(W, x, ws=ws, split=3))
+    # team mode: the warps of a team share a unit, each a slice of k; partial sums meet in shared memory
+    for team in (1, 4, 16):
+        y3 = F.gemv(W, x, ws=ws, team=team)
+        torch.testing.assert_close(y3.float(), ref, rtol=2e-2, atol=2e-2)
+        assert torch.equal(y3, F.gemv(W, x, ws=ws, team=team))
 
 
 @pytest.mark.parametrize("M", [1, 5, 16])
@@ -101,7 +102,7 @@ def test_gemv_rowpar_allreduce_emulated_ranks(tp, Kfull):
     from tileinfer_b200.ops.lib import ChainParams
     from tileinfer_b200.parallel.symm_mem import LocalRanks
     N, M = 5120, 3
-    K = Kfull // tp                       # Kfull = 8192: the k range is also cut into slices (S > 1)
+    K = Kfull // tp                       # Kfull = 8192: team mode (four warps share a unit)
     wfull = _rand_w(N, Kfull, seed=7)
     x = (torch.randn(M, Kfull, device="cuda")).to(BF16)
     resid = (torch.randn(M, N, device="cuda")).to(BF16)
@@ -114,8 +115,8 @@ def test_gemv_rowpar_allreduce_emulated_ranks(tp, Kfull):
         out = torch.zeros(M, N, dtype=BF16, device="cuda")
         ws = F.GemvWorkspace()
         p = F.make_gemv_params(W, xr, out, M, epi=F.EPI_ROWPAR, resid=resid, ws=ws, comm=ranks.view(r), order=0, ncta=ncta,
-                               split=4 if Kfull == 8192 else None)
-        assert (p.S > 1) == (Kfull == 8192)
+                               team=4 if Kfull == 8192 else 1)
+        assert p.T == (4 if Kfull == 8192 else 1)
         Ws.append(W); outs.append(out); params.append(p); keep.append((xr, ws))
     size = ctypes.sizeof(ChainParams)
     chains = [F.make_chain([p]) for p in params]
@@ -157,8 +158,8 @@ def test_gemv_chain_of_four_matches_separate_launches(quant, M, H):
         act = torch.zeros(M, I, dtype=BF16, device="cuda")
         proj = torch.zeros(M, NI, dtype=BF16, device="cuda")
         ps = [F.make_gemv_params(Wo, x, h1, M, xmode=F.XGLOBAL, epi=F.EPI_ROWPAR, resid=h0, ws=ws),
-              F.make_gemv_params(Wgu, h1, act, M, xmode=F.XNORM, epi=F.EPI_SWIGLU, norm_w=n1, ws=ws, split=2),
-              F.make_gemv_params(Wd, act, h2, M, xmode=F.XGLOBAL, epi=F.EPI_ROWPAR, resid=h1, ws=ws, split=2),
+              F.make_gemv_params(Wgu, h1, act, M, xmode=F.XNORM, epi=F.EPI_SWIGLU, norm_w=n1, ws=ws, team=2),
+              F.make_gemv_params(Wd, act, h2, M, xmode=F.XGLOBAL, epi=F.EPI_ROWPAR, resid=h1, ws=ws, team=2),
               F.make_gemv_params(Wi, h2, proj, M, xmode=F.XNORM, epi=F.EPI_STORE, norm_w=n2, ws=ws)]
         if chained:
             F.gemv_chain_launch(ps, wt)

@@ -261,34 +261,53 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ AttnP
   }
 }
 
-// Combines the split-KV partials of one (query group, kv head), normalises, applies the sigmoid
-// output gate and writes bf16 [T, hq*D].
+// Combines the split-KV partials of one (query group, kv head, row), normalises, applies the sigmoid
+// output gate and writes bf16 [T, hq*D].  One block per row: the split weights are worked out once in
+// shared memory, then every thread owns two adjacent output dims and sums the partials with independent
+// (unrolled) loads, so the kernel costs a few dependent memory round trips whatever the split count.
+constexpr int kMaxSplit = 64;
 template <int D>
-__global__ void __launch_bounds__(128) attn_merge_kernel(const __grid_constant__ AttnParams p) {
-  const int qg = blockIdx.x, kh = blockIdx.y;
+__global__ void __launch_bounds__(D / 2) attn_merge_kernel(const __grid_constant__ AttnParams p) {
+  __shared__ float w_s[kMaxSplit], wl_s[kMaxSplit];
+  const int qg = blockIdx.x, kh = blockIdx.y, r = blockIdx.z, tid = threadIdx.x;
   pdl_trigger();
   pdl_wait();
   const PageRange pr = page_range(p, qg);
-  if (pr.ntok == 0) return;
-  const int nact = (pr.npages + pr.pps - 1) / pr.pps;
   const int G = p.hq / p.hkv;
+  if (pr.ntok == 0 || r >= pr.ntok * G) return;
+  const int nact = (pr.npages + pr.pps - 1) / pr.pps;
   const size_t item0 = ((size_t)qg * p.hkv + kh) * p.nsplit;
-  const int rows = pr.ntok * G;
-  for (int idx = threadIdx.x; idx < rows * D; idx += 128) {
-    const int r = idx / D, d = idx - r * D;
-    float M = kNegBig;
-    for (int s = 0; s < nact; ++s) M = fmaxf(M, p.ml_part[((item0 + s) * 16 + r) * 2]);
-    float acc = 0.f, L = 0.f;
-    for (int s = 0; s < nact; ++s) {
-      const float w = exp2f(p.ml_part[((item0 + s) * 16 + r) * 2] - M);
-      acc += w * p.o_part[((item0 + s) * 16 + r) * D + d];
-      L += w * p.ml_part[((item0 + s) * 16 + r) * 2 + 1];
-    }
-    const int tk = r / G, hg = r - tk * G;
-    const int tok = pr.tok0 + tk, head = kh * G + hg;
-    const float gate = __bfloat162float(p.gate_src[(size_t)tok * p.ld + (size_t)head * 2 * D + D + d]);
-    p.out[(size_t)tok * p.hq * D + (size_t)head * D + d] = __float2bfloat16_rn(acc / L * sigmoid_f(gate));
+  for (int s = tid; s < nact; s += D / 2) {
+    const float2 ml = *reinterpret_cast<const float2*>(p.ml_part + ((item0 + s) * 16 + r) * 2);
+    w_s[s] = ml.x;
+    wl_s[s] = ml.y;
   }
+  __syncthreads();
+  float M = kNegBig;
+  for (int s = 0; s < nact; ++s) M = fmaxf(M, w_s[s]);
+  __syncthreads();
+  for (int s = tid; s < nact; s += D / 2) {
+    const float w = exp2f(w_s[s] - M);
+    w_s[s] = w;
+    wl_s[s] *= w;
+  }
+  __syncthreads();
+  const int d = tid * 2;
+  float a0 = 0.f, a1 = 0.f, L = 0.f;
+  const float* src = p.o_part + (item0 * 16 + r) * D + d;
+#pragma unroll 8
+  for (int s = 0; s < nact; ++s) {
+    const float2 o = *reinterpret_cast<const float2*>(src + (size_t)s * 16 * D);
+    a0 += w_s[s] * o.x;
+    a1 += w_s[s] * o.y;
+    L += wl_s[s];
+  }
+  const int tk = r / G, hg = r - tk * G;
+  const int tok = pr.tok0 + tk, head = kh * G + hg;
+  const uint32_t gw = *reinterpret_cast<const uint32_t*>(p.gate_src + (size_t)tok * p.ld + (size_t)head * 2 * D + D + d);
+  const float inv = 1.f / L;
+  *reinterpret_cast<uint32_t*>(p.out + (size_t)tok * p.hq * D + (size_t)head * D + d) =
+      pack_bf16(a0 * inv * sigmoid_f(bf16lo(gw)), a1 * inv * sigmoid_f(bf16hi(gw)));
 }
 
 }  // namespace ti
@@ -314,18 +333,18 @@ int ti_qkv_prep(const ti::QkvPrepParams* p, int T, int D, void* stream) {
 int ti_attn_paged(const ti::AttnParams* p, int D, void* stream) {
   if (p->num_qg <= 0) return 0;
   const int G = p->hq / p->hkv;
-  if (p->hq % p->hkv || G > 16 || p->nsplit < 1) return -2;
-  dim3 grid(p->num_qg, p->hkv, p->nsplit), mgrid(p->num_qg, p->hkv);
+  if (p->hq % p->hkv || G > 16 || p->nsplit < 1 || p->nsplit > ti::kMaxSplit) return -2;
+  dim3 grid(p->num_qg, p->hkv, p->nsplit), mgrid(p->num_qg, p->hkv, 16);
   cudaStream_t st = (cudaStream_t)stream;
   if (D == 256) {
     ti::launch_kernel(ti::attn_kernel<256, 2>, grid, dim3(128), 0, st, true, *p);
     ti::launch_kernel(ti::attn_merge_kernel<256>, mgrid, dim3(128), 0, st, true, *p);
   } else if (D == 128) {
     ti::launch_kernel(ti::attn_kernel<128, 1>, grid, dim3(128), 0, st, true, *p);
-    ti::launch_kernel(ti::attn_merge_kernel<128>, mgrid, dim3(128), 0, st, true, *p);
+    ti::launch_kernel(ti::attn_merge_kernel<128>, mgrid, dim3(64), 0, st, true, *p);
   } else if (D == 64) {
     ti::launch_kernel(ti::attn_kernel<64, 1>, grid, dim3(128), 0, st, true, *p);
-    ti::launch_kernel(ti::attn_merge_kernel<64>, mgrid, dim3(128), 0, st, true, *p);
+    ti::launch_kernel(ti::attn_merge_kernel<64>, mgrid, dim3(32), 0, st, true, *p);
   } else {
     return -3;
   }

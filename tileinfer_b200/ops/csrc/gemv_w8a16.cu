@@ -51,8 +51,9 @@ struct GemvParams {
   int tp, rank, order, m_cap;
   float eps;
   int stages;                    // depth of the per-warp weight ring (1..8)
-  int J;                         // k-slices a CTA group owns (S % J == 0): CTA c stages slice c % J of x
-  unsigned long long* dbg;       // optional [ncta][8] globaltimer stamps of warp 0 (profiling aid)
+  int T;                         // team size (1, 2, 4, 8 or 16 warps of a CTA share a unit, each a k-slice)
+  unsigned long long* dbg;       // optional [ncta][32] globaltimer stamps of warp 0 (profiling aid): 0 start, 1 ring
+                                 // primed, 5 end; per product op at 8 + 4*op: marker reached, barrier passed, x staged, last unit done
   int* sched;                    // dynamic scheduling state: [0] launches finished, [1] CTAs finished, [8 + 3*16] tickets
   int tps;                       // 512-byte tiles per ring stage (4, 8 or 16)
   int xmode, epi;                // XGLOBAL | XNORM ; EPI_*
@@ -91,17 +92,36 @@ constexpr int kTPS = 8;                    // 512-byte tiles per ring stage (4 K
 constexpr int kMaxTilesPerStage = 16;
 constexpr int kWarps = kThreads / 32;
 constexpr int kCQ = 16;                    // per-warp queue of scheduled units
-constexpr int kLook = 6;                   // entries a warp keeps queued ahead of its consumer side
+constexpr int kLook = 1;                   // entries a warp queues ahead of its consumer side.  Kept small on purpose: a warp
+                                           // that draws tickets far ahead (or one ticket in advance) hoards units of a product
+                                           // while it is still idle or busy elsewhere, and the product then ends on the few
+                                           // warps that hold three or four units each
 constexpr int kMaxR = 4;                   // row tiles per unit
+constexpr int kTeamBytes = 2 * kWarps * 32 * 16;   // team-mode exchange buffer
 
-TI_DEVICE void epilogue(const GemvParams& p, int nt, int g, int t, const float (&acc)[4]) {
+// Operands of the epilogue that do not depend on the product: fetched when a warp STARTS a row tile, so that
+// their latency (an L2 round trip for the residual) is not paid after the last tile, where in team mode the whole
+// team would wait for it.
+struct EpiPre { float s0, s1; uint32_t r0, r1; };
+TI_DEVICE EpiPre epi_prefetch(const GemvParams& p, int nt, int g, int t) {
+  EpiPre e{1.f, 1.f, 0u, 0u};
+  const int n = nt * 8 + 2 * t;
+  if (n >= p.N) return e;
+  if (p.scale != nullptr) {
+    e.s0 = bf16_to_f(p.scale[n]);
+    e.s1 = bf16_to_f(p.scale[n + 1]);
+  }
+  if (p.epi == EPI_ROWPAR && p.tp == 1) {
+    if (g < p.M) e.r0 = __ldcg(reinterpret_cast<const uint32_t*>(p.resid + (size_t)g * p.N + n));
+    if (g + 8 < p.M) e.r1 = __ldcg(reinterpret_cast<const uint32_t*>(p.resid + (size_t)(g + 8) * p.N + n));
+  }
+  return e;
+}
+
+TI_DEVICE void epilogue(const GemvParams& p, int nt, int g, int t, const float (&acc)[4], const EpiPre& pre) {
   const int n = nt * 8 + 2 * t;
   if (n >= p.N) return;
-  float s0 = 1.f, s1 = 1.f;
-  if (p.scale != nullptr) {
-    s0 = bf16_to_f(p.scale[n]);
-    s1 = bf16_to_f(p.scale[n + 1]);
-  }
+  const float s0 = pre.s0, s1 = pre.s1;
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const int m = g + half * 8;
@@ -128,7 +148,7 @@ TI_DEVICE void epilogue(const GemvParams& p, int nt, int g, int t, const float (
         const size_t mine = ((((size_t)slot * p.tp + p.rank) * p.m_cap + m) * (size_t)(p.N >> 1) + (n >> 1)) * 16;
         for (int q = 0; q < p.tp; ++q) ll_store2(reinterpret_cast<uint8_t*>(p.peer_ll[q]) + mine, v0, v1, tag);
       } else {
-        const uint32_t rw = __ldcg(reinterpret_cast<const uint32_t*>(p.resid + (size_t)m * p.N + n));
+        const uint32_t rw = half ? pre.r1 : pre.r0;
         uint32_t* o = reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.N + n);
         *o = pack_bf16(bf16lo(rw) + v0, bf16hi(rw) + v1);
       }
@@ -420,15 +440,21 @@ TI_DEVICE void stage_bf16_norm(const GemvParams& p, __nv_bfloat16* xs, int xs_st
 // unit through a private ring of shared memory filled by TMA bulk copies (the tiles of a row tile are
 // contiguous), deep enough to cover HBM latency at that warp's share of the bandwidth, and keeps
 // streaming across units and across the products of a chain.  Units are dealt to warps: the first ones
-// statically (spread over the SMs first), the rest through one ticket counter per product, drawn one
-// unit ahead.  A per-warp queue in shared memory carries the unit sequence from the issuing side (lane 0
+// statically (spread over the SMs first), the rest through one ticket counter per product, drawn when
+// the copy side runs out of work.  A per-warp queue in shared memory carries the unit sequence from the issuing side (lane 0
 // runs ahead with the copies) to the consuming side.
-// With S > 1 the k range of a row-tile group is cut into S slices of kb_per_split tiles: unit = group * S + slice.
-// The partial sums of a slice go to the workspace (fp32, [row tile][slice][128]); once the whole grid has passed
-// the product's barrier they are added in slice order (deterministic) and handed to the epilogue.  This is for
-// products with few rows (N = 5120: 640 row tiles for 2368 warps), where whole-k units would leave most warps,
-// and with them most of the bytes in flight, idle.
-TI_DEVICE int num_units(const GemvParams& p) { return ((p.n_tiles + p.R - 1) / p.R) * p.S; }
+// Products with few row tiles (N = 5120: 640 row tiles for 2368 warps) would leave most warps, and with them
+// most of the bytes in flight, idle.  They run in team mode instead (T > 1): the T warps of a team (same CTA,
+// adjacent warp ids) share a unit, each streams its own slice of the k range, the partial sums meet in shared
+// memory behind a named barrier and the first warp of the team adds them in slice order and runs the epilogue.
+// Team units are dealt statically, unit u to team u mod (number of teams).
+TI_DEVICE int num_units(const GemvParams& p) { return (p.n_tiles + p.R - 1) / p.R; }
+// k-slice [kt0, kt0 + run) of team member j
+TI_DEVICE void team_slice(const GemvParams& p, int j, int& kt0, int& run) {
+  const int base = p.KB / p.T, rem = p.KB - base * p.T;
+  kt0 = j * base + min(j, rem);
+  run = base + (j < rem ? 1 : 0);
+}
 #define TI_UNIT_END (-1)
 constexpr int kUnitMask = (1 << 26) - 1;
 TI_DEVICE int pack_unit(int op, int unit) { return (op << 26) | unit; }
@@ -442,8 +468,8 @@ TI_DEVICE int num_static(const GemvParams& p, int W) { return max(1, num_units(p
 
 struct WarpStream {           // registers of lane 0 of each warp; queue storage in shared memory
   // scheduling side
-  int op, pre, sk, wr, rd;
-  bool pre_valid, sdone, can_ticket, opened;
+  int op, sk, wr, rd;
+  bool sdone, can_ticket, opened;
   // copy side
   int cs, idx, left, row_left, kb_row;
   uint32_t ist, skip;
@@ -453,37 +479,40 @@ struct WarpStream {           // registers of lane 0 of each warp; queue storage
   TI_DEVICE void push(volatile int* q, int e) { q[wr++ % kCQ] = e; }
   // queue the next entries of this warp's unit sequence, at most up to `ahead` entries beyond `rd`
   TI_DEVICE void schedule(const ChainParams& c, int widx, int W, volatile int* q, int ahead) {
-    while (!sdone && wr - rd < ahead) {
+    while (!sdone && wr - rd < kCQ - 2) {
       const GemvParams& p = c.op[op];
-      const int U = num_units(p), ns = num_static(p, W);
+      const int U = num_units(p);
+      // team mode: the "worker" is the team, and every unit is static
+      const int ncta = W / kWarps;
+      const int Wd = p.T > 1 ? W / p.T : W;
+      const int wd = p.T > 1 ? (widx / ncta / p.T) * ncta + widx % ncta : widx;
+      const int ns = p.T > 1 ? (U + Wd - 1) / Wd : num_static(p, W);
       if (!opened) {
         opened = true;
         push(q, pack_begin(op));
         continue;
       }
       if (sk < ns) {
-        const int u = sk * W + widx;
+        // static units take from nobody: they may be queued further ahead than tickets (matters for the small
+        // units of team mode, where the ring holds more than one unit)
+        const int u = sk * Wd + wd;
         ++sk;
         if (u < U) push(q, pack_unit(op, u));
         continue;
       }
-      if (!can_ticket) return;
-      int* ticket = p.sched + 8 + op * 16;
-      if (!pre_valid) {
-        pre = atomicAdd(ticket, 1);
-        pre_valid = true;
-      }
-      const int u = ns * W + pre;
+      if (!can_ticket || wr - rd >= ahead) return;
+      // drawn only when the copy side has handed the whole previous unit to the TMA engine: the consumer side
+      // is then still a ring's depth of chunks behind, which covers the latency of the atomic
+      const int u = p.T > 1 ? U : ns * W + atomicAdd(p.sched + 8 + op * 16, 1);
       if (u >= U) {
         sk = 0;
-        pre_valid = opened = false;
+        opened = false;
         if (++op >= c.n_ops) {
           push(q, TI_UNIT_END);
           sdone = true;
         }
         continue;
       }
-      pre = atomicAdd(ticket, 1);          // next ticket, used one unit from now
       push(q, pack_unit(op, u));
     }
   }
@@ -502,9 +531,10 @@ struct WarpStream {           // registers of lane 0 of each warp; queue storage
         continue;
       }
       const GemvParams& p = c.op[e >> 26];
-      // one run of tiles per row tile of the unit; with S == 1 the runs are adjacent in memory
-      const int grp = unit / p.S, sl = unit - grp * p.S;
-      const int kt0 = sl * p.kb_per_split, run = min(p.KB, kt0 + p.kb_per_split) - kt0;
+      // one run of tiles per row tile of the unit; outside team mode the runs are adjacent in memory
+      const int grp = unit;
+      int kt0 = 0, run = p.KB;
+      if (p.T > 1) team_slice(p, (widx / (W / kWarps)) % p.T, kt0, run);
       const int rn = min(p.R, p.n_tiles - grp * p.R);
       left = rn * run;
       row_left = run;
@@ -540,25 +570,6 @@ struct WarpStream {           // registers of lane 0 of each warp; queue storage
   }
 };
 
-// Adds the S slice partials of every row tile in slice order and runs the epilogue.  One thread per (row tile,
-// fragment lane); the whole grid takes part.  Called after a grid barrier that follows the product.
-TI_DEVICE void split_reduce(const GemvParams& p, int cta, int ncta) {
-  const int total = p.n_tiles * 32;
-  for (int i = cta * blockDim.x + threadIdx.x; i < total; i += ncta * blockDim.x) {
-    const int nt = i >> 5, lane = i & 31;
-    const float4* src = reinterpret_cast<const float4*>(p.ws + (size_t)nt * p.S * 128) + lane;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int sl = 0; sl < p.S; ++sl) {
-      const float4 v = __ldcg(src + sl * 32);
-      acc[0] += v.x;
-      acc[1] += v.y;
-      acc[2] += v.z;
-      acc[3] += v.w;
-    }
-    epilogue(p, nt, lane >> 2, lane & 3, acc);
-  }
-}
-
 // Grid-wide barrier between chained products.  All CTAs of the launch are resident (one per SM), the
 // counter is reset by the last CTA of the launch.  The wait is bounded like every other wait here.
 TI_DEVICE void grid_barrier(int* counter, int target, unsigned* status) {
@@ -588,7 +599,7 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const GemvParams& p0 = c.op[0];
   const bool stamp = p0.dbg != nullptr && tid == 0;
-  if (stamp) p0.dbg[cta * 8 + 0] = globaltimer_ns();
+  if (stamp) p0.dbg[cta * 32 + 0] = globaltimer_ns();
   const size_t x_bytes = (size_t)c.x_bytes;
   const int W = ncta * kWarps, widx = warp * ncta + cta;      // consecutive units land on different SMs
 
@@ -601,10 +612,11 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
   uint8_t* after_ring = ring0 + (size_t)kWarps * stages * stage_bytes;
   const uint32_t bar0 = smem_u32(after_ring) + warp * stages * 8;
   volatile int* q = reinterpret_cast<volatile int*>(after_ring + kWarps * stages * 8) + warp * kCQ;
+  float4* tscr = reinterpret_cast<float4*>(after_ring + kWarps * (stages * 8 + kCQ * 4));   // [2][kWarps][32], team mode
 
   WarpStream ws;
-  ws.op = ws.pre = ws.sk = ws.wr = ws.rd = 0;
-  ws.pre_valid = ws.sdone = ws.can_ticket = ws.opened = false;
+  ws.op = ws.sk = ws.wr = ws.rd = 0;
+  ws.sdone = ws.can_ticket = ws.opened = false;
   ws.cs = ws.idx = ws.left = ws.row_left = ws.kb_row = 0;
   ws.ist = ws.skip = 0;
   ws.have = ws.cdone = false;
@@ -620,7 +632,7 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
   // be using the tickets) has completed.
   pdl_trigger();
   pdl_wait();
-  if (stamp) p0.dbg[cta * 8 + 1] = globaltimer_ns();
+  if (stamp) p0.dbg[cta * 32 + 1] = globaltimer_ns();
   if (lane == 0) ws.can_ticket = true;
 
   unsigned cidx = 0;                            // chunks consumed by this warp so far
@@ -645,10 +657,6 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
     e = __shfl_sync(0xffffffffu, e, 0);
     if ((e == TI_UNIT_END || (e & kUnitMask) == kUnitMask) && cur_op >= 0) {
       const GemvParams& pp = c.op[cur_op];
-      if (pp.S > 1) {                             // every slice partial is in the workspace after this barrier
-        grid_barrier(p0.sched + 2, ++nbar * ncta, p0.status);
-        split_reduce(pp, cta, ncta);
-      }
       // this warp has sent everything it owns of the previous product: collect the all-reduce
       if (pp.epi == EPI_ROWPAR && pp.tp > 1) rowpar_reduce(pp, cta, ncta);
     }
@@ -657,9 +665,13 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
     const GemvParams& p = c.op[op];
     if (unit == kUnitMask) {
       cur_op = op;
+      if (stamp) p0.dbg[cta * 32 + 8 + 4 * op] = globaltimer_ns();
+      if (lane == 0)                              // start streaming this product's first unit while waiting
+        for (int s = ws.idx - (int)cidx; s < stages; ++s) ws.next(c, widx, W, q, ring_u32, bar0, stages);
       // ---- product boundary: every warp of every CTA is done with the previous product
       if (op > 0) grid_barrier(p0.sched + 2, ++nbar * ncta, p0.status);
       else __syncthreads();
+      if (stamp) p0.dbg[cta * 32 + 9 + 4 * op] = globaltimer_ns();
       lstride = limb_stride(p.K);
       xl = smem + (size_t)p.M * lstride;
       if (WT == W_INT8) stage_limbs(p, 0, p.K, xh, xl, lstride, scratch);
@@ -668,15 +680,19 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
         inv0 = g < p.M ? scratch[288 + g] : 0.f;
         inv1 = g + 8 < p.M ? scratch[288 + g + 8] : 0.f;
       }
-      if (stamp && op == 0) p0.dbg[cta * 8 + 2] = globaltimer_ns();
+      if (stamp) p0.dbg[cta * 32 + 10 + 4 * op] = globaltimer_ns();
       continue;
     }
     if (lane == 0)                                // keep the ring full
       for (int s = ws.idx - (int)cidx; s < stages; ++s) ws.next(c, widx, W, q, ring_u32, bar0, stages);
 
     const bool hi = p.M > 8;
-    const int grp = unit / p.S, sl = unit - grp * p.S;
-    const int kt0 = sl * p.kb_per_split, kt1 = min(p.KB, kt0 + p.kb_per_split);
+    const int grp = unit;
+    int kt0 = 0, kt1 = p.KB;
+    if (p.T > 1) {
+      team_slice(p, warp % p.T, kt0, kt1);
+      kt1 += kt0;
+    }
     const int rn = min(p.R, p.n_tiles - grp * p.R);
     // rows of the staged activations this lane feeds to the MMA (rows >= M are clamped: their results
     // are never written)
@@ -685,6 +701,8 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
     const uint32_t xh1 = smem_u32(xh) + xrow1 * (uint32_t)lstride + t * 16, xl1 = smem_u32(xl) + xrow1 * (uint32_t)lstride + t * 16;
     const uint32_t xs0 = smem_u32(xs) + (xrow0 * (uint32_t)(p.K + 8) + t * 8) * 2, xs1 = smem_u32(xs) + (xrow1 * (uint32_t)(p.K + 8) + t * 8) * 2;
     for (int r = 0; r < rn; ++r) {
+      EpiPre pre{1.f, 1.f, 0u, 0u};
+      if (p.T == 1 || warp % p.T == 0) pre = epi_prefetch(p, grp * p.R + r, g, t);
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       int ah[2][4], al[2][4];                    // two accumulator sets: consecutive tiles do not chain
 #pragma unroll
@@ -753,14 +771,33 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
         for (int b = 0; b < 4; ++b)
           acc[b] = ((float)(ah[0][b] + ah[1][b]) * 256.f + (float)(al[0][b] + al[1][b])) * (b < 2 ? inv0 : inv1);
       }
-      if (p.S > 1)
-        reinterpret_cast<float4*>(p.ws + ((size_t)(grp * p.R + r) * p.S + sl) * 128)[lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      else
-        epilogue(p, grp * p.R + r, g, t, acc);
+      if (p.T > 1) {
+        // partial sums of the team meet in shared memory (two alternating slots: the barrier of exchange n+1
+        // orders the leader's reads of slot n before anybody's writes of exchange n+2)
+        // (the slot is the parity of the team's unit count WITHIN this product: teams of different sizes in
+        // consecutive products are made of warps with different histories)
+        const int slot = (unit / (W / p.T) * p.R + r) & 1;
+        float4* ex = tscr + (size_t)slot * kWarps * 32;
+        ex[warp * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        const int team = warp / p.T;
+        asm volatile("bar.sync %0, %1;\n" ::"r"(1 + team), "r"(p.T * 32) : "memory");
+        if (warp % p.T == 0) {
+          for (int j = 1; j < p.T; ++j) {
+            const float4 v = ex[(warp + j) * 32 + lane];
+            acc[0] += v.x;
+            acc[1] += v.y;
+            acc[2] += v.z;
+            acc[3] += v.w;
+          }
+          epilogue(p, grp * p.R + r, g, t, acc, pre);
+        }
+      } else {
+        epilogue(p, grp * p.R + r, g, t, acc, pre);
+      }
     }
-    if (stamp) p0.dbg[cta * 8 + 4] = globaltimer_ns();
+    if (stamp) p0.dbg[cta * 32 + 11 + 4 * op] = globaltimer_ns();
   }
-  if (stamp) p0.dbg[cta * 8 + 5] = globaltimer_ns();
+  if (stamp) p0.dbg[cta * 32 + 5] = globaltimer_ns();
   // the last CTA of the launch resets the tickets and the barrier counter for the next launch
   __syncthreads();
   if (tid == 0) {
@@ -794,17 +831,19 @@ static int op_x_bytes(const GemvParams& p, int wt) { return (int)x_smem_bytes_im
 
 static size_t smem_bytes(const ChainParams& c) {
   const GemvParams& p = c.op[0];
-  return (size_t)c.x_bytes + (size_t)kWarps * (p.stages * (p.tps * 512 + 8) + kCQ * 4);
+  bool team = false;
+  for (int i = 0; i < c.n_ops; ++i) team = team || c.op[i].T > 1;
+  return (size_t)c.x_bytes + (size_t)kWarps * (p.stages * (p.tps * 512 + 8) + kCQ * 4) + (team ? kTeamBytes : 0);
 }
 
 static int check(const GemvParams& p, int wt) {
   const int tk = wt == W_INT8 ? 64 : 32;
   if (p.M < 1 || p.M > 16 || p.N < 2 || (p.N & 1) || p.K % tk || p.KB * tk != p.K) return -2;
   if (p.R < 1 || p.R > kMaxR || p.n_tiles < 1 || p.n_tiles >= (1 << 26)) return -3;
-  if (p.S < 1 || p.kb_per_split < 1 || (long long)(p.S - 1) * p.kb_per_split >= p.KB ||
-      (long long)p.S * p.kb_per_split < p.KB || (p.S > 1 && p.ws == nullptr))
-    return -6;
-  if ((long long)((p.n_tiles + p.R - 1) / p.R) * p.S >= kUnitMask) return -3;
+  if (p.S != 1 || p.kb_per_split != p.KB) return -6;
+  if (p.T != 1 && p.T != 2 && p.T != 4 && p.T != 8 && p.T != 16) return -6;
+  if (p.T > kWarps || p.KB < p.T) return -6;
+  if ((p.n_tiles + p.R - 1) / p.R >= kUnitMask) return -3;
   if (p.tps != kTPS) return -7;
   if (p.sched == nullptr || p.stages < 1 || p.stages > 8) return -7;
   if (p.xmode < 0 || p.xmode > 1 || p.epi < 0 || p.epi > 3) return -8;

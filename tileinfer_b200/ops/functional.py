@@ -158,18 +158,31 @@ def plan_gemv(wt: int, xmode: int, M: int, n_tiles: int, KB: int, ncta: int = NU
     return None
 
 
-def plan_split(n_tiles: int, KB: int, R: int, split: int | None = None, ncta: int = NUM_SMS):
-    """(S, kb_per_split): cuts the k range of a product into S slices (multiples of 8 tiles, one ring stage) whose
-    partial sums meet in the workspace after a grid barrier.  Off by default (S = 1, whole-k units): on B200 the
-    extra barrier and the reduction pass cost more (about 10 us) than the idle warps of a 640-row-tile product;
-    `split` (or TI_GEMV_S) asks for about that many slices."""
-    if split is None:
-        split = int(os.environ.get("TI_GEMV_S", "1"))
-    if split <= 1 or KB < 16:
-        return 1, KB
-    kbps = min(KB, max(8, -(-KB // split) // 8 * 8))
-    S = -(-KB // kbps)
-    return (S, kbps) if S > 1 else (1, KB)
+TEAM_BYTES = 2 * GEMV_WARPS * 32 * 16      # exchange buffer of team mode (must mirror kTeamBytes)
+
+
+def plan_team(n_tiles: int, KB: int, R: int, team: int | None = None, ncta: int = NUM_SMS) -> int:
+    """Team size T for a product: how many warps of a CTA share one unit, each streaming a slice of k.
+    A product with fewer units than warps would leave warps (and the bytes they keep in flight) idle; T is
+    then the power of two that fills the grid's teams best, units being dealt round-robin to teams.
+    `team` (or TI_GEMV_T) forces a size."""
+    if team is None and "TI_GEMV_T" in os.environ:
+        team = int(os.environ["TI_GEMV_T"])
+    U = -(-n_tiles // R)
+    if team is not None:
+        return team if KB >= team else 1
+    W = ncta * GEMV_WARPS
+    if U >= 0.8 * W:
+        return 1
+    best, best_eff = 1, U / W
+    for T in (2, 4, 8, 16):
+        if T > GEMV_WARPS or KB < 16 * T:      # slices shorter than two ring stages are latency-bound
+            break
+        nt = W // T
+        eff = U / (-(-U // nt) * nt)
+        if eff > best_eff + 0.05:
+            best, best_eff = T, eff
+    return best
 
 
 def max_rows(wt: int, xmode: int, K: int) -> int:
@@ -213,7 +226,7 @@ def default_workspace():
 
 
 def make_gemv_params(W: LinearW, x, out, M, *, xmode=XGLOBAL, epi=EPI_STORE, norm_w=None, resid=None, ws=None,
-                     eps=1e-6, ldx=None, ldo=None, comm=None, order=0, ncta=NUM_SMS, split=None) -> GemvParams:
+                     eps=1e-6, ldx=None, ldo=None, comm=None, order=0, ncta=NUM_SMS, team=None) -> GemvParams:
     p = GemvParams()
     p.w, p.scale, p.x, p.norm_w = ptr(W.tiles), ptr(W.scale), ptr(x), ptr(norm_w)
     p.out, p.resid = ptr(out), ptr(resid)
@@ -223,15 +236,13 @@ def make_gemv_params(W: LinearW, x, out, M, *, xmode=XGLOBAL, epi=EPI_STORE, nor
     R, tps, stages = plan
     if ws is None:
         ws = default_workspace()
-    S, kbps = plan_split(W.n_tiles, W.KB, R, split, ncta)
-    if S > 1 and W.n_tiles * S > ws.max_units:
-        S, kbps = 1, W.KB
-    p.M, p.N, p.n_tiles, p.K, p.KB, p.S, p.kb_per_split = M, W.N, W.n_tiles, W.K, W.KB, S, kbps
+    p.M, p.N, p.n_tiles, p.K, p.KB, p.S, p.kb_per_split = M, W.N, W.n_tiles, W.K, W.KB, 1, W.KB
     p.ws = ptr(ws.ws)
     p.ldx = ldx if ldx is not None else (x.stride(0) if x.dim() > 1 else W.K)
     p.ldo = ldo if ldo is not None else (out.stride(0) if out.dim() > 1 else W.N)
     p.eps = eps
-    p.stages, p.J, p.tps, p.R = stages, 1, tps, R
+    p.stages, p.T, p.tps, p.R = stages, plan_team(W.n_tiles, W.KB, R, team, ncta), tps, R
+    p._xb = x_smem_bytes(W.wt, xmode, M, W.K, W.K)
     p.xmode, p.epi = xmode, epi
     if ws is None:
         ws = default_workspace()
@@ -253,6 +264,14 @@ def make_chain(params: list) -> ChainParams:
     c.n_ops = len(params)
     # one ring geometry per launch: the one of the op that has the least room
     tps, stages = min((p.tps * p.stages, p.tps, p.stages) for p in params)[1:]
+    # team mode needs its exchange buffer next to the rings: give up ring stages for it, or, failing that, teams
+    xb = max(getattr(p, "_xb", 0) for p in params)
+    while any(p.T > 1 for p in params) and xb + TEAM_BYTES + GEMV_WARPS * (stages * (tps * 512 + 8) + 64) > 227 * 1024:
+        if stages > 1:
+            stages -= 1
+        else:
+            for p in params:
+                p.T = 1
     for i, p in enumerate(params):
         p.tps, p.stages = tps, stages
         c.op[i] = p
@@ -273,7 +292,7 @@ def gemv_launch(p: GemvParams, wt: int, xmode: int = None, epi: int = None, ncta
 
 
 def gemv(W: LinearW, x: torch.Tensor, *, out=None, xmode=XGLOBAL, epi=EPI_STORE, norm_w=None, resid=None, ws=None,
-         eps=1e-6, comm=None, order=0, split=None) -> torch.Tensor:
+         eps=1e-6, comm=None, order=0, team=None) -> torch.Tensor:
     """Convenience form (allocates `out`); loops over row chunks that fit in shared memory."""
     M = x.shape[0]
     step = max_rows(W.wt, xmode, W.K)
@@ -285,7 +304,7 @@ def gemv(W: LinearW, x: torch.Tensor, *, out=None, xmode=XGLOBAL, epi=EPI_STORE,
         m = min(step, M - m0)
         p = make_gemv_params(W, x[m0:m0 + m], out[m0:m0 + m], m, xmode=xmode, epi=epi, norm_w=norm_w,
                              resid=None if resid is None else resid[m0:m0 + m], ws=ws, eps=eps,
-                             ldx=x.stride(0), ldo=out.stride(0), comm=comm, order=order, split=split)
+                             ldx=x.stride(0), ldo=out.stride(0), comm=comm, order=order, team=team)
         gemv_launch(p, W.wt, xmode, epi)
     return out
 
