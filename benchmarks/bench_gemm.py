@@ -1,7 +1,7 @@
 """Prefill GEMM micro-benchmark (tcgen05 kind::i8 W8A16): time, int8 tensor throughput of the two limb
 products and weight-streaming bandwidth per shape.  Weight copies are rotated so each launch streams from HBM.
 
-    python benchmarks/bench_gemm.py [--M 128 512 2048]
+    python benchmarks/bench_gemm.py [--M 32 64 128 512 2048]
 """
 import argparse
 import os
@@ -18,7 +18,7 @@ SHAPES = {"in_proj": (16480, 5120, F.GEPI_STORE), "gate_up": (34816, 5120, F.GEP
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--M", type=int, nargs="*", default=[128, 512, 2048])
+    ap.add_argument("--M", type=int, nargs="*", default=[32, 64, 128, 512, 2048])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--only", default=None)
     args = ap.parse_args()

@@ -430,7 +430,9 @@ def test_topk(k):
     assert torch.equal(idx[1:].long() - 1000, ri[1:])
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (200, 1552, 384), (64, 5120, 768), (300, 2048, 5120)])
+# token tiles of 32 / 64 / 128; (24, 1024, 4096), (48, 1552, 2048) and (64, 5120, 4096) also split k over gridDim.z
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (200, 1552, 384), (64, 5120, 768), (300, 2048, 5120),
+                                   (24, 1024, 4096), (48, 1552, 2048), (64, 5120, 4096), (17, 640, 1024)])
 def test_tcgen05_gemm_w8a16(M, N, K):
     """TMA-fed tcgen05 kind::i8 GEMM with two-limb activations against fp32 matmul, all three epilogues."""
     F = _F()
@@ -441,6 +443,7 @@ def test_tcgen05_gemm_w8a16(M, N, K):
     torch.testing.assert_close(recon, x.float(), rtol=0, atol=float(x.float().abs().max()) * 2.0 ** -14)
     y = F.gemm_w8a16(W, limbs)
     torch.cuda.synchronize()
+    assert torch.equal(y, F.gemm_w8a16(W, limbs)), "deterministic (split-k partials are added in a fixed order)"
     ref = x.float() @ W.dense().float().t()
     tol = dict(rtol=2e-2, atol=3e-2 if K < 2048 else 8e-2)      # outputs of magnitude ~10: one bf16 ulp is 0.06
     torch.testing.assert_close(y.float(), ref, **tol)
@@ -449,7 +452,8 @@ def test_tcgen05_gemm_w8a16(M, N, K):
     torch.testing.assert_close(y2.float(), r.float() + ref, rtol=2e-2, atol=tol["atol"] + 1e-2)
     y3 = F.gemm_w8a16(W, limbs, epi=F.GEPI_SWIGLU)
     gu = ref.to(BF16).float()
-    torch.testing.assert_close(y3.float(), torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2], rtol=3e-2, atol=0.3)
+    torch.testing.assert_close(y3.float(), torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2], rtol=3e-2,
+                               atol=0.3 if K < 2048 else 0.6)
     # fused RMSNorm in the limb kernel
     nw = (torch.randn(K, device="cuda") * 0.1).to(BF16)
     ln = F.quant_rows(x, norm_w=nw)

@@ -21,7 +21,8 @@ STAMP = os.path.join(BUILD, "stamp.txt")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
-              "-DTI_GEMV_WARPS=" + os.environ.get("TI_GEMV_WARPS", "16")]
+              "-DTI_GEMV_WARPS=" + os.environ.get("TI_GEMV_WARPS", "16"),
+              "-DTI_GEMV_TPS=" + os.environ.get("TI_GEMV_TPS", "8")]
 
 
 def _nvcc() -> str:

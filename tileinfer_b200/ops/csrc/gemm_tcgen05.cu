@@ -14,22 +14,36 @@
 // of the weight tiles ([N/8][K/64][8][64] layout -> 128 rows x 64 B, 64-byte swizzle) and two 2-D copies of
 // the limb planes; warp 1 = MMA issuer (one lane): four tcgen05.mma (2 k-steps x 2 limbs) per slab, then
 // tcgen05.commit to release the stage; warps 2..5 = epilogue: tcgen05.ld of their 32 TMEM lanes, scale,
-// fused epilogue (bf16 store / SwiGLU / residual add), coalesced stores.  8 stages of 24 KB.
+// fused epilogue (bf16 store / SwiGLU / residual add), coalesced stores.
+// The token tile is a template parameter (32, 64 or 128 tokens): a decode batch of 17..64 rows then moves 4-8 KB of
+// limbs per 8 KB of weights instead of 16 KB, and the ring holds 12-16 stages, so the kernel streams weights at
+// HBM speed.  Products with few weight-row tiles (N = 5120: 40 tiles for 148 SMs) are split along k over
+// gridDim.z; the scaled fp32 partials meet in a workspace and the last CTA of a tile to arrive adds them in split
+// order (deterministic) and runs the epilogue.
 // Every mbarrier wait is bounded; on expiry the status word is set, the roles drain and TMEM is freed.
 #include <cuda.h>
+
+#include <algorithm>
+#include <map>
+#include <mutex>
+#include <tuple>
 
 #include "common.cuh"
 
 namespace ti {
 
 constexpr int kBM = 128;          // weight rows per CTA (TMEM lanes)
-constexpr int kBN = 128;          // tokens per CTA (TMEM columns per accumulator)
 constexpr int kBK = 64;           // bytes of k per stage (one 64-byte swizzle row)
-constexpr int kGStages = 8;
-constexpr int kStageA = kBM * kBK;                 // 8 KB
-constexpr int kStageB = kBN * kBK;                 // 8 KB per limb plane
-constexpr int kStageBytesG = kStageA + 2 * kStageB;
+constexpr int kStageA = kBM * kBK;                 // 8 KB of weights per stage
 constexpr int kGemmThreads = 192;
+constexpr int kGemmRingBytes = 192 * 1024;
+// BN = tokens per CTA (TMEM columns per accumulator)
+template <int BN> struct GemmGeom {
+  static constexpr int kStageB = BN * kBK;                         // one limb plane
+  static constexpr int kStageBytes = kStageA + 2 * kStageB;
+  static constexpr int kStages = kGemmRingBytes / kStageBytes;     // 128: 8, 64: 12, 32: 16
+  static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 16 * kStages + 64 + 1024;
+};
 constexpr unsigned long long kGemmWaitNs = 2000000000ull;
 
 struct GemmParams {
@@ -41,7 +55,10 @@ struct GemmParams {
   const __nv_bfloat16* resid;      // ROWPAR: [M, N]
   void* out;                       // bf16 [M, ldo]  (SWIGLU: N/2 columns)
   unsigned* status;
+  float* part;                     // split-k partials [S][M][N] fp32
+  unsigned* tile_count;            // [tiles_n * tiles_m] arrival counters, zero between launches
   int M, N, K, ldo, epi;
+  int kb_per_split;                // 64-byte k slabs per gridDim.z slice
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -107,36 +124,77 @@ TI_DEVICE uint64_t smem_desc_sw64(uint32_t saddr) {
   d |= (uint64_t)4 << 61;                              // layout type: SWIZZLE_64B
   return d;
 }
-// kind::i8 instruction descriptor: D = s32, A = int8 (K-major), B = int8 / uint8 (K-major), M = 128, N = 128
-TI_DEVICE constexpr uint32_t idesc_i8(bool b_signed) {
-  return (2u << 4) | (1u << 7) | ((b_signed ? 1u : 0u) << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+// kind::i8 instruction descriptor: D = s32, A = int8 (K-major), B = int8 / uint8 (K-major), M = 128, N = BN
+template <int BN> TI_DEVICE constexpr uint32_t idesc_i8(bool b_signed) {
+  return (2u << 4) | (1u << 7) | ((b_signed ? 1u : 0u) << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
 
 enum { GEPI_STORE = 0, GEPI_SWIGLU = 1, GEPI_ROWPAR = 2 };
 
+// value of output (token m, weight row n) -> fused epilogue
+TI_DEVICE void gemm_epilogue(const GemmParams& p, int m, int n, int lane, float v) {
+  if (p.epi == GEPI_SWIGLU) {
+    // rows come interleaved (gate, up): lanes 2i / 2i+1
+    const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+    if ((lane & 1) == 0 && n < p.N) {
+      const float gate = round_bf16(v), up = round_bf16(other);
+      static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] = __float2bfloat16_rn(silu_f(gate) * up);
+    }
+  } else if (n < p.N) {
+    float r = v;
+    if (p.epi == GEPI_ROWPAR) r += __bfloat162float(p.resid[(size_t)m * p.N + n]);
+    static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(r);
+  }
+}
+
+// the same for four adjacent weight rows n..n+3 of one token (N is a multiple of 4 here)
+TI_DEVICE void gemm_epilogue4(const GemmParams& p, int m, int n, float4 v) {
+  if (p.epi == GEPI_SWIGLU) {
+    const float g0 = round_bf16(v.x), u0 = round_bf16(v.y), g1 = round_bf16(v.z), u1 = round_bf16(v.w);
+    *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + (n >> 1)) =
+        pack_bf16(silu_f(g0) * u0, silu_f(g1) * u1);
+    return;
+  }
+  if (p.epi == GEPI_ROWPAR) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p.resid + (size_t)m * p.N + n);
+    v.x += bf16lo(r.x);
+    v.y += bf16hi(r.x);
+    v.z += bf16lo(r.y);
+    v.w += bf16hi(r.y);
+  }
+  *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + n) =
+      make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+}
+
+template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w8a16_kernel(const __grid_constant__ GemmParams p) {
+  using G = GemmGeom<BN>;
+  constexpr int kStages = G::kStages, kStageBytes = G::kStageBytes, kStageB = G::kStageB;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte aligned stage buffers (the swizzle pattern repeats every 512 bytes)
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t stage0 = smem_u32(smem);
-  const uint32_t bars = stage0 + kGStages * kStageBytesG;       // full[8], empty[8], acc_full, tmem slot
-  const uint32_t full0 = bars, empty0 = bars + 8 * kGStages, acc_bar = bars + 16 * kGStages, tmem_slot = acc_bar + 8;
-  uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem + kGStages * kStageBytesG + 16 * kGStages + 8);
+  const uint32_t bars = stage0 + kStages * kStageBytes;         // full[], empty[], acc_full, tmem slot
+  const uint32_t full0 = bars, empty0 = bars + 8 * kStages, acc_bar = bars + 16 * kStages, tmem_slot = acc_bar + 8;
+  uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem + kStages * kStageBytes + 16 * kStages + 8);
+  __shared__ int s_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+  const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z, S = gridDim.z;
   const int KB = p.K / kBK;
+  const int kb0 = split * p.kb_per_split, kb1 = min(KB, kb0 + p.kb_per_split);
+  constexpr uint32_t kCols = 2 * BN < 32 ? 32 : 2 * BN;          // TMEM allocation: a power of two >= 32
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kGStages; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
     mbar_init(acc_bar, 1);
     fence_mbar_init();
   }
-  if (warp == 1) {                       // one warp allocates 256 TMEM columns (two 128-column accumulators)
-    tmem_alloc(tmem_slot, 256);
+  if (warp == 1) {                       // one warp allocates the TMEM columns of the two accumulators
+    tmem_alloc(tmem_slot, kCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -148,34 +206,34 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w8a16_kernel(const __gri
     // ------------------------------------------------------------ TMA producer
     if (elect_one()) {
       bool ok = true;
-      for (int kb = 0; kb < KB && ok; ++kb) {
-        const int s = kb % kGStages;
-        const uint32_t par = ((kb / kGStages) & 1) ^ 1;           // a fresh barrier passes a wait on parity 1
+      for (int kb = kb0; kb < kb1 && ok; ++kb) {
+        const int it = kb - kb0, s = it % kStages;
+        const uint32_t par = ((it / kStages) & 1) ^ 1;            // a fresh barrier passes a wait on parity 1
         ok = mbar_wait(empty0 + 8 * s, par, kGemmWaitNs, p.status);
         if (!ok) break;
-        const uint32_t dst = stage0 + s * kStageBytesG;
-        mbar_expect_tx(full0 + 8 * s, kStageBytesG);
+        const uint32_t dst = stage0 + s * kStageBytes;
+        mbar_expect_tx(full0 + 8 * s, kStageBytes);
         tma_load_4d(dst, &p.map_w, 0, 0, kb, tile_n * (kBM / 8), full0 + 8 * s);
-        tma_load_2d(dst + kStageA, &p.map_xh, kb * kBK, tile_m * kBN, full0 + 8 * s);
-        tma_load_2d(dst + kStageA + kStageB, &p.map_xl, kb * kBK, tile_m * kBN, full0 + 8 * s);
+        tma_load_2d(dst + kStageA, &p.map_xh, kb * kBK, tile_m * BN, full0 + 8 * s);
+        tma_load_2d(dst + kStageA + kStageB, &p.map_xl, kb * kBK, tile_m * BN, full0 + 8 * s);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       bool ok = true;
-      for (int kb = 0; kb < KB && ok; ++kb) {
-        const int s = kb % kGStages;
-        ok = mbar_wait(full0 + 8 * s, (kb / kGStages) & 1, kGemmWaitNs, p.status);
+      for (int kb = kb0; kb < kb1 && ok; ++kb) {
+        const int it = kb - kb0, s = it % kStages;
+        ok = mbar_wait(full0 + 8 * s, (it / kStages) & 1, kGemmWaitNs, p.status);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a = stage0 + s * kStageBytesG, bh = a + kStageA, bl = bh + kStageB;
+        const uint32_t a = stage0 + s * kStageBytes, bh = a + kStageA, bl = bh + kStageB;
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks) {                          // two 32-byte k steps inside the 64-byte slab
           const uint64_t da = smem_desc_sw64(a + ks * 32);
-          const uint32_t acc = (kb > 0 || ks > 0) ? 1u : 0u;
-          umma_i8(tmem_base, da, smem_desc_sw64(bh + ks * 32), idesc_i8(true), acc);
-          umma_i8(tmem_base + kBN, da, smem_desc_sw64(bl + ks * 32), idesc_i8(false), acc);
+          const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
+          umma_i8(tmem_base, da, smem_desc_sw64(bh + ks * 32), idesc_i8<BN>(true), acc);
+          umma_i8(tmem_base + BN, da, smem_desc_sw64(bl + ks * 32), idesc_i8<BN>(false), acc);
         }
         umma_commit(empty0 + 8 * s);                              // stage may be refilled once these MMAs are done
       }
@@ -189,36 +247,65 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w8a16_kernel(const __gri
     const int n = tile_n * kBM + quarter * 32 + lane;             // weight row == output feature of this lane
     const float ws = (ok && n < p.N) ? __bfloat162float(p.wscale[n]) : 0.f;
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    for (int c0 = 0; c0 < kBN; c0 += 32) {
+    for (int c0 = 0; c0 < BN; c0 += 32) {
       uint32_t hi[32], lo[32];
       tmem_ld32(taddr + c0, hi);
-      tmem_ld32(taddr + kBN + c0, lo);
+      tmem_ld32(taddr + BN + c0, lo);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
-        const int m = tile_m * kBN + c0 + j;                      // token (uniform over the warp)
+        const int m = tile_m * BN + c0 + j;                       // token (uniform over the warp)
         if (m >= p.M) break;
         const float v = ((float)(int)hi[j] * 256.f + (float)(int)lo[j]) * p.xscale[m] * ws;
-        if (p.epi == GEPI_SWIGLU) {
-          // rows come interleaved (gate, up): lanes 2i / 2i+1
-          const float other = __shfl_xor_sync(0xffffffffu, v, 1);
-          if ((lane & 1) == 0 && n < p.N) {
-            const float gate = round_bf16(v), up = round_bf16(other);
-            static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] = __float2bfloat16_rn(silu_f(gate) * up);
-          }
-        } else if (n < p.N) {
-          float r = v;
-          if (p.epi == GEPI_ROWPAR) r += __bfloat162float(p.resid[(size_t)m * p.N + n]);
-          static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(r);
-        }
+        if (S == 1) gemm_epilogue(p, m, n, lane, v);
+        else if (n < p.N) p.part[((size_t)split * p.M + m) * p.N + n] = v;
       }
     }
     tc_fence_before();
   }
+  if (S > 1) {
+    // ---- split-k: the last CTA of this output tile to arrive adds the partials in split order
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned prev = atomicAdd(p.tile_count + tile_m * gridDim.x + tile_n, 1u);
+      s_last = prev + 1 == (unsigned)S;
+      if (s_last) p.tile_count[tile_m * gridDim.x + tile_n] = 0;   // ready for the next launch
+      __threadfence();
+    }
+    __syncthreads();
+    if (s_last && warp >= 2) {
+      // lane -> four adjacent output features, warp -> every fourth token; the loads of four tokens and all
+      // slices are issued before the first is used
+      const int n4 = tile_n * kBM + lane * 4;
+      const int m_end = min(p.M, (tile_m + 1) * BN);
+      for (int m0 = tile_m * BN + (warp - 2); m0 < m_end; m0 += 16) {
+        float4 acc[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          const int m = m0 + 4 * u;
+          if (m < m_end && n4 < p.N)
+            for (int z = 0; z < S; ++z) {
+              const float4 v = __ldcg(reinterpret_cast<const float4*>(p.part + ((size_t)z * p.M + m) * p.N + n4));
+              acc[u].x += v.x;
+              acc[u].y += v.y;
+              acc[u].z += v.z;
+              acc[u].w += v.w;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int m = m0 + 4 * u;
+          if (m < m_end && n4 < p.N) gemm_epilogue4(p, m, n4, acc[u]);
+        }
+      }
+    }
+  }
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, kCols);
   }
 }
 
@@ -306,6 +393,54 @@ static int encode_map(CUtensorMap* map, const void* base, int rank, const cuuint
   return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
+// Tensor maps are a pure function of (base, extents, box): encoding one costs a driver call of a few
+// microseconds, three of them per GEMM would dominate a batched decode step, so they are cached.
+struct MapKey {
+  const void* base;
+  int d0, d1, box;
+  bool operator<(const MapKey& o) const { return std::tie(base, d0, d1, box) < std::tie(o.base, o.d0, o.d1, o.box); }
+};
+// box == 0: weight map over [n_tiles = d1][KB = d0][8][64]; box > 0: limb plane [M = d1][K = d0], box {64, box}
+static int cached_map(CUtensorMap* dst, const void* base, int d0, int d1, int box) {
+  static std::map<MapKey, CUtensorMap> cache;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  const MapKey key{base, d0, d1, box};
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    CUtensorMap m;
+    int rc;
+    if (box == 0) {
+      const cuuint64_t dims[4] = {64, 8, (cuuint64_t)d0, (cuuint64_t)d1};
+      const cuuint64_t strides[3] = {64, 512, (cuuint64_t)d0 * 512};
+      const cuuint32_t bx[4] = {64, 8, 1, 16};
+      rc = encode_map(&m, base, 4, dims, strides, bx);
+    } else {
+      const cuuint64_t dims[2] = {(cuuint64_t)d0, (cuuint64_t)d1};
+      const cuuint64_t strides[1] = {(cuuint64_t)d0};
+      const cuuint32_t bx[2] = {64, (cuuint32_t)box};
+      rc = encode_map(&m, base, 2, dims, strides, bx);
+    }
+    if (rc) return rc;
+    if (cache.size() > 8192) cache.clear();
+    it = cache.emplace(key, m).first;
+  }
+  *dst = it->second;
+  return 0;
+}
+
+template <int BN>
+static int launch_gemm(const GemmParams& p, dim3 grid, cudaStream_t st) {
+  static bool configured = false;
+  auto k = gemm_w8a16_kernel<BN>;
+  if (!configured) {
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmGeom<BN>::kSmem);
+    configured = true;
+  }
+  k<<<grid, kGemmThreads, GemmGeom<BN>::kSmem, st>>>(p);
+  return (int)cudaGetLastError();
+}
+
 }  // namespace ti
 
 extern "C" {
@@ -320,28 +455,22 @@ int ti_quant_rows(const void* x, int ldx, const void* norm_w, float eps, int M, 
 }
 
 // y = x W^T for tiled int8 weights `w` ([n_tiles][K/64][8][64]) and the limb planes of x.
+// `part` / `tile_count`: split-k workspace (fp32 [S][M][N]) and zeroed per-tile counters, may be null (no split);
+// `part_bytes` / `n_count` are their capacities.  The token tile (32 / 64 / 128) and the k split follow from M, N.
 int ti_gemm_w8a16(const void* w, const void* wscale, int n_tiles, int N, int K, const void* xh, const void* xl,
-                  const void* xscale, int M, const void* resid, void* out, int ldo, int epi, void* status, void* stream) {
+                  const void* xscale, int M, const void* resid, void* out, int ldo, int epi, void* status, void* part,
+                  size_t part_bytes, void* tile_count, int n_count, void* stream) {
   if (M <= 0) return 0;
   if (K % 64 || N < 1 || epi < 0 || epi > 2) return -2;
   ti::GemmParams p = {};
   const int KB = K / 64;
-  {
-    const cuuint64_t dims[4] = {64, 8, (cuuint64_t)KB, (cuuint64_t)n_tiles};
-    const cuuint64_t strides[3] = {64, 512, (cuuint64_t)KB * 512};
-    const cuuint32_t box[4] = {64, 8, 1, 16};
-    const int rc = ti::encode_map(&p.map_w, w, 4, dims, strides, box);
-    if (rc) return rc;
-  }
-  {
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
-    const cuuint64_t strides[1] = {(cuuint64_t)K};
-    const cuuint32_t box[2] = {64, 128};
-    int rc = ti::encode_map(&p.map_xh, xh, 2, dims, strides, box);
-    if (rc) return rc;
-    rc = ti::encode_map(&p.map_xl, xl, 2, dims, strides, box);
-    if (rc) return rc;
-  }
+  const int BN = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+  int rc = ti::cached_map(&p.map_w, w, KB, n_tiles, 0);
+  if (rc) return rc;
+  rc = ti::cached_map(&p.map_xh, xh, K, M, BN);
+  if (rc) return rc;
+  rc = ti::cached_map(&p.map_xl, xl, K, M, BN);
+  if (rc) return rc;
   p.xscale = (const float*)xscale;
   p.wscale = (const __nv_bfloat16*)wscale;
   p.resid = (const __nv_bfloat16*)resid;
@@ -352,15 +481,23 @@ int ti_gemm_w8a16(const void* w, const void* wscale, int n_tiles, int N, int K, 
   p.K = K;
   p.ldo = ldo;
   p.epi = epi;
-  const size_t smem = (size_t)ti::kGStages * ti::kStageBytesG + 16 * ti::kGStages + 64 + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(ti::gemm_w8a16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    configured = true;
+  const int tiles_n = (n_tiles * 8 + ti::kBM - 1) / ti::kBM, tiles_m = (M + BN - 1) / BN;
+  // k split: fill the 148 SMs when there are few output tiles, at least 16 slabs per slice
+  int S = 1;
+  if (part != nullptr && tile_count != nullptr && tiles_n * tiles_m < 120 && N % 4 == 0 && ldo % 4 == 0) {
+    S = std::min(std::min(148 / (tiles_n * tiles_m), KB / 16), 16);
+    while (S > 1 && ((size_t)S * M * N * 4 > part_bytes || tiles_n * tiles_m > n_count)) --S;
+    if (S < 1) S = 1;
   }
-  dim3 grid((n_tiles * 8 + ti::kBM - 1) / ti::kBM, (M + ti::kBN - 1) / ti::kBN);
-  ti::gemm_w8a16_kernel<<<grid, ti::kGemmThreads, smem, (cudaStream_t)stream>>>(p);
-  return (int)cudaGetLastError();
+  p.kb_per_split = (KB + S - 1) / S;
+  S = (KB + p.kb_per_split - 1) / p.kb_per_split;              // no empty slice
+  p.part = (float*)part;
+  p.tile_count = (unsigned*)tile_count;
+  dim3 grid(tiles_n, tiles_m, S);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (BN == 32) return ti::launch_gemm<32>(p, grid, st);
+  if (BN == 64) return ti::launch_gemm<64>(p, grid, st);
+  return ti::launch_gemm<128>(p, grid, st);
 }
 
 }  // extern "C"

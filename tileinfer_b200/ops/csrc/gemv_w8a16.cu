@@ -88,7 +88,11 @@ enum { W_INT8 = 0, W_BF16 = 1 };
 #define TI_GEMV_WARPS 16
 #endif
 constexpr int kThreads = TI_GEMV_WARPS * 32;
-constexpr int kTPS = 8;                    // 512-byte tiles per ring stage (4 KB)
+#ifndef TI_GEMV_TPS
+#define TI_GEMV_TPS 8
+#endif
+constexpr int kTPS = TI_GEMV_TPS;          // 512-byte tiles per ring stage (8: 4 KB)
+constexpr int kMaxStages = 16;
 constexpr int kMaxTilesPerStage = 16;
 constexpr int kWarps = kThreads / 32;
 constexpr int kCQ = 16;                    // per-warp queue of scheduled units
@@ -250,6 +254,13 @@ TI_DEVICE void stage_limbs(const GemvParams& p, int k_lo, int k_hi, int8_t* xh, 
       }
     }
     if (p.xmode == XNORM) {
+      // the norm weights do not depend on x: their loads are in flight together with those of x
+      uint4 nwv[5];
+#pragma unroll
+      for (int j = 0; j < 5; ++j) {
+        const int c = c_lo + tid + j * nthreads;
+        nwv[j] = c < c_hi ? ldg_cached16(p.norm_w + (size_t)c * 8) : make_uint4(0, 0, 0, 0);
+      }
       ss = warp_sum(ss);
       if (lane == 0) red[warp] = ss;
       __syncthreads();
@@ -260,7 +271,7 @@ TI_DEVICE void stage_limbs(const GemvParams& p, int k_lo, int k_hi, int8_t* xh, 
       for (int j = 0; j < 5; ++j) {
         const int c = c_lo + tid + j * nthreads;
         if (c >= c_hi) continue;
-        const uint4 nw = ldg_cached16(p.norm_w + (size_t)c * 8);
+        const uint4 nw = nwv[j];
         const uint32_t n4[4] = {nw.x, nw.y, nw.z, nw.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -845,7 +856,7 @@ static int check(const GemvParams& p, int wt) {
   if (p.T > kWarps || p.KB < p.T) return -6;
   if ((p.n_tiles + p.R - 1) / p.R >= kUnitMask) return -3;
   if (p.tps != kTPS) return -7;
-  if (p.sched == nullptr || p.stages < 1 || p.stages > 8) return -7;
+  if (p.sched == nullptr || p.stages < 1 || p.stages > kMaxStages) return -7;
   if (p.xmode < 0 || p.xmode > 1 || p.epi < 0 || p.epi > 3) return -8;
   if (p.K % 8 || p.ldx % 8) return -4;
   if (p.tp > kMaxRanks || (p.tp > 1 && p.M > p.m_cap)) return -5;

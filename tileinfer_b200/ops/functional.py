@@ -75,7 +75,7 @@ _l.register("ti_memset_async", _I, [_P, _I, ctypes.c_size_t, _P])
 _l.register("ti_wait_flag_probe", _I, [_P, ctypes.c_uint, ctypes.c_ulonglong, _P, _P, _P])
 
 _l.register("ti_quant_rows", _I, [_P, _I, _P, _F, _I, _I, _P, _P, _P, _P])
-_l.register("ti_gemm_w8a16", _I, [_P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _P, _P])
+_l.register("ti_gemm_w8a16", _I, [_P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _P, _P, ctypes.c_size_t, _P, _I, _P])
 
 _checked = False
 
@@ -142,7 +142,8 @@ def x_smem_bytes(wt: int, xmode: int, M: int, K: int, kslice: int) -> int:
 
 
 PART_BYTES = 0
-_RING_CHOICES = ((8, 6), (8, 5), (8, 4), (8, 3), (8, 2), (8, 1))
+GEMV_TPS = int(os.environ.get("TI_GEMV_TPS", "8"))       # must match the -DTI_GEMV_TPS the library was built with
+_RING_CHOICES = tuple((GEMV_TPS, s) for s in range(48 // GEMV_TPS, 0, -1))
 
 
 def plan_gemv(wt: int, xmode: int, M: int, n_tiles: int, KB: int, ncta: int = NUM_SMS):
@@ -386,7 +387,21 @@ def gemm_w8a16(W: "LinearW", limbs: Limbs, *, out=None, epi=GEPI_STORE, resid=No
     M = limbs.M
     if out is None:
         out = torch.empty(M, W.N // 2 if epi == GEPI_SWIGLU else W.N, dtype=torch.bfloat16, device=limbs.hi.device)
+    part, count = _gemm_workspace(limbs.hi.device)
     check(L().ti_gemm_w8a16(ptr(W.tiles), ptr(W.scale), W.n_tiles, W.N, W.K, ptr(limbs.hi), ptr(limbs.lo),
-                            ptr(limbs.scale), M, ptr(resid), ptr(out), out.stride(0), epi, status_ptr(), stream()),
-          "ti_gemm_w8a16")
+                            ptr(limbs.scale), M, ptr(resid), ptr(out), out.stride(0), epi, status_ptr(), ptr(part),
+                            part.numel() * 4, ptr(count), count.numel(), stream()), "ti_gemm_w8a16")
     return out
+
+
+_GEMM_WS = {}
+
+
+def _gemm_workspace(device):
+    """Split-k partials (fp32, 32 MB: 16 slices of 128 rows x 4096 columns, or fewer of wider products) and the
+    per-tile arrival counters, one set per device; launches on one stream use them one after the other."""
+    key = str(device)
+    if key not in _GEMM_WS:
+        _GEMM_WS[key] = (torch.empty(8 << 20, dtype=torch.float32, device=device),
+                         torch.zeros(256, dtype=torch.int32, device=device))
+    return _GEMM_WS[key]
