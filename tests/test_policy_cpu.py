@@ -94,6 +94,21 @@ def test_prefix_reuse_gives_identical_tokens_and_skips_compute():
     assert got3 == got2 and llm.stats()["prefix_hit_tokens"] >= 64 + 64
 
 
+def test_prefix_state_survives_until_the_hit_sequence_runs():
+    """A sequence that was admitted with a prefix hit may run its first chunk steps later; the snapshot it
+    needs must not be evicted by the snapshots other sequences save in between (tiny snapshot LRU)."""
+    shared = _prompt(64, 70)
+    prompts = [shared + _prompt(40 + 3 * i, 71 + i) for i in range(10)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    want = _llm(enable_prefix_caching=False, num_kvcache_blocks=256, max_num_seqs=8).generate_token_ids(prompts, sp)
+    llm = _llm(prefix_state_stride=16, max_prefix_states=2, num_kvcache_blocks=256, max_num_seqs=8,
+               max_prefill_chunk_tokens=32, max_num_batched_tokens=40)
+    first = llm.generate_token_ids(prompts[:1], sp)
+    rest = llm.generate_token_ids(prompts[1:], sp)
+    assert first + rest == want
+    assert llm.stats()["prefix_hits"] >= 1 and not llm.model_runner.pinned_prefix_states
+
+
 def test_swap_preemption_preserves_outputs():
     prompts = [_prompt(60, 20 + i) for i in range(4)]
     sp = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)

@@ -48,6 +48,7 @@ class ModelRunner:
         self.seq_to_slot: dict = {}
         self.oom_preempted: list = []
         self.prefix_state_cache: OrderedDict = OrderedDict()    # node_id -> (rec, conv) host tensors
+        self.pinned_prefix_states: dict = {}                    # seq_id -> node_id it has yet to restore
         self.pending_snapshots: dict = {}                        # (seq_id, abs tokens) -> (rec, conv)
         self.max_prefix_states = config.max_prefix_states
         self.on_prefix_state_dropped = None                      # callable(node_id)
@@ -113,6 +114,7 @@ class ModelRunner:
         if slot is not None:
             self.free_deltanet_slots.append(slot)
         self.swapped.pop(seq_id, None)
+        self.pinned_prefix_states.pop(seq_id, None)
         for key in [k for k in self.pending_snapshots if k[0] == seq_id]:
             del self.pending_snapshots[key]
 
@@ -128,8 +130,11 @@ class ModelRunner:
             return False
         self.prefix_state_cache[node_id] = snap
         self.prefix_state_cache.move_to_end(node_id)
-        while len(self.prefix_state_cache) > self.max_prefix_states:
-            old, _ = self.prefix_state_cache.popitem(last=False)
+        # LRU, except snapshots a scheduled sequence still has to restore (its first chunk may run a step later)
+        pinned = set(self.pinned_prefix_states.values())
+        over = len(self.prefix_state_cache) - self.max_prefix_states
+        for old in [k for k in self.prefix_state_cache if k not in pinned and k != node_id][:max(0, over)]:
+            del self.prefix_state_cache[old]
             if self.on_prefix_state_dropped is not None:
                 self.on_prefix_state_dropped(old)
         return True
@@ -137,11 +142,13 @@ class ModelRunner:
     def has_prefix_state(self, seq: Sequence, node_id: int, num_tokens: int) -> bool:
         if node_id in self.prefix_state_cache:
             self.prefix_state_cache.move_to_end(node_id)
+            self.pinned_prefix_states[seq.seq_id] = node_id
             return True
         return False
 
     def drop_prefix_state(self, node_id: int):
-        self.prefix_state_cache.pop(node_id, None)
+        if node_id not in self.pinned_prefix_states.values():
+            self.prefix_state_cache.pop(node_id, None)
 
     # ---- swap ------------------------------------------------------------------
     def swap_out(self, seq: Sequence, dev_blocks: list, host_blocks: list):
@@ -191,6 +198,7 @@ class ModelRunner:
             if seq.prefix_restore_key is not None:
                 self.model.state_in(slot, self.prefix_state_cache[seq.prefix_restore_key])
                 seq.prefix_restore_key = None
+                self.pinned_prefix_states.pop(seq.seq_id, None)
             start, n = seq.num_cached_tokens, seq.num_scheduled_tokens
             ids.extend(seq.token_ids[start:start + n])
             pos.extend(range(start, start + n))
