@@ -19,6 +19,25 @@ from tileinfer_b200.models.reference_cpu import Batch  # noqa: E402
 from tileinfer_b200.models.weights import RandomWeights  # noqa: E402
 
 
+def prefill(m, cfg, args):
+    """One sequence, one chunk of --prefill tokens, eager (the path a prefill step takes)."""
+    T = args.prefill
+    nblk = T // 16 + 2
+    m.alloc_cache(nblk + 1, 16, 2)
+    batch = Batch(torch.randint(0, cfg.vocab_size - 1, (T,)), torch.arange(T), [0, T], [T], [list(range(nblk))],
+                  torch.arange(T), [0])
+    m.forward(batch)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        m.forward(batch)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(f"model={cfg.name} prefill tokens={T} ms/forward={ms:.3f} tok/s={T / ms * 1e3:.0f}")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="preset:qwen3.6-27b-8l")
@@ -26,10 +45,13 @@ def main():
     ap.add_argument("--ctx", type=int, default=256)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--quant", default="w8a16")
+    ap.add_argument("--prefill", type=int, default=0, help="run eager prefill forwards of this many tokens instead")
     args = ap.parse_args()
     cfg = get_preset(args.model)
     torch.cuda.set_device(0)
     m = B200HybridModel(cfg, RandomWeights(cfg, 0, device="cuda"), quant=args.quant)
+    if args.prefill:
+        return prefill(m, cfg, args)
     B = args.batch
     nblk_seq = args.ctx // 16 + 2
     m.alloc_cache(B * nblk_seq + 1, 16, B + 1)

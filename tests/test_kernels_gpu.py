@@ -462,3 +462,25 @@ def test_tcgen05_gemm_w8a16(M, N, K):
     y4 = F.gemm_w8a16(W, ln)
     torch.testing.assert_close(y4.float(), xn @ W.dense().float().t(), **tol)
     assert int(torch.zeros(1, device="cuda").item()) == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(24, 1024, 2048), (64, 5128, 768), (200, 1552, 384), (130, 2048, 5120)])
+def test_tcgen05_gemm_bf16(M, N, K):
+    """kind::f16 variant (bf16 weights in the GEMV tile layout, bf16 activations, fp32 accumulation in TMEM)."""
+    F = _F()
+    W = F.LinearW(_rand_w(N, K, seed=41), False)
+    x = (torch.randn(M, K, device="cuda") * 1.5).to(BF16)
+    ref = x.float() @ W.dense().float().t()
+    lg = F.gemm_bf16(W, x, epi=F.GEPI_F32)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(lg, ref, rtol=1e-3, atol=1e-2)
+    assert torch.equal(lg, F.gemm_bf16(W, x, epi=F.GEPI_F32))
+    y = F.gemm_bf16(W, x)
+    torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=3e-2 if K < 2048 else 8e-2)
+    r = torch.randn(M, N, device="cuda").to(BF16)
+    y2 = F.gemm_bf16(W, x, epi=F.GEPI_ROWPAR, resid=r)
+    torch.testing.assert_close(y2.float(), r.float() + ref, rtol=2e-2, atol=4e-2 if K < 2048 else 9e-2)
+    y3 = F.gemm_bf16(W, x, epi=F.GEPI_SWIGLU)
+    gu = ref.to(BF16).float()
+    torch.testing.assert_close(y3.float(), torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2], rtol=3e-2,
+                               atol=0.3 if K < 2048 else 0.6)

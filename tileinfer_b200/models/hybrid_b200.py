@@ -115,7 +115,7 @@ class _ModelBase:
         self._launches = 0
         self._pending, self._pending_wt = [], 0
         self.chain = os.environ.get("TI_GEMV_CHAIN", "1") != "0"
-        self.gemm_min_rows = int(os.environ.get("TI_GEMM_MIN_ROWS", "16"))   # more rows than this: tcgen05 GEMM
+        self.gemm_min_rows = int(os.environ.get("TI_GEMM_MIN_ROWS", "8"))    # more rows than this: tcgen05 GEMM
 
     # ------------------------------------------------------------------ caches
     def weight_bytes(self) -> int:
@@ -211,16 +211,29 @@ class _StepMixin:
 
     # ------------------------------------------------------------------ launches
     def _gemm(self, W: LinearW, x, out, M, *, epi, norm_w=None, resid=None):
-        """Prefill path (many rows): limb planes of x (RMSNorm fused), then the tcgen05 GEMM."""
+        """Many rows (prefill, batched decode): the tcgen05 GEMM.  int8 weights: limb planes of x first
+        (RMSNorm fused); bf16 weights: RMSNorm kernel first when the product wants normalised input."""
         self._flush()
-        limbs = F.quant_rows(x[:M], norm_w=norm_w, eps=self.cfg.rms_eps)
-        gepi = {EPI_STORE: F.GEPI_STORE, EPI_SWIGLU: F.GEPI_SWIGLU, EPI_ROWPAR: F.GEPI_ROWPAR}[epi]
-        F.gemm_w8a16(W, limbs, out=out[:M], epi=gepi, resid=None if resid is None else resid[:M])
-        self._launches += 2
+        gepi = {EPI_STORE: F.GEPI_STORE, EPI_SWIGLU: F.GEPI_SWIGLU, EPI_ROWPAR: F.GEPI_ROWPAR, EPI_F32: F.GEPI_F32}[epi]
+        r = None if resid is None else resid[:M]
+        if W.wt == F.W_INT8:
+            limbs = F.quant_rows(x[:M], norm_w=norm_w, eps=self.cfg.rms_eps)
+            F.gemm_w8a16(W, limbs, out=out[:M], epi=gepi, resid=r)
+            self._launches += 2
+            return
+        xs = x[:M]
+        if norm_w is not None:
+            xs = F.rmsnorm(xs, norm_w, self.cfg.rms_eps)
+            self._launches += 1
+        elif xs.stride(0) != W.K:
+            xs = xs.contiguous()
+            self._launches += 1
+        F.gemm_bf16(W, xs, out=out[:M], epi=gepi, resid=r)
+        self._launches += 1
 
     def _gemv(self, W: LinearW, x, out, M, *, xmode, epi, norm_w=None, resid=None, ldo=None):
         """y = x W^T in row chunks of 16; counts launches; assigns collective order numbers."""
-        if M > self.gemm_min_rows and W.wt == F.W_INT8 and epi != EPI_F32 and not (epi == EPI_ROWPAR and self.tp > 1):
+        if M > self.gemm_min_rows and (W.wt == F.W_BF16 or epi != EPI_F32) and not (epi == EPI_ROWPAR and self.tp > 1):
             return self._gemm(W, x, out, M, epi=epi, norm_w=norm_w if xmode == XNORM else None, resid=resid)
         step = F.max_rows(W.wt, xmode, W.K)
         for m0 in range(0, M, step):
@@ -252,7 +265,11 @@ class _StepMixin:
 
     def _rowpar(self, W: LinearW, x, resid, out, M):
         """Row-parallel projection + all-reduce + residual add -> out."""
-        if self.tp > 1 and M > self.gemm_min_rows and W.wt == F.W_INT8:
+        # Under tensor parallelism, steps of up to m_cap rows (every decode bucket, so everything a CUDA graph
+        # captures) keep the fused peer-memory all-reduce of the GEMV; only larger (eager prefill) steps take the
+        # tcgen05 GEMM followed by an NCCL all-reduce.
+        fused_cap = self.peer.m_cap if self.peer is not None else self.gemm_min_rows
+        if self.tp > 1 and M > max(fused_cap, self.gemm_min_rows):
             # prefill under tensor parallelism: tcgen05 GEMM to a bf16 partial, NCCL all-reduce, residual add
             part = torch.empty(M, W.N, dtype=BF16, device=self.dev)
             self._gemm(W, x, part, M, epi=EPI_STORE)

@@ -7,7 +7,8 @@
 // replaces kernels/causal_conv1d.py:60-115 and the chunk kernel of
 // kernels/gated_delta_rule_prefill.py:28-120, which drops the (v - S^T k) correction.  Here prefill
 // runs the same exact recurrence token by token with the state held in registers, so a prompt
-// processed in one piece, in chunks, or one token at a time gives the same state.
+// processed in one piece, in chunks, or one token at a time gives the same state; everything that is not
+// the recurrence itself (conv, norms, gates, output norm) is done for 16 tokens at a time.
 //
 // Mapping: one block per (v-head, sequence); thread = (column c of the state, quarter dg of the
 // key dimension) with the four quarters of a column in adjacent lanes, so both matrix-vector
@@ -45,13 +46,24 @@ template <typename ST> TI_DEVICE void st_state(ST* p, float v);
 template <> TI_DEVICE void st_state<float>(float* p, float v) { *p = v; }
 template <> TI_DEVICE void st_state<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
+// Tokens are processed in tiles of kTT.  Per tile: (1) every conv channel runs its window over the tile's tokens
+// (independent global loads, no synchronisation) and the per-token scalars (q/k norms, decay, beta) are worked
+// out in parallel; (2) the recurrence walks the tile token by token out of shared memory: two matrix-vector
+// products per token, reduced with warp shuffles, nothing else on the serial path; (3) the gated norm and the
+// output are again parallel over the tile.  The arithmetic of a token does not depend on the tiling.
+constexpr int kTT = 16;
+
 template <int DK, int DV, typename ST>
 __global__ void __launch_bounds__(DV * 4) gdn_kernel(const __grid_constant__ GdnParams p) {
   constexpr int DPT = DK / 4;           // state elements per thread
   constexpr int NCH = 2 * DK + DV;      // conv channels this block needs
   constexpr int NW = DV * 4 / 32;
   static_assert(NCH <= DV * 4, "one thread per conv channel");
-  __shared__ float qs[DK], ks[DK], vs[DV], red[NW];
+  // q/k rows are padded by 4 floats per quarter so that the four quarters (lanes dg = 0..3 read different
+  // quarters at the same time) fall into different banks
+  constexpr int DKP = DK + 16;
+  __shared__ __align__(16) float qs[kTT][DKP], ks[kTT][DKP], vs[kTT][DV];     // vs holds v, then the un-normalised output
+  __shared__ float qn_s[kTT], kn_s[kTT], decay_s[kTT], beta_s[kTT], rr_s[kTT];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int c = tid >> 2, dg = tid & 3;
@@ -85,74 +97,107 @@ __global__ void __launch_bounds__(DV * 4) gdn_kernel(const __grid_constant__ Gdn
   const int bcol = 2 * p.hk * DK + 2 * p.hv * DV + vh;
   const int acol = bcol + p.hv;
   const float neg_a = p.neg_a_exp[vh], dtb = p.dt_bias[vh];
-  const float nw = p.norm_w[c];
   const float qscale = rsqrtf((float)DK);
   pdl_trigger();
   pdl_wait();                                    // `proj` comes from the preceding projection kernel
 
-  for (int tok = t0; tok < t1; ++tok) {
-    const __nv_bfloat16* row = p.proj + (size_t)tok * p.ld;
+  for (int tile0 = t0; tile0 < t1; tile0 += kTT) {
+    const int nt = min(kTT, t1 - tile0);
+    // ---- (1a) conv + SiLU of every channel over the tile
     if (tid < NCH) {
-      const float x3 = __bfloat162float(row[col]);
-      const float y = silu_f(cw0 * x0 + cw1 * x1 + cw2 * x2 + cw3 * x3);
-      x0 = x1; x1 = x2; x2 = x3;
-      if (tid < DK) qs[tid] = y;
-      else if (tid < 2 * DK) ks[tid - DK] = y;
-      else vs[tid - 2 * DK] = y;
-    }
-    __syncthreads();
-    float sq = 0.f, sk = 0.f;
-    for (int i = lane; i < DK; i += 32) { sq += qs[i] * qs[i]; sk += ks[i] * ks[i]; }
-    sq = warp_sum(sq);
-    sk = warp_sum(sk);
-    const float qn = rsqrtf(sq + 1e-6f) * qscale, kn = rsqrtf(sk + 1e-6f);
-    const float a = __bfloat162float(row[acol]) + dtb;
-    const float sp = a > 20.f ? a : log1pf(__expf(a));
-    const float decay = __expf(neg_a * sp);
-    const float beta = sigmoid_f(__bfloat162float(row[bcol]));
-
-    float kv = 0.f;
+      float xin[kTT];
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) { S[i] *= decay; kv += S[i] * ks[dg * DPT + i]; }
-    kv += __shfl_xor_sync(0xffffffffu, kv, 1);
-    kv += __shfl_xor_sync(0xffffffffu, kv, 2);
-    const float delta = (vs[c] - kv * kn) * beta;
-    const float kd = kn * delta;
-    float o = 0.f;
+      for (int j = 0; j < kTT; ++j)
+        xin[j] = j < nt ? __bfloat162float(p.proj[(size_t)(tile0 + j) * p.ld + col]) : 0.f;
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) { S[i] += ks[dg * DPT + i] * kd; o += S[i] * qs[dg * DPT + i]; }
-    o += __shfl_xor_sync(0xffffffffu, o, 1);
-    o += __shfl_xor_sync(0xffffffffu, o, 2);
-    o *= qn;
-
-    float o2 = dg == 0 ? o * o : 0.f;
-    o2 = warp_sum(o2);
-    if (lane == 0) red[warp] = o2;
-    __syncthreads();
-    float tot = 0.f;
-#pragma unroll
-    for (int w = 0; w < NW; ++w) tot += red[w];
-    const float rr = rsqrtf(tot / (float)DV + p.eps);
-    if (dg == 0) {
-      const float z = __bfloat162float(row[zcol + c]);
-      p.out[(size_t)tok * p.hv * DV + vh * DV + c] = __float2bfloat16_rn(o * rr * nw * silu_f(z));
-    }
-    if (p.snap_rel != nullptr) {
-      const int done = tok - t0 + 1;
-      for (int j = 0; j < p.num_snap; ++j) {
-        if (p.snap_rel[s * p.num_snap + j] != done) continue;
-        float* dst = p.snap_state + (((size_t)s * p.num_snap + j) * p.hv + vh) * DK * DV;
-#pragma unroll
-        for (int i = 0; i < DPT; ++i) dst[(size_t)(dg * DPT + i) * DV + c] = S[i];
-        if (tid < NCH) {
-          __nv_bfloat16* dc = p.snap_conv + (((size_t)s * p.num_snap + j) * p.hv + vh) * 3 * NCH;
-          dc[tid] = __float2bfloat16_rn(x0);
-          dc[NCH + tid] = __float2bfloat16_rn(x1);
-          dc[2 * NCH + tid] = __float2bfloat16_rn(x2);
+      for (int j = 0; j < kTT; ++j) {
+        if (j < nt) {
+          const float x3 = xin[j];
+          const float y = silu_f(cw0 * x0 + cw1 * x1 + cw2 * x2 + cw3 * x3);
+          x0 = x1; x1 = x2; x2 = x3;
+          if (tid < DK) qs[j][tid + 4 * (tid / DPT)] = y;
+          else if (tid < 2 * DK) ks[j][(tid - DK) + 4 * ((tid - DK) / DPT)] = y;
+          else vs[j][tid - 2 * DK] = y;
+          if (p.snap_rel != nullptr) {             // conv window after token (tile0 + j)
+            const int done = tile0 + j - t0 + 1;
+            for (int q = 0; q < p.num_snap; ++q) {
+              if (p.snap_rel[s * p.num_snap + q] != done) continue;
+              __nv_bfloat16* dc = p.snap_conv + (((size_t)s * p.num_snap + q) * p.hv + vh) * 3 * NCH;
+              dc[tid] = __float2bfloat16_rn(x0);
+              dc[NCH + tid] = __float2bfloat16_rn(x1);
+              dc[2 * NCH + tid] = __float2bfloat16_rn(x2);
+            }
+          }
         }
       }
     }
     __syncthreads();
+    // ---- (1b) per-token scalars: a warp per token
+    for (int j = warp; j < nt; j += NW) {
+      const __nv_bfloat16* row = p.proj + (size_t)(tile0 + j) * p.ld;
+      float sq = 0.f, sk = 0.f;
+      for (int i = lane; i < DK; i += 32) {
+        const float a = qs[j][i + 4 * (i / DPT)], b = ks[j][i + 4 * (i / DPT)];
+        sq += a * a;
+        sk += b * b;
+      }
+      sq = warp_sum(sq);
+      sk = warp_sum(sk);
+      if (lane == 0) {
+        qn_s[j] = rsqrtf(sq + 1e-6f) * qscale;
+        kn_s[j] = rsqrtf(sk + 1e-6f);
+        const float a = __bfloat162float(row[acol]) + dtb;
+        const float sp = a > 20.f ? a : log1pf(__expf(a));
+        decay_s[j] = __expf(neg_a * sp);
+        beta_s[j] = sigmoid_f(__bfloat162float(row[bcol]));
+      }
+    }
+    __syncthreads();
+    // ---- (2) the recurrence, token by token, out of shared memory
+    for (int j = 0; j < nt; ++j) {
+      const float decay = decay_s[j], kn = kn_s[j];
+      const float* kj = ks[j] + dg * (DPT + 4);
+      const float* qj = qs[j] + dg * (DPT + 4);
+      float kv = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) { S[i] *= decay; kv += S[i] * kj[i]; }
+      kv += __shfl_xor_sync(0xffffffffu, kv, 1);
+      kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+      const float delta = (vs[j][c] - kv * kn) * beta_s[j];
+      const float kd = kn * delta;
+      float o = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) { S[i] += kj[i] * kd; o += S[i] * qj[i]; }
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      __syncwarp();                                // all four lanes of the column have read vs[j][c]
+      if (dg == 0) vs[j][c] = o * qn_s[j];
+      if (p.snap_rel != nullptr) {
+        const int done = tile0 + j - t0 + 1;
+        for (int q = 0; q < p.num_snap; ++q) {
+          if (p.snap_rel[s * p.num_snap + q] != done) continue;
+          float* dst = p.snap_state + (((size_t)s * p.num_snap + q) * p.hv + vh) * DK * DV;
+#pragma unroll
+          for (int i = 0; i < DPT; ++i) dst[(size_t)(dg * DPT + i) * DV + c] = S[i];
+        }
+      }
+    }
+    __syncthreads();
+    // ---- (3) gated RMSNorm * silu(z): a warp per token for the statistics, then all threads for the output
+    for (int j = warp; j < nt; j += NW) {
+      float o2 = 0.f;
+      for (int i = lane; i < DV; i += 32) o2 += vs[j][i] * vs[j][i];
+      o2 = warp_sum(o2);
+      if (lane == 0) rr_s[j] = rsqrtf(o2 / (float)DV + p.eps);
+    }
+    __syncthreads();
+    for (int e = tid; e < nt * DV; e += DV * 4) {
+      const int j = e / DV, cc = e - j * DV;
+      const size_t tok = (size_t)(tile0 + j);
+      const float z = __bfloat162float(p.proj[tok * p.ld + zcol + cc]);
+      p.out[tok * p.hv * DV + vh * DV + cc] = __float2bfloat16_rn(vs[j][cc] * rr_s[j] * p.norm_w[cc] * silu_f(z));
+    }
+    __syncthreads();                               // the tile buffers are reused
   }
 
 #pragma unroll

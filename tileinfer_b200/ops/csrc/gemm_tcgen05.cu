@@ -37,18 +37,18 @@ constexpr int kBK = 64;           // bytes of k per stage (one 64-byte swizzle r
 constexpr int kStageA = kBM * kBK;                 // 8 KB of weights per stage
 constexpr int kGemmThreads = 192;
 constexpr int kGemmRingBytes = 192 * 1024;
-// BN = tokens per CTA (TMEM columns per accumulator)
-template <int BN> struct GemmGeom {
-  static constexpr int kStageB = BN * kBK;                         // one limb plane
-  static constexpr int kStageBytes = kStageA + 2 * kStageB;
-  static constexpr int kStages = kGemmRingBytes / kStageBytes;     // 128: 8, 64: 12, 32: 16
+// BN = tokens per CTA (TMEM columns per accumulator); BF16: bf16 weights and activations (one plane, one accumulator)
+template <int BN, bool BF16> struct GemmGeom {
+  static constexpr int kStageB = BN * kBK;                         // one limb plane / the bf16 activation tile
+  static constexpr int kStageBytes = kStageA + (BF16 ? 1 : 2) * kStageB;
+  static constexpr int kStages = kGemmRingBytes / kStageBytes < 24 ? kGemmRingBytes / kStageBytes : 24;
   static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 16 * kStages + 64 + 1024;
 };
 constexpr unsigned long long kGemmWaitNs = 2000000000ull;
 
 struct GemmParams {
   alignas(64) CUtensorMap map_w;   // uint8 [n_tiles][KB][8][64], box {64, 8, 1, 16}, 64B swizzle
-  alignas(64) CUtensorMap map_xh;  // uint8 [M][K], box {64, 128}, 64B swizzle
+  alignas(64) CUtensorMap map_xh;  // uint8 [M][K], box {64, BN}, 64B swizzle (bf16 mode: the activations, [M][2K] bytes)
   alignas(64) CUtensorMap map_xl;
   const float* xscale;             // [M] value of one fixed-point unit (2^(e-14))
   const __nv_bfloat16* wscale;     // [N_pad]
@@ -98,6 +98,14 @@ TI_DEVICE void umma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32
       : "memory");
 }
 // arrives on `bar` once all tcgen05.mma issued so far by this thread have completed
+// the same with bf16 operands and fp32 accumulation
+TI_DEVICE void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 TI_DEVICE void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
@@ -129,7 +137,12 @@ template <int BN> TI_DEVICE constexpr uint32_t idesc_i8(bool b_signed) {
   return (2u << 4) | (1u << 7) | ((b_signed ? 1u : 0u) << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
 
-enum { GEPI_STORE = 0, GEPI_SWIGLU = 1, GEPI_ROWPAR = 2 };
+// kind::f16 instruction descriptor: D = f32, A = B = bf16 (K-major), M = 128, N = BN
+template <int BN> TI_DEVICE constexpr uint32_t idesc_bf16() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+enum { GEPI_STORE = 0, GEPI_SWIGLU = 1, GEPI_ROWPAR = 2, GEPI_F32 = 3 };
 
 // value of output (token m, weight row n) -> fused epilogue
 TI_DEVICE void gemm_epilogue(const GemmParams& p, int m, int n, int lane, float v) {
@@ -141,6 +154,10 @@ TI_DEVICE void gemm_epilogue(const GemmParams& p, int m, int n, int lane, float 
       static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] = __float2bfloat16_rn(silu_f(gate) * up);
     }
   } else if (n < p.N) {
+    if (p.epi == GEPI_F32) {
+      static_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+      return;
+    }
     float r = v;
     if (p.epi == GEPI_ROWPAR) r += __bfloat162float(p.resid[(size_t)m * p.N + n]);
     static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(r);
@@ -155,6 +172,10 @@ TI_DEVICE void gemm_epilogue4(const GemmParams& p, int m, int n, float4 v) {
         pack_bf16(silu_f(g0) * u0, silu_f(g1) * u1);
     return;
   }
+  if (p.epi == GEPI_F32) {
+    *reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)m * p.ldo + n) = v;
+    return;
+  }
   if (p.epi == GEPI_ROWPAR) {
     const uint2 r = *reinterpret_cast<const uint2*>(p.resid + (size_t)m * p.N + n);
     v.x += bf16lo(r.x);
@@ -166,9 +187,9 @@ TI_DEVICE void gemm_epilogue4(const GemmParams& p, int m, int n, float4 v) {
       make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
 }
 
-template <int BN>
+template <int BN, bool BF16>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w8a16_kernel(const __grid_constant__ GemmParams p) {
-  using G = GemmGeom<BN>;
+  using G = GemmGeom<BN, BF16>;
   constexpr int kStages = G::kStages, kStageBytes = G::kStageBytes, kStageB = G::kStageB;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte aligned stage buffers (the swizzle pattern repeats every 512 bytes)
@@ -183,7 +204,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w8a16_kernel(const __gri
   const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z, S = gridDim.z;
   const int KB = p.K / kBK;
   const int kb0 = split * p.kb_per_split, kb1 = min(KB, kb0 + p.kb_per_split);
-  constexpr uint32_t kCols = 2 * BN < 32 ? 32 : 2 * BN;          // TMEM allocation: a power of two >= 32
+  constexpr uint32_t kCols = (BF16 ? 1 : 2) * BN < 32 ? 32 : (BF16 ? 1 : 2) * BN;   // TMEM allocation: a power of two >= 32
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -215,7 +236,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w8a16_kernel(const __gri
         mbar_expect_tx(full0 + 8 * s, kStageBytes);
         tma_load_4d(dst, &p.map_w, 0, 0, kb, tile_n * (kBM / 8), full0 + 8 * s);
         tma_load_2d(dst + kStageA, &p.map_xh, kb * kBK, tile_m * BN, full0 + 8 * s);
-        tma_load_2d(dst + kStageA + kStageB, &p.map_xl, kb * kBK, tile_m * BN, full0 + 8 * s);
+        if (!BF16) tma_load_2d(dst + kStageA + kStageB, &p.map_xl, kb * kBK, tile_m * BN, full0 + 8 * s);
       }
     }
   } else if (warp == 1) {
@@ -232,8 +253,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w8a16_kernel(const __gri
         for (int ks = 0; ks < 2; ++ks) {                          // two 32-byte k steps inside the 64-byte slab
           const uint64_t da = smem_desc_sw64(a + ks * 32);
           const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
-          umma_i8(tmem_base, da, smem_desc_sw64(bh + ks * 32), idesc_i8<BN>(true), acc);
-          umma_i8(tmem_base + BN, da, smem_desc_sw64(bl + ks * 32), idesc_i8<BN>(false), acc);
+          if (BF16) {
+            umma_bf16(tmem_base, da, smem_desc_sw64(bh + ks * 32), idesc_bf16<BN>(), acc);
+          } else {
+            umma_i8(tmem_base, da, smem_desc_sw64(bh + ks * 32), idesc_i8<BN>(true), acc);
+            umma_i8(tmem_base + BN, da, smem_desc_sw64(bl + ks * 32), idesc_i8<BN>(false), acc);
+          }
         }
         umma_commit(empty0 + 8 * s);                              // stage may be refilled once these MMAs are done
       }
@@ -245,18 +270,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w8a16_kernel(const __gri
     const bool ok = mbar_wait(acc_bar, 0, 2 * kGemmWaitNs, p.status);
     tc_fence_after();
     const int n = tile_n * kBM + quarter * 32 + lane;             // weight row == output feature of this lane
-    const float ws = (ok && n < p.N) ? __bfloat162float(p.wscale[n]) : 0.f;
+    const float ws = (ok && n < p.N) ? (BF16 ? 1.f : __bfloat162float(p.wscale[n])) : 0.f;
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     for (int c0 = 0; c0 < BN; c0 += 32) {
       uint32_t hi[32], lo[32];
       tmem_ld32(taddr + c0, hi);
-      tmem_ld32(taddr + BN + c0, lo);
+      if (!BF16) tmem_ld32(taddr + BN + c0, lo);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const int m = tile_m * BN + c0 + j;                       // token (uniform over the warp)
         if (m >= p.M) break;
-        const float v = ((float)(int)hi[j] * 256.f + (float)(int)lo[j]) * p.xscale[m] * ws;
+        const float v = BF16 ? __uint_as_float(hi[j]) * ws
+                             : ((float)(int)hi[j] * 256.f + (float)(int)lo[j]) * p.xscale[m] * ws;
         if (S == 1) gemm_epilogue(p, m, n, lane, v);
         else if (n < p.N) p.part[((size_t)split * p.M + m) * p.N + n] = v;
       }
@@ -429,16 +455,31 @@ static int cached_map(CUtensorMap* dst, const void* base, int d0, int d1, int bo
   return 0;
 }
 
-template <int BN>
+template <int BN, bool BF16>
 static int launch_gemm(const GemmParams& p, dim3 grid, cudaStream_t st) {
   static bool configured = false;
-  auto k = gemm_w8a16_kernel<BN>;
+  auto k = gemm_w8a16_kernel<BN, BF16>;
   if (!configured) {
-    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmGeom<BN>::kSmem);
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmGeom<BN, BF16>::kSmem);
     configured = true;
   }
-  k<<<grid, kGemmThreads, GemmGeom<BN>::kSmem, st>>>(p);
+  k<<<grid, kGemmThreads, GemmGeom<BN, BF16>::kSmem, st>>>(p);
   return (int)cudaGetLastError();
+}
+
+// k split that fills the 148 SMs when there are few output tiles (at least 16 slabs per slice); sets kb_per_split
+static int plan_split(GemmParams& p, int KB, int tiles, int M, int N, int ldo, void* part, size_t part_bytes,
+                      void* tile_count, int n_count) {
+  int S = 1;
+  if (part != nullptr && tile_count != nullptr && tiles < 120 && N % 4 == 0 && ldo % 4 == 0) {
+    S = std::min(std::min(148 / tiles, KB / 16), 16);
+    while (S > 1 && ((size_t)S * M * N * 4 > part_bytes || tiles > n_count)) --S;
+    if (S < 1) S = 1;
+  }
+  p.kb_per_split = (KB + S - 1) / S;
+  p.part = (float*)part;
+  p.tile_count = (unsigned*)tile_count;
+  return (KB + p.kb_per_split - 1) / p.kb_per_split;           // no empty slice
 }
 
 }  // namespace ti
@@ -482,22 +523,42 @@ int ti_gemm_w8a16(const void* w, const void* wscale, int n_tiles, int N, int K, 
   p.ldo = ldo;
   p.epi = epi;
   const int tiles_n = (n_tiles * 8 + ti::kBM - 1) / ti::kBM, tiles_m = (M + BN - 1) / BN;
-  // k split: fill the 148 SMs when there are few output tiles, at least 16 slabs per slice
-  int S = 1;
-  if (part != nullptr && tile_count != nullptr && tiles_n * tiles_m < 120 && N % 4 == 0 && ldo % 4 == 0) {
-    S = std::min(std::min(148 / (tiles_n * tiles_m), KB / 16), 16);
-    while (S > 1 && ((size_t)S * M * N * 4 > part_bytes || tiles_n * tiles_m > n_count)) --S;
-    if (S < 1) S = 1;
-  }
-  p.kb_per_split = (KB + S - 1) / S;
-  S = (KB + p.kb_per_split - 1) / p.kb_per_split;              // no empty slice
-  p.part = (float*)part;
-  p.tile_count = (unsigned*)tile_count;
+  const int S = ti::plan_split(p, KB, tiles_n * tiles_m, M, N, ldo, part, part_bytes, tile_count, n_count);
   dim3 grid(tiles_n, tiles_m, S);
   cudaStream_t st = (cudaStream_t)stream;
-  if (BN == 32) return ti::launch_gemm<32>(p, grid, st);
-  if (BN == 64) return ti::launch_gemm<64>(p, grid, st);
-  return ti::launch_gemm<128>(p, grid, st);
+  if (BN == 32) return ti::launch_gemm<32, false>(p, grid, st);
+  if (BN == 64) return ti::launch_gemm<64, false>(p, grid, st);
+  return ti::launch_gemm<128, false>(p, grid, st);
+}
+
+// The same for bf16 weights tiled [n_tiles][K/32][8][32] (lm_head, unquantised mode) and bf16 activations x [M][K]
+// (contiguous rows): tcgen05.mma kind::f16, fp32 accumulation.  epi 3 stores fp32 (logits).
+int ti_gemm_bf16(const void* w, int n_tiles, int N, int K, const void* x, int M, const void* resid, void* out, int ldo,
+                 int epi, void* status, void* part, size_t part_bytes, void* tile_count, int n_count, void* stream) {
+  if (M <= 0) return 0;
+  if (K % 32 || N < 1 || epi < 0 || epi > 3) return -2;
+  ti::GemmParams p = {};
+  const int KB = K / 32;                                       // 64-byte slabs
+  const int BN = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
+  int rc = ti::cached_map(&p.map_w, w, KB, n_tiles, 0);
+  if (rc) return rc;
+  rc = ti::cached_map(&p.map_xh, x, 2 * K, M, BN);
+  if (rc) return rc;
+  p.resid = (const __nv_bfloat16*)resid;
+  p.out = out;
+  p.status = (unsigned*)status;
+  p.M = M;
+  p.N = N;
+  p.K = 2 * K;                                                 // bytes of k: the kernel counts 64-byte slabs
+  p.ldo = ldo;
+  p.epi = epi;
+  const int tiles_n = (n_tiles * 8 + ti::kBM - 1) / ti::kBM, tiles_m = (M + BN - 1) / BN;
+  const int S = ti::plan_split(p, KB, tiles_n * tiles_m, M, N, ldo, part, part_bytes, tile_count, n_count);
+  dim3 grid(tiles_n, tiles_m, S);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (BN == 32) return ti::launch_gemm<32, true>(p, grid, st);
+  if (BN == 64) return ti::launch_gemm<64, true>(p, grid, st);
+  return ti::launch_gemm<128, true>(p, grid, st);
 }
 
 }  // extern "C"

@@ -75,6 +75,7 @@ _l.register("ti_memset_async", _I, [_P, _I, ctypes.c_size_t, _P])
 _l.register("ti_wait_flag_probe", _I, [_P, ctypes.c_uint, ctypes.c_ulonglong, _P, _P, _P])
 
 _l.register("ti_quant_rows", _I, [_P, _I, _P, _F, _I, _I, _P, _P, _P, _P])
+_l.register("ti_gemm_bf16", _I, [_P, _I, _I, _I, _P, _I, _P, _P, _I, _I, _P, _P, ctypes.c_size_t, _P, _I, _P])
 _l.register("ti_gemm_w8a16", _I, [_P, _P, _I, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _P, _P, ctypes.c_size_t, _P, _I, _P])
 
 _checked = False
@@ -358,7 +359,7 @@ def topk(p: TopkParams):
 
 
 # ------------------------------------------------------------------------------------ prefill GEMM (tcgen05)
-GEPI_STORE, GEPI_SWIGLU, GEPI_ROWPAR = 0, 1, 2
+GEPI_STORE, GEPI_SWIGLU, GEPI_ROWPAR, GEPI_F32 = 0, 1, 2, 3
 
 
 class Limbs:
@@ -391,6 +392,20 @@ def gemm_w8a16(W: "LinearW", limbs: Limbs, *, out=None, epi=GEPI_STORE, resid=No
     check(L().ti_gemm_w8a16(ptr(W.tiles), ptr(W.scale), W.n_tiles, W.N, W.K, ptr(limbs.hi), ptr(limbs.lo),
                             ptr(limbs.scale), M, ptr(resid), ptr(out), out.stride(0), epi, status_ptr(), ptr(part),
                             part.numel() * 4, ptr(count), count.numel(), stream()), "ti_gemm_w8a16")
+    return out
+
+
+def gemm_bf16(W: "LinearW", x: torch.Tensor, *, out=None, epi=GEPI_STORE, resid=None) -> torch.Tensor:
+    """y = x W^T on the tcgen05 tensor cores (kind::f16) for bf16-tiled W and bf16 x [M, K] with contiguous rows.
+    epi GEPI_F32 stores fp32 (logits)."""
+    assert W.wt == W_BF16 and x.shape[1] == W.K and x.stride(1) == 1 and x.stride(0) == W.K and x.dtype == torch.bfloat16
+    M = x.shape[0]
+    if out is None:
+        cols = W.N // 2 if epi == GEPI_SWIGLU else W.N
+        out = torch.empty(M, cols, dtype=torch.float32 if epi == GEPI_F32 else torch.bfloat16, device=x.device)
+    part, count = _gemm_workspace(x.device)
+    check(L().ti_gemm_bf16(ptr(W.tiles), W.n_tiles, W.N, W.K, ptr(x), M, ptr(resid), ptr(out), out.stride(0), epi,
+                           status_ptr(), ptr(part), part.numel() * 4, ptr(count), count.numel(), stream()), "ti_gemm_bf16")
     return out
 
 
