@@ -267,8 +267,20 @@ def test_gdn_step_matches_recurrence(dk, hk, hv, state_bf16):
     p.state, p.conv_state, p.slots, p.cu, p.out = state.data_ptr(), cs.data_ptr(), slots.data_ptr(), cu.data_ptr(), out.data_ptr()
     p.snap_rel, p.snap_state, p.snap_conv, p.num_snap = snap_rel.data_ptr(), snap_state.data_ptr(), snap_conv.data_ptr(), 1
     p.ld, p.hk, p.hv, p.eps = ld, hk, hv, 1e-6
+    # the column-split (cluster) form first, on copies: it must agree with the one-block form
+    st2, cs2, out2 = state0.clone(), cs0.clone(), torch.zeros_like(out)
+    sn2, sc2 = torch.zeros_like(snap_state), torch.zeros_like(snap_conv)
+    p.state, p.conv_state, p.out, p.snap_state, p.snap_conv = st2.data_ptr(), cs2.data_ptr(), out2.data_ptr(), sn2.data_ptr(), sc2.data_ptr()
+    F.gdn_step(p, S, dk, dv, state_bf16, split=True)
+    p.state, p.conv_state, p.out = state.data_ptr(), cs.data_ptr(), out.data_ptr()
+    p.snap_state, p.snap_conv = snap_state.data_ptr(), snap_conv.data_ptr()
     F.gdn_step(p, S, dk, dv, state_bf16)
     torch.cuda.synchronize()
+    # same arithmetic per token; the two instantiations may contract a multiply-add differently (one bf16 ulp)
+    torch.testing.assert_close(out.float(), out2.float(), rtol=8e-3, atol=2e-3)
+    torch.testing.assert_close(state.float(), st2.float(), rtol=1e-2 if state_bf16 else 1e-5, atol=1e-3 if state_bf16 else 1e-6)
+    assert torch.equal(cs, cs2) and torch.equal(snap_conv, sc2)
+    torch.testing.assert_close(snap_state, sn2, rtol=1e-5, atol=1e-6)
     tol = dict(rtol=3e-2, atol=3e-2)
     for s in range(S):
         t0, t1, slot = int(cu[s]), int(cu[s + 1]), int(slots[s])

@@ -19,6 +19,8 @@ def prompt(n, seed):
 
 
 def main():
+    import faulthandler
+    faulthandler.dump_traceback_later(int(os.environ.get("TI_TEST_WATCHDOG_S", "150")), exit=True)   # a stuck rank says where
     fused = os.environ.get("TI_TEST_FUSED", "1") == "1"
     tp = int(os.environ["WORLD_SIZE"])
     llm = LLM("preset:tiny-hybrid-tp", quantization="w8a16", tp_size=tp, num_kvcache_blocks=128, max_num_seqs=8,
@@ -37,9 +39,13 @@ def main():
     if llm.comm.rank == 0:
         print("TP_RESULT " + json.dumps({"ranks": box, "prompts": prompts, "fused": fused}), flush=True)
     dist.barrier()
+    # graphs that captured collectives go before the communicator does
+    llm.model_runner.model.graphs.clear()
+    torch.cuda.synchronize()
     if llm.model_runner.model.peer is not None:
         llm.model_runner.model.peer.close()
     dist.destroy_process_group()
+    faulthandler.cancel_dump_traceback_later()
 
 
 if __name__ == "__main__":

@@ -115,6 +115,7 @@ class _ModelBase:
         self._launches = 0
         self._pending, self._pending_wt = [], 0
         self.chain = os.environ.get("TI_GEMV_CHAIN", "1") != "0"
+        self.gdn_split = os.environ.get("TI_GDN_SPLIT", "0") == "1"   # prefill: a head's columns over a 4-block cluster
         self.gemm_min_rows = int(os.environ.get("TI_GEMM_MIN_ROWS", "8"))    # more rows than this: tcgen05 GEMM
 
     # ------------------------------------------------------------------ caches
@@ -310,7 +311,7 @@ class _StepMixin:
                     p.snap_rel, p.num_snap = ptr(x.snap_rel), x.num_snap
                     p.snap_state, p.snap_conv = ptr(x.snap_state[ig]), ptr(x.snap_conv[ig])
                 self._flush()
-                F.gdn_step(p, S, self.dk, self.dv, self.state_bf16)
+                F.gdn_step(p, S, self.dk, self.dv, self.state_bf16, split=self.gdn_split and T > S)
                 self._launches += 1
                 # the kernel writes [T, hv*dv] densely
                 mix = x.mix.view(-1)[:T * self.hv * self.dv].view(T, self.hv * self.dv)

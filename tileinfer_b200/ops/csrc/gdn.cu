@@ -10,10 +10,10 @@
 // processed in one piece, in chunks, or one token at a time gives the same state; everything that is not
 // the recurrence itself (conv, norms, gates, output norm) is done for 16 tokens at a time.
 //
-// Mapping: one block per (v-head, sequence); thread = (column c of the state, quarter dg of the
-// key dimension) with the four quarters of a column in adjacent lanes, so both matrix-vector
-// products of a step reduce with two warp shuffles.  A state column never interacts with other
-// columns, only the gated norm needs a block-wide sum.
+// Mapping: one block (decode) or a cluster of blocks (prefill) per (v-head, sequence); thread = (column c of
+// the state, quarter dg of the key dimension) with the four quarters of a column in adjacent lanes, so both
+// matrix-vector products of a step reduce with two warp shuffles.  A state column never interacts with other
+// columns, only the gated norm needs a sum over the head.
 //
 // Conv history layout: [slot][v-head][3][2*DK + DV]; every v-head keeps its own copy of the q/k
 // history of the key head it shares, so blocks never write memory another block reads.
@@ -53,47 +53,81 @@ template <> TI_DEVICE void st_state<__nv_bfloat16>(__nv_bfloat16* p, float v) { 
 // output are again parallel over the tile.  The arithmetic of a token does not depend on the tiling.
 constexpr int kTT = 16;
 
-template <int DK, int DV, typename ST>
-__global__ void __launch_bounds__(DV * 4) gdn_kernel(const __grid_constant__ GdnParams p) {
+// NS = 1: one block per (v-head, sequence), DV*4 threads.  NS = 4 (prefill): the DV state columns of a head are
+// dealt to the NS blocks of a thread-block cluster (columns never interact); the only quantity that spans the
+// columns, the sum of squares of the gated norm, is exchanged through distributed shared memory once per tile.
+// Both forms add the same four 32-column partial sums in the same order.
+TI_DEVICE void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+TI_DEVICE float ld_cluster_f32(const float* local, int rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+template <int DK, int DV, typename ST, int NS>
+__global__ void __launch_bounds__(DV / NS * 4) gdn_kernel(const __grid_constant__ GdnParams p) {
   constexpr int DPT = DK / 4;           // state elements per thread
-  constexpr int NCH = 2 * DK + DV;      // conv channels this block needs
-  constexpr int NW = DV * 4 / 32;
-  static_assert(NCH <= DV * 4, "one thread per conv channel");
+  constexpr int CB = DV / NS;           // state columns of this block
+  constexpr int NT = CB * 4;            // threads
+  constexpr int NCH = 2 * DK + DV;      // conv channels of a head (layout of the conv history)
+  constexpr int NCHL = 2 * DK + CB;     // conv channels this block needs: q, k, its own v columns
+  constexpr int NCPT = (NCHL + NT - 1) / NT;   // channels per thread
+  constexpr int NW = NT / 32;
+  constexpr int NG = CB / 32;           // 32-column groups of this block (DV / 32 in total)
+  static_assert(CB % 32 == 0 && DV / 32 <= 8, "column groups");
   // q/k rows are padded by 4 floats per quarter so that the four quarters (lanes dg = 0..3 read different
   // quarters at the same time) fall into different banks
   constexpr int DKP = DK + 16;
-  __shared__ __align__(16) float qs[kTT][DKP], ks[kTT][DKP], vs[kTT][DV];     // vs holds v, then the un-normalised output
+  __shared__ __align__(16) float qs[kTT][DKP], ks[kTT][DKP], vs[kTT][CB];     // vs holds v, then the un-normalised output
   __shared__ float qn_s[kTT], kn_s[kTT], decay_s[kTT], beta_s[kTT], rr_s[kTT];
+  __shared__ float o2_s[2][kTT][NG];    // partial sums of squares per column group (double-buffered by tile)
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int c = tid >> 2, dg = tid & 3;
-  const int vh = blockIdx.x, s = blockIdx.y;
+  const int c = tid >> 2, dg = tid & 3;              // local column, k quarter
+  const int part = NS > 1 ? (int)(blockIdx.x % NS) : 0;
+  const int vh = blockIdx.x / NS, s = blockIdx.y;
   const int kh = vh / (p.hv / p.hk);
   // cu / slots are written by host copies that precede every kernel of the step; the recurrent state
   // and conv history were last written one step ago: all of this may be read before pdl_wait()
   const int t0 = p.cu ? p.cu[s] : s, t1 = p.cu ? p.cu[s + 1] : s + 1;
   const int slot = p.slots[s];
 
-  ST* Sp = static_cast<ST*>(p.state) + ((size_t)slot * p.hv + vh) * DK * DV;
-  float S[DPT];
+  ST* Sp = static_cast<ST*>(p.state) + ((size_t)slot * p.hv + vh) * DK * DV + part * CB;
+  float2 S2[DPT / 2];                  // S2[i] = state rows (dg*DPT + 2i, 2i+1) of column c
 #pragma unroll
-  for (int i = 0; i < DPT; ++i) S[i] = ld_state<ST>(Sp + (size_t)(dg * DPT + i) * DV + c);
-
-  // conv channel owned by this thread: column in `proj` and row of conv_w
-  __nv_bfloat16* cs = p.conv_state + ((size_t)slot * p.hv + vh) * 3 * NCH;
-  float x0 = 0.f, x1 = 0.f, x2 = 0.f, cw0 = 0.f, cw1 = 0.f, cw2 = 0.f, cw3 = 0.f;
-  int col = 0;
-  if (tid < NCH) {
-    if (tid < DK) col = kh * DK + tid;
-    else if (tid < 2 * DK) col = p.hk * DK + kh * DK + (tid - DK);
-    else col = 2 * p.hk * DK + vh * DV + (tid - 2 * DK);
-    const float4 w = *reinterpret_cast<const float4*>(p.conv_w + (size_t)col * 4);
-    cw0 = w.x; cw1 = w.y; cw2 = w.z; cw3 = w.w;
-    x0 = __bfloat162float(cs[tid]);
-    x1 = __bfloat162float(cs[NCH + tid]);
-    x2 = __bfloat162float(cs[2 * NCH + tid]);
+  for (int i = 0; i < DPT / 2; ++i) {
+    S2[i].x = ld_state<ST>(Sp + (size_t)(dg * DPT + 2 * i) * DV + c);
+    S2[i].y = ld_state<ST>(Sp + (size_t)(dg * DPT + 2 * i + 1) * DV + c);
   }
-  const int zcol = 2 * p.hk * DK + p.hv * DV + vh * DV;
+
+  // conv channels owned by this thread: local channel ch -> index in the head's history, column of `proj`
+  __nv_bfloat16* cs = p.conv_state + ((size_t)slot * p.hv + vh) * 3 * NCH;
+  float x0[NCPT], x1[NCPT], x2[NCPT], cw[NCPT][4];
+  int col[NCPT], hch[NCPT];
+#pragma unroll
+  for (int u = 0; u < NCPT; ++u) {
+    const int ch = tid + u * NT;
+    x0[u] = x1[u] = x2[u] = 0.f;
+    col[u] = hch[u] = 0;
+    cw[u][0] = cw[u][1] = cw[u][2] = cw[u][3] = 0.f;
+    if (ch < NCHL) {
+      if (ch < DK) { col[u] = kh * DK + ch; hch[u] = ch; }
+      else if (ch < 2 * DK) { col[u] = p.hk * DK + kh * DK + (ch - DK); hch[u] = ch; }
+      else { col[u] = 2 * p.hk * DK + vh * DV + part * CB + (ch - 2 * DK); hch[u] = 2 * DK + part * CB + (ch - 2 * DK); }
+      const float4 w = *reinterpret_cast<const float4*>(p.conv_w + (size_t)col[u] * 4);
+      cw[u][0] = w.x; cw[u][1] = w.y; cw[u][2] = w.z; cw[u][3] = w.w;
+      x0[u] = __bfloat162float(cs[hch[u]]);
+      x1[u] = __bfloat162float(cs[NCH + hch[u]]);
+      x2[u] = __bfloat162float(cs[2 * NCH + hch[u]]);
+    }
+  }
+  // q/k history is common to the blocks of a head: block 0 writes it back
+  const int zcol = 2 * p.hk * DK + p.hv * DV + vh * DV + part * CB;
   const int bcol = 2 * p.hk * DK + 2 * p.hv * DV + vh;
   const int acol = bcol + p.hv;
   const float neg_a = p.neg_a_exp[vh], dtb = p.dt_bias[vh];
@@ -101,31 +135,38 @@ __global__ void __launch_bounds__(DV * 4) gdn_kernel(const __grid_constant__ Gdn
   pdl_trigger();
   pdl_wait();                                    // `proj` comes from the preceding projection kernel
 
-  for (int tile0 = t0; tile0 < t1; tile0 += kTT) {
+  int tile_idx = 0;
+  for (int tile0 = t0; tile0 < t1; tile0 += kTT, ++tile_idx) {
     const int nt = min(kTT, t1 - tile0);
-    // ---- (1a) conv + SiLU of every channel over the tile
-    if (tid < NCH) {
-      float xin[kTT];
+    // ---- (1a) conv + SiLU of every channel over the tile (all loads of the tile are issued first)
+    float xin[NCPT][kTT];
+#pragma unroll
+    for (int u = 0; u < NCPT; ++u)
 #pragma unroll
       for (int j = 0; j < kTT; ++j)
-        xin[j] = j < nt ? __bfloat162float(p.proj[(size_t)(tile0 + j) * p.ld + col]) : 0.f;
+        xin[u][j] = (tid + u * NT < NCHL && j < nt) ? __bfloat162float(p.proj[(size_t)(tile0 + j) * p.ld + col[u]]) : 0.f;
 #pragma unroll
-      for (int j = 0; j < kTT; ++j) {
-        if (j < nt) {
-          const float x3 = xin[j];
-          const float y = silu_f(cw0 * x0 + cw1 * x1 + cw2 * x2 + cw3 * x3);
-          x0 = x1; x1 = x2; x2 = x3;
-          if (tid < DK) qs[j][tid + 4 * (tid / DPT)] = y;
-          else if (tid < 2 * DK) ks[j][(tid - DK) + 4 * ((tid - DK) / DPT)] = y;
-          else vs[j][tid - 2 * DK] = y;
-          if (p.snap_rel != nullptr) {             // conv window after token (tile0 + j)
-            const int done = tile0 + j - t0 + 1;
-            for (int q = 0; q < p.num_snap; ++q) {
-              if (p.snap_rel[s * p.num_snap + q] != done) continue;
-              __nv_bfloat16* dc = p.snap_conv + (((size_t)s * p.num_snap + q) * p.hv + vh) * 3 * NCH;
-              dc[tid] = __float2bfloat16_rn(x0);
-              dc[NCH + tid] = __float2bfloat16_rn(x1);
-              dc[2 * NCH + tid] = __float2bfloat16_rn(x2);
+    for (int u = 0; u < NCPT; ++u) {
+      const int ch = tid + u * NT;
+      if (ch < NCHL) {
+#pragma unroll
+        for (int j = 0; j < kTT; ++j) {
+          if (j < nt) {
+            const float x3 = xin[u][j];
+            const float y = silu_f(cw[u][0] * x0[u] + cw[u][1] * x1[u] + cw[u][2] * x2[u] + cw[u][3] * x3);
+            x0[u] = x1[u]; x1[u] = x2[u]; x2[u] = x3;
+            if (ch < DK) qs[j][ch + 4 * (ch / DPT)] = y;
+            else if (ch < 2 * DK) ks[j][(ch - DK) + 4 * ((ch - DK) / DPT)] = y;
+            else vs[j][ch - 2 * DK] = y;
+            if (p.snap_rel != nullptr && (part == 0 || ch >= 2 * DK)) {   // conv window after token (tile0 + j)
+              const int done = tile0 + j - t0 + 1;
+              for (int q = 0; q < p.num_snap; ++q) {
+                if (p.snap_rel[s * p.num_snap + q] != done) continue;
+                __nv_bfloat16* dc = p.snap_conv + (((size_t)s * p.num_snap + q) * p.hv + vh) * 3 * NCH;
+                dc[hch[u]] = __float2bfloat16_rn(x0[u]);
+                dc[NCH + hch[u]] = __float2bfloat16_rn(x1[u]);
+                dc[2 * NCH + hch[u]] = __float2bfloat16_rn(x2[u]);
+              }
             }
           }
         }
@@ -156,18 +197,36 @@ __global__ void __launch_bounds__(DV * 4) gdn_kernel(const __grid_constant__ Gdn
     // ---- (2) the recurrence, token by token, out of shared memory
     for (int j = 0; j < nt; ++j) {
       const float decay = decay_s[j], kn = kn_s[j];
-      const float* kj = ks[j] + dg * (DPT + 4);
-      const float* qj = qs[j] + dg * (DPT + 4);
-      float kv = 0.f;
+      // 128-bit shared-memory loads and packed fp32 arithmetic (two state elements per instruction); four
+      // independent partial sums per product, so no chain of DPT dependent FMAs
+      const float4* kj = reinterpret_cast<const float4*>(ks[j] + dg * (DPT + 4));
+      const float4* qj = reinterpret_cast<const float4*>(qs[j] + dg * (DPT + 4));
+      const float2 dec2 = make_float2(decay, decay);
+      float2 kva = make_float2(0.f, 0.f), kvb = kva;
 #pragma unroll
-      for (int i = 0; i < DPT; ++i) { S[i] *= decay; kv += S[i] * kj[i]; }
+      for (int i = 0; i < DPT / 4; ++i) {
+        const float4 k4 = kj[i];
+        S2[2 * i] = __fmul2_rn(S2[2 * i], dec2);
+        S2[2 * i + 1] = __fmul2_rn(S2[2 * i + 1], dec2);
+        kva = __ffma2_rn(S2[2 * i], make_float2(k4.x, k4.y), kva);
+        kvb = __ffma2_rn(S2[2 * i + 1], make_float2(k4.z, k4.w), kvb);
+      }
+      float kv = (kva.x + kva.y) + (kvb.x + kvb.y);
       kv += __shfl_xor_sync(0xffffffffu, kv, 1);
       kv += __shfl_xor_sync(0xffffffffu, kv, 2);
       const float delta = (vs[j][c] - kv * kn) * beta_s[j];
       const float kd = kn * delta;
-      float o = 0.f;
+      const float2 kd2 = make_float2(kd, kd);
+      float2 oa = make_float2(0.f, 0.f), ob = oa;
 #pragma unroll
-      for (int i = 0; i < DPT; ++i) { S[i] += kj[i] * kd; o += S[i] * qj[i]; }
+      for (int i = 0; i < DPT / 4; ++i) {
+        const float4 k4 = kj[i], q4 = qj[i];
+        S2[2 * i] = __ffma2_rn(make_float2(k4.x, k4.y), kd2, S2[2 * i]);
+        S2[2 * i + 1] = __ffma2_rn(make_float2(k4.z, k4.w), kd2, S2[2 * i + 1]);
+        oa = __ffma2_rn(S2[2 * i], make_float2(q4.x, q4.y), oa);
+        ob = __ffma2_rn(S2[2 * i + 1], make_float2(q4.z, q4.w), ob);
+      }
+      float o = (oa.x + oa.y) + (ob.x + ob.y);
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
       __syncwarp();                                // all four lanes of the column have read vs[j][c]
@@ -176,37 +235,84 @@ __global__ void __launch_bounds__(DV * 4) gdn_kernel(const __grid_constant__ Gdn
         const int done = tile0 + j - t0 + 1;
         for (int q = 0; q < p.num_snap; ++q) {
           if (p.snap_rel[s * p.num_snap + q] != done) continue;
-          float* dst = p.snap_state + (((size_t)s * p.num_snap + q) * p.hv + vh) * DK * DV;
+          float* dst = p.snap_state + (((size_t)s * p.num_snap + q) * p.hv + vh) * DK * DV + part * CB;
 #pragma unroll
-          for (int i = 0; i < DPT; ++i) dst[(size_t)(dg * DPT + i) * DV + c] = S[i];
+          for (int i = 0; i < DPT / 2; ++i) {
+            dst[(size_t)(dg * DPT + 2 * i) * DV + c] = S2[i].x;
+            dst[(size_t)(dg * DPT + 2 * i + 1) * DV + c] = S2[i].y;
+          }
         }
       }
     }
     __syncthreads();
-    // ---- (3) gated RMSNorm * silu(z): a warp per token for the statistics, then all threads for the output
-    for (int j = warp; j < nt; j += NW) {
-      float o2 = 0.f;
-      for (int i = lane; i < DV; i += 32) o2 += vs[j][i] * vs[j][i];
-      o2 = warp_sum(o2);
-      if (lane == 0) rr_s[j] = rsqrtf(o2 / (float)DV + p.eps);
+    // ---- (3) gated RMSNorm * silu(z): sums of squares per 32-column group (a warp per (token, group)), added in
+    //      group order over the whole head (the other blocks' groups come through distributed shared memory)
+    float(*o2)[NG] = o2_s[tile_idx & 1];
+    for (int e = warp; e < nt * NG; e += NW) {
+      const int j = e / NG, gq = e - j * NG;
+      const float v = vs[j][gq * 32 + lane];
+      const float t = warp_sum(v * v);
+      if (lane == 0) o2[j][gq] = t;
+    }
+    if (NS > 1) cluster_sync_all(); else __syncthreads();
+    if (tid < nt) {
+      float tot = 0.f;
+      for (int r = 0; r < NS; ++r)
+        for (int gq = 0; gq < NG; ++gq) tot += (NS > 1 && r != part) ? ld_cluster_f32(&o2[tid][gq], r) : o2[tid][gq];
+      rr_s[tid] = rsqrtf(tot / (float)DV + p.eps);
     }
     __syncthreads();
-    for (int e = tid; e < nt * DV; e += DV * 4) {
-      const int j = e / DV, cc = e - j * DV;
+    for (int e = tid; e < nt * CB; e += NT) {
+      const int j = e / CB, cc = e - j * CB;
       const size_t tok = (size_t)(tile0 + j);
       const float z = __bfloat162float(p.proj[tok * p.ld + zcol + cc]);
-      p.out[tok * p.hv * DV + vh * DV + cc] = __float2bfloat16_rn(vs[j][cc] * rr_s[j] * p.norm_w[cc] * silu_f(z));
+      p.out[tok * p.hv * DV + vh * DV + part * CB + cc] =
+          __float2bfloat16_rn(vs[j][cc] * rr_s[j] * p.norm_w[part * CB + cc] * silu_f(z));
     }
     __syncthreads();                               // the tile buffers are reused
   }
 
 #pragma unroll
-  for (int i = 0; i < DPT; ++i) st_state<ST>(Sp + (size_t)(dg * DPT + i) * DV + c, S[i]);
-  if (tid < NCH) {
-    cs[tid] = __float2bfloat16_rn(x0);
-    cs[NCH + tid] = __float2bfloat16_rn(x1);
-    cs[2 * NCH + tid] = __float2bfloat16_rn(x2);
+  for (int i = 0; i < DPT / 2; ++i) {
+    st_state<ST>(Sp + (size_t)(dg * DPT + 2 * i) * DV + c, S2[i].x);
+    st_state<ST>(Sp + (size_t)(dg * DPT + 2 * i + 1) * DV + c, S2[i].y);
   }
+#pragma unroll
+  for (int u = 0; u < NCPT; ++u) {
+    const int ch = tid + u * NT;
+    if (ch < NCHL && (part == 0 || ch >= 2 * DK)) {
+      cs[hch[u]] = __float2bfloat16_rn(x0[u]);
+      cs[NCH + hch[u]] = __float2bfloat16_rn(x1[u]);
+      cs[2 * NCH + hch[u]] = __float2bfloat16_rn(x2[u]);
+    }
+  }
+  if (NS > 1) cluster_sync_all();                  // nobody leaves while a neighbour may still read its partial sums
+}
+
+// Launch with programmatic stream serialization and, for NS > 1, clusters of NS blocks along x.
+template <int DK, int DV, typename ST, int NS>
+static cudaError_t launch_gdn(const GdnParams& p, int num_seqs, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.hv * NS, num_seqs);
+  cfg.blockDim = dim3(DV / NS * 4);
+  cfg.stream = st;
+  cudaLaunchAttribute at[2];
+  int n = 0;
+  if (pdl_enabled()) {
+    at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (NS > 1) {
+    at[n].id = cudaLaunchAttributeClusterDimension;
+    at[n].val.clusterDim.x = NS;
+    at[n].val.clusterDim.y = 1;
+    at[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = at;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, gdn_kernel<DK, DV, ST, NS>, p);
 }
 
 }  // namespace ti
@@ -216,20 +322,23 @@ extern "C" {
 int ti_gdn_params_size() { return (int)sizeof(ti::GdnParams); }
 
 // state_bf16: 0 = fp32 state pool, 1 = bf16.  (dk, dv) must be (128,128) or (64,64).
-int ti_gdn_step(const ti::GdnParams* p, int num_seqs, int dk, int dv, int state_bf16, void* stream) {
+// split != 0: the columns of a head go to a cluster of 4 (dv 128) or 2 (dv 64) blocks; meant for steps with long
+// sequences (prefill), where one block per head would leave most SMs idle.
+int ti_gdn_step(const ti::GdnParams* p, int num_seqs, int dk, int dv, int state_bf16, int split, void* stream) {
   if (num_seqs <= 0) return 0;
   if (p->hv % p->hk) return -2;
-  dim3 grid(p->hv, num_seqs);
   cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e;
   if (dk == 128 && dv == 128) {
-    if (state_bf16) ti::launch_kernel(ti::gdn_kernel<128, 128, __nv_bfloat16>, grid, dim3(512), 0, st, true, *p);
-    else ti::launch_kernel(ti::gdn_kernel<128, 128, float>, grid, dim3(512), 0, st, true, *p);
+    if (split) e = state_bf16 ? ti::launch_gdn<128, 128, __nv_bfloat16, 4>(*p, num_seqs, st) : ti::launch_gdn<128, 128, float, 4>(*p, num_seqs, st);
+    else e = state_bf16 ? ti::launch_gdn<128, 128, __nv_bfloat16, 1>(*p, num_seqs, st) : ti::launch_gdn<128, 128, float, 1>(*p, num_seqs, st);
   } else if (dk == 64 && dv == 64) {
-    if (state_bf16) ti::launch_kernel(ti::gdn_kernel<64, 64, __nv_bfloat16>, grid, dim3(256), 0, st, true, *p);
-    else ti::launch_kernel(ti::gdn_kernel<64, 64, float>, grid, dim3(256), 0, st, true, *p);
+    if (split) e = state_bf16 ? ti::launch_gdn<64, 64, __nv_bfloat16, 2>(*p, num_seqs, st) : ti::launch_gdn<64, 64, float, 2>(*p, num_seqs, st);
+    else e = state_bf16 ? ti::launch_gdn<64, 64, __nv_bfloat16, 1>(*p, num_seqs, st) : ti::launch_gdn<64, 64, float, 1>(*p, num_seqs, st);
   } else {
     return -3;
   }
+  if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();
 }
 

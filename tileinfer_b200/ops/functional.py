@@ -58,7 +58,7 @@ _l.register("ti_rmsnorm", _I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _P])
 _l.register("ti_act_mul", _I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P])
 _l.register("ti_swiglu_interleaved", _I, [_P, _P, _I, _I, _I, _I, _P])
 _l.register("ti_gdn_params_size", _I, [])
-_l.register("ti_gdn_step", _I, [ctypes.POINTER(GdnParams), _I, _I, _I, _I, _P])
+_l.register("ti_gdn_step", _I, [ctypes.POINTER(GdnParams), _I, _I, _I, _I, _I, _P])
 _l.register("ti_qkv_prep_params_size", _I, [])
 _l.register("ti_attn_params_size", _I, [])
 _l.register("ti_qkv_prep", _I, [ctypes.POINTER(QkvPrepParams), _I, _I, _P])
@@ -342,8 +342,9 @@ def swiglu_interleaved(gu, out=None):
 
 
 # ------------------------------------------------------------------------------------ launches by params
-def gdn_step(p: GdnParams, num_seqs: int, dk: int, dv: int, state_bf16: bool):
-    check(L().ti_gdn_step(ctypes.byref(p), num_seqs, dk, dv, int(state_bf16), stream()), "ti_gdn_step")
+def gdn_step(p: GdnParams, num_seqs: int, dk: int, dv: int, state_bf16: bool, split: bool = False):
+    """split: the state columns of a head go to a cluster of blocks (prefill: few sequences, many tokens)."""
+    check(L().ti_gdn_step(ctypes.byref(p), num_seqs, dk, dv, int(state_bf16), int(split), stream()), "ti_gdn_step")
 
 
 def qkv_prep(p: QkvPrepParams, T: int, D: int):
