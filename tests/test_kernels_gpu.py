@@ -496,3 +496,48 @@ def test_tcgen05_gemm_bf16(M, N, K):
     gu = ref.to(BF16).float()
     torch.testing.assert_close(y3.float(), torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2], rtol=3e-2,
                                atol=0.3 if K < 2048 else 0.6)
+
+
+@pytest.mark.parametrize("tp,M", [(2, 1), (2, 5), (4, 3)])
+def test_gemv_rowpar_handoff_to_next_product_emulated_ranks(tp, M):
+    """Chain [row-parallel product -> product that consumes its all-reduced output] with `xll`: the consumer's
+    CTAs collect the packets themselves (no collect pass, no grid barrier).  All ranks in one cooperative launch."""
+    import ctypes
+    F = _F()
+    from tileinfer_b200.parallel.symm_mem import LocalRanks
+    N, Kfull, N2 = 1024, 2048, 1536
+    K = Kfull // tp
+    w1 = _rand_w(N, Kfull, seed=21)
+    W2 = F.LinearW(_rand_w(N2, N, seed=22), True)
+    x = torch.randn(M, Kfull, device="cuda").to(BF16)
+    resid = torch.randn(M, N, device="cuda").to(BF16)
+    nw = (torch.randn(N, device="cuda") * 0.1).to(BF16)
+    ranks = LocalRanks(tp, N, m_cap=16)
+    ncta = 148 // tp
+    chains, keep, hs, projs = [], [], [], []
+    for r in range(tp):
+        W1 = F.LinearW(w1[:, r * K:(r + 1) * K].contiguous(), True)
+        xr = x[:, r * K:(r + 1) * K].contiguous()
+        h = torch.zeros(M, N, dtype=BF16, device="cuda")
+        proj = torch.zeros(M, N2, dtype=BF16, device="cuda")
+        ws = F.GemvWorkspace()
+        p1 = F.make_gemv_params(W1, xr, h, M, epi=F.EPI_ROWPAR, resid=resid, ws=ws, comm=ranks.view(r), order=0, ncta=ncta)
+        p2 = F.make_gemv_params(W2, h, proj, M, xmode=F.XNORM, epi=F.EPI_STORE, norm_w=nw, ws=ws, ncta=ncta, xll=True)
+        c = F.make_chain([p1, p2])
+        assert F.L().ti_gemv_chain_prepare(ctypes.byref(c), F.W_INT8, ncta) == 0
+        chains.append(c); keep.append((W1, xr, ws)); hs.append(h); projs.append(proj)
+    dev_params = torch.frombuffer(bytearray(b"".join(bytes(c) for c in chains)), dtype=torch.uint8).cuda()
+    rc = F.L().ti_gemv_ranks(ctypes.byref(chains[0]), dev_params.data_ptr(), tp, ncta, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(ranks.ctrl[1]) == 0, "no peer wait may time out"
+    ref_h = resid.float()
+    for r in range(tp):
+        ref_h = ref_h + x[:, r * K:(r + 1) * K].float() @ keep[r][0].dense().float().t()
+    hb = ref_h.to(BF16).float()
+    xn = (hb * torch.rsqrt(hb.pow(2).mean(-1, keepdim=True) + 1e-6) * (1 + nw.float())).to(BF16).float()
+    ref_p = xn @ W2.dense().float().t()
+    for r in range(tp):
+        torch.testing.assert_close(hs[r].float(), ref_h, rtol=2e-2, atol=4e-2)
+        torch.testing.assert_close(projs[r].float(), ref_p, rtol=3e-2, atol=6e-2)
+        assert torch.equal(hs[r], hs[0]) and torch.equal(projs[r], projs[0])

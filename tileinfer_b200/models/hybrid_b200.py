@@ -115,6 +115,7 @@ class _ModelBase:
         self._launches = 0
         self._pending, self._pending_wt = [], 0
         self.chain = os.environ.get("TI_GEMV_CHAIN", "1") != "0"
+        self.ll_handoff = os.environ.get("TI_LL_HANDOFF", "1") == "1"
         self.gdn_split = os.environ.get("TI_GDN_SPLIT", "0") == "1"   # prefill: a head's columns over a 4-block cluster
         self.gemm_min_rows = int(os.environ.get("TI_GEMM_MIN_ROWS", "8"))    # more rows than this: tcgen05 GEMM
 
@@ -243,11 +244,17 @@ class _StepMixin:
             if epi == EPI_ROWPAR:
                 order = self._order
                 self._order += 1
+            # the product that consumes an all-reduced row-parallel output collects the packets itself (same launch)
+            prev = self._pending[-1] if self._pending else None
+            xll = (self.ll_handoff and prev is not None and M <= step and self.chain and prev.epi == EPI_ROWPAR
+                   and prev.tp > 1 and prev.M == m and prev.out == x.data_ptr() and prev.N == W.K
+                   and x.stride(0) == W.K and xmode == XNORM and self._pending_wt == W.wt
+                   and len(self._pending) < F.MAX_CHAIN)
             p = F.make_gemv_params(
                 W, x[m0:m0 + m], out[m0:m0 + m], m, xmode=xmode, epi=epi, norm_w=norm_w,
                 resid=None if resid is None else resid[m0:m0 + m], ws=self.ws, eps=self.cfg.rms_eps,
                 ldx=x.stride(0), ldo=out.stride(0) if ldo is None else ldo,
-                comm=self.peer if epi == EPI_ROWPAR else None, order=order)
+                comm=self.peer if epi == EPI_ROWPAR else None, order=order, xll=xll)
             if M <= step and self.chain:
                 # dependent products are collected and launched together (up to four per launch)
                 if self._pending and (self._pending_wt != W.wt or len(self._pending) >= F.MAX_CHAIN):

@@ -58,6 +58,9 @@ struct GemvParams {
   int tps;                       // 512-byte tiles per ring stage (4, 8 or 16)
   int xmode, epi;                // XGLOBAL | XNORM ; EPI_*
   int R;                         // row tiles (of 8 weight rows) per unit: 1 or 2
+  int xll;                       // 1: x is the all-reduced output of the PREVIOUS product of the chain (row-parallel, tp > 1);
+                                 // every CTA collects that product's packets itself instead of waiting for a collect pass
+                                 // and a grid barrier
 };
 
 // Up to four dependent products run back to back in one launch (e.g. out_proj -> gate_up -> down -> the
@@ -163,6 +166,8 @@ TI_DEVICE void epilogue(const GemvParams& p, int nt, int g, int t, const float (
 // Second half of the fused all-reduce of a row-parallel product (tp > 1): every thread of the grid takes
 // some (row, column pair) positions, waits (bounded) for the tagged packets of all ranks, adds them in rank
 // order (so every rank computes bit-identical sums) and adds the residual.
+// (cta, ncta) = (blockIdx, gridDim): the grid shares the positions; (0, 1): this CTA takes all of them (every CTA
+// of the grid then writes the same values: the consumer is the next product's staging in the same CTA).
 TI_DEVICE void rowpar_reduce(const GemvParams& p, int cta, int ncta) {
   const unsigned tag = (*p.step_ptr) * 65536u + (unsigned)p.order + 1u;
   const int slot = p.order & 1;
@@ -668,8 +673,10 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
     e = __shfl_sync(0xffffffffu, e, 0);
     if ((e == TI_UNIT_END || (e & kUnitMask) == kUnitMask) && cur_op >= 0) {
       const GemvParams& pp = c.op[cur_op];
-      // this warp has sent everything it owns of the previous product: collect the all-reduce
-      if (pp.epi == EPI_ROWPAR && pp.tp > 1) rowpar_reduce(pp, cta, ncta);
+      // this warp has sent everything it owns of the previous product: collect the all-reduce, unless the next
+      // product does so itself while staging (xll)
+      const bool handed = e != TI_UNIT_END && c.op[e >> 26].xll;
+      if (pp.epi == EPI_ROWPAR && pp.tp > 1 && !handed) rowpar_reduce(pp, cta, ncta);
     }
     if (e == TI_UNIT_END) break;
     const int op = e >> 26, unit = e & kUnitMask;
@@ -680,8 +687,17 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
       if (lane == 0)                              // start streaming this product's first unit while waiting
         for (int s = ws.idx - (int)cidx; s < stages; ++s) ws.next(c, widx, W, q, ring_u32, bar0, stages);
       // ---- product boundary: every warp of every CTA is done with the previous product
-      if (op > 0) grid_barrier(p0.sched + 2, ++nbar * ncta, p0.status);
-      else __syncthreads();
+      if (op > 0 && p.xll) {
+        // the packets of the previous product are their own synchronisation: no grid barrier.  Every CTA adds
+        // them up (rank order) with the residual and writes the row(s) out; it then stages from what it wrote.
+        __syncthreads();                            // the CTA's warps are done with the staged x of that product
+        rowpar_reduce(c.op[op - 1], 0, 1);
+        __syncthreads();
+      } else if (op > 0) {
+        grid_barrier(p0.sched + 2, ++nbar * ncta, p0.status);
+      } else {
+        __syncthreads();
+      }
       if (stamp) p0.dbg[cta * 32 + 9 + 4 * op] = globaltimer_ns();
       lstride = limb_stride(p.K);
       xl = smem + (size_t)p.M * lstride;
@@ -870,6 +886,11 @@ static int prepare(ChainParams& c, int wt) {
     const int rc = check(c.op[i], wt);
     if (rc) return rc;
     if (c.op[i].sched != c.op[0].sched || c.op[i].stages != c.op[0].stages || c.op[i].tps != c.op[0].tps) return -9;
+    if (c.op[i].xll) {
+      if (i == 0) return -10;
+      const GemvParams &q = c.op[i - 1], &p = c.op[i];
+      if (q.epi != EPI_ROWPAR || q.tp < 2 || q.M != p.M || q.N != p.K || q.out != (void*)p.x || p.ldx != q.N) return -10;
+    }
     xb = std::max(xb, op_x_bytes(c.op[i], wt));
   }
   c.x_bytes = xb;

@@ -228,7 +228,7 @@ def default_workspace():
 
 
 def make_gemv_params(W: LinearW, x, out, M, *, xmode=XGLOBAL, epi=EPI_STORE, norm_w=None, resid=None, ws=None,
-                     eps=1e-6, ldx=None, ldo=None, comm=None, order=0, ncta=NUM_SMS, team=None) -> GemvParams:
+                     eps=1e-6, ldx=None, ldo=None, comm=None, order=0, ncta=NUM_SMS, team=None, xll=False) -> GemvParams:
     p = GemvParams()
     p.w, p.scale, p.x, p.norm_w = ptr(W.tiles), ptr(W.scale), ptr(x), ptr(norm_w)
     p.out, p.resid = ptr(out), ptr(resid)
@@ -246,6 +246,7 @@ def make_gemv_params(W: LinearW, x, out, M, *, xmode=XGLOBAL, epi=EPI_STORE, nor
     p.stages, p.T, p.tps, p.R = stages, plan_team(W.n_tiles, W.KB, R, team, ncta), tps, R
     p._xb = x_smem_bytes(W.wt, xmode, M, W.K, W.K)
     p.xmode, p.epi = xmode, epi
+    p.xll = int(bool(xll))
     if ws is None:
         ws = default_workspace()
     p.sched = ptr(ws.sched)
