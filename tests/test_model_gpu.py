@@ -90,3 +90,28 @@ def test_prefix_reuse_and_swap_on_gpu():
     assert st["preemptions"] >= 1 and st["swaps_out"] >= 1 and st["swaps_in"] >= 1
     for p, o in zip(prompts, outs):
         _near_greedy(o, p, "w8a16")
+
+
+def test_weight_shard_cache_round_trip(tmp_path):
+    """First start writes the rank's weights in kernel layout; the second start loads them (no sharding, no
+    quantisation) and generates the same tokens."""
+    from tileinfer_b200.engine.llm import LLM
+    from tileinfer_b200.engine.sampling_params import SamplingParams
+    kw = dict(quantization="w8a16", num_kvcache_blocks=64, max_num_seqs=4, max_model_len=256,
+              weight_cache_dir=str(tmp_path))
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    prompts = [list(range(5, 40)), [7, 8, 9]]
+    a = LLM("preset:tiny-hybrid", **kw).generate_token_ids(prompts, sp)
+    files = list(tmp_path.iterdir())
+    assert len(files) == 1 and files[0].stat().st_size > 1 << 20
+    from tileinfer_b200.models.hybrid_b200 import B200HybridModel
+
+    def boom(self, *args):
+        raise AssertionError("the cached shards must be used")
+    keep = B200HybridModel._build_shards
+    B200HybridModel._build_shards = boom
+    try:
+        b = LLM("preset:tiny-hybrid", **kw).generate_token_ids(prompts, sp)
+    finally:
+        B200HybridModel._build_shards = keep
+    assert a == b

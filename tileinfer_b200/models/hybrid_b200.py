@@ -56,8 +56,52 @@ class _ModelBase:
         self.nch = 2 * self.dk + self.dv
         assert (self.dk, self.dv) in ((128, 128), (64, 64)), "gdn kernel instances: 128x128 and 64x64"
         assert self.D in (64, 128, 256)
-        sh = ShardSpec(tp, rank)
         dev = self.dev
+        cache = None
+        if config is not None and getattr(config, "weight_cache_dir", None):
+            from .weights import shard_cache_path
+            spec = f"{getattr(config, 'model', cfg.name)}|{getattr(config, 'weights', '')}|seed{getattr(config, 'seed', 0)}"
+            cache = shard_cache_path(config.weight_cache_dir, cfg, spec, quant, tp, rank)
+        if cache is not None and os.path.exists(cache):
+            self._load_shards(cache)
+        else:
+            self._build_shards(src, q8)
+            if cache is not None:
+                self._save_shards(cache)
+        torch.cuda.empty_cache()
+
+        self.ws = GemvWorkspace(dev)
+        self.peer = None
+        if tp > 1 and self.fused:
+            from ..parallel.symm_mem import PeerComm
+            self.peer = PeerComm(comm, self.H, m_cap=64)
+        self.ctrl = self.peer.ctrl if self.peer is not None else torch.zeros(4, dtype=torch.int32, device=dev)
+        self.step_ptr = self.ctrl.data_ptr()
+        self.block_size = 16
+        self.kv = None
+        self.graphs = {}
+        self.snapshots = {}
+        self._order = 0
+        self.host_steps = 0
+        self.proj_cols = max([L.in_proj.N for L in self.layers if L.is_gdn] + [L.qkv.N for L in self.layers if not L.is_gdn])
+        self.mix_cols = max(self.hv * self.dv, self.hq * self.D)
+        self.launches_per_decode_step = 0
+        self._launches = 0
+        self._pending, self._pending_wt = [], 0
+        self.chain = os.environ.get("TI_GEMV_CHAIN", "1") != "0"
+        self.ll_handoff = os.environ.get("TI_LL_HANDOFF", "1") == "1"
+        self.gdn_split = os.environ.get("TI_GDN_SPLIT", "0") == "1"   # prefill: a head's columns over a 4-block cluster
+        self.gemm_min_rows = int(os.environ.get("TI_GEMM_MIN_ROWS", "8"))    # more rows than this: tcgen05 GEMM
+
+    # ------------------------------------------------------------------ weights: build / on-disk shard cache
+    _LINEAR = ("gate_up", "down", "in_proj", "out", "qkv", "o")
+    _PLAIN = ("input_norm", "post_norm", "conv_w", "neg_a_exp", "dt_bias", "norm_w", "q_norm", "k_norm")
+
+    def _build_shards(self, src, q8: bool):
+        """Shards, quantises and tiles this rank's weights from the source (replaces the per-layer CPU slicing and
+        GPU quantisation of model/qwen_36.py:445-521, 861-898)."""
+        c, tp, rank, dev = self.cfg, self.tp, self.rank, self.dev
+        sh = ShardSpec(tp, rank)
         self.layers = []
         for i in range(c.num_layers):
             lw = shard_layer(c, src, i, sh)
@@ -94,30 +138,49 @@ class _ModelBase:
         self.lm_head = LinearW(head, False, dev)
         self.v_local = self.lm_head.N
         del head
-        torch.cuda.empty_cache()
 
-        self.ws = GemvWorkspace(dev)
-        self.peer = None
-        if tp > 1 and self.fused:
-            from ..parallel.symm_mem import PeerComm
-            self.peer = PeerComm(comm, self.H, m_cap=64)
-        self.ctrl = self.peer.ctrl if self.peer is not None else torch.zeros(4, dtype=torch.int32, device=dev)
-        self.step_ptr = self.ctrl.data_ptr()
-        self.block_size = 16
-        self.kv = None
-        self.graphs = {}
-        self.snapshots = {}
-        self._order = 0
-        self.host_steps = 0
-        self.proj_cols = max([L.in_proj.N for L in self.layers if L.is_gdn] + [L.qkv.N for L in self.layers if not L.is_gdn])
-        self.mix_cols = max(self.hv * self.dv, self.hq * self.D)
-        self.launches_per_decode_step = 0
-        self._launches = 0
-        self._pending, self._pending_wt = [], 0
-        self.chain = os.environ.get("TI_GEMV_CHAIN", "1") != "0"
-        self.ll_handoff = os.environ.get("TI_LL_HANDOFF", "1") == "1"
-        self.gdn_split = os.environ.get("TI_GDN_SPLIT", "0") == "1"   # prefill: a head's columns over a 4-block cluster
-        self.gemm_min_rows = int(os.environ.get("TI_GEMM_MIN_ROWS", "8"))    # more rows than this: tcgen05 GEMM
+    def _save_shards(self, path: str):
+        """Writes this rank's weights in kernel layout (int8 tiles + bf16 scales, bf16 tiles) so that the next start
+        skips sharding and quantisation.  Written to a temporary name first: a reader never sees half a file."""
+        layers = []
+        for L in self.layers:
+            d = {"is_gdn": L.is_gdn}
+            for k in self._LINEAR:
+                if hasattr(L, k):
+                    d[k] = {n: (v.cpu() if torch.is_tensor(v) else v) for n, v in getattr(L, k).state().items()}
+            for k in self._PLAIN:
+                if hasattr(L, k):
+                    d[k] = getattr(L, k).cpu()
+            layers.append(d)
+        blob = {"format": 1, "layers": layers, "embed": self.embed.cpu(), "final_norm": self.final_norm.cpu(),
+                "lm_head": {n: (v.cpu() if torch.is_tensor(v) else v) for n, v in self.lm_head.state().items()},
+                "vocab_start": self.vocab_start}
+        os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
+        tmp = f"{path}.tmp{os.getpid()}"
+        torch.save(blob, tmp)
+        os.replace(tmp, path)
+
+    def _load_shards(self, path: str):
+        blob = torch.load(path, map_location="cpu", weights_only=False)
+        if blob.get("format") != 1 or len(blob["layers"]) != self.cfg.num_layers:
+            raise RuntimeError(f"{path}: not a shard cache of this model")
+        dev = self.dev
+        self.layers = []
+        for d in blob["layers"]:
+            L = _Layer()
+            L.is_gdn = d["is_gdn"]
+            for k in self._LINEAR:
+                if k in d:
+                    setattr(L, k, LinearW.from_state(d[k], dev))
+            for k in self._PLAIN:
+                if k in d:
+                    setattr(L, k, d[k].to(dev))
+            self.layers.append(L)
+        self.embed = blob["embed"].to(dev)
+        self.final_norm = blob["final_norm"].to(dev)
+        self.lm_head = LinearW.from_state(blob["lm_head"], dev)
+        self.vocab_start = blob["vocab_start"]
+        self.v_local = self.lm_head.N
 
     # ------------------------------------------------------------------ caches
     def weight_bytes(self) -> int:

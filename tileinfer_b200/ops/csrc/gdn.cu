@@ -138,7 +138,21 @@ __global__ void __launch_bounds__(DV / NS * 4) gdn_kernel(const __grid_constant_
   int tile_idx = 0;
   for (int tile0 = t0; tile0 < t1; tile0 += kTT, ++tile_idx) {
     const int nt = min(kTT, t1 - tile0);
-    // ---- (1a) conv + SiLU of every channel over the tile (all loads of the tile are issued first)
+    // ---- (1a) conv + SiLU of every channel over the tile.  All global loads of the tile (conv inputs, gate
+    //      inputs a / b, output gates z) are issued first, so the tile pays one memory round trip
+    constexpr int ZPT = kTT * CB / NT;              // z values per thread
+    float zin[ZPT];
+#pragma unroll
+    for (int k = 0; k < ZPT; ++k) {
+      const int e = tid + k * NT, j = e / CB, cc = e - j * CB;
+      zin[k] = e < nt * CB ? __bfloat162float(p.proj[(size_t)(tile0 + j) * p.ld + zcol + cc]) : 0.f;
+    }
+    float a_in = 0.f, b_in = 0.f;
+    if (tid < nt) {
+      const __nv_bfloat16* row = p.proj + (size_t)(tile0 + tid) * p.ld;
+      a_in = __bfloat162float(row[acol]);
+      b_in = __bfloat162float(row[bcol]);
+    }
     float xin[NCPT][kTT];
 #pragma unroll
     for (int u = 0; u < NCPT; ++u)
@@ -172,10 +186,15 @@ __global__ void __launch_bounds__(DV / NS * 4) gdn_kernel(const __grid_constant_
         }
       }
     }
+    if (tid < nt) {                                 // gates of token tid
+      const float a = a_in + dtb;
+      const float sp = a > 20.f ? a : log1pf(__expf(a));
+      decay_s[tid] = __expf(neg_a * sp);
+      beta_s[tid] = sigmoid_f(b_in);
+    }
     __syncthreads();
-    // ---- (1b) per-token scalars: a warp per token
+    // ---- (1b) q / k norms: a warp per token
     for (int j = warp; j < nt; j += NW) {
-      const __nv_bfloat16* row = p.proj + (size_t)(tile0 + j) * p.ld;
       float sq = 0.f, sk = 0.f;
       for (int i = lane; i < DK; i += 32) {
         const float a = qs[j][i + 4 * (i / DPT)], b = ks[j][i + 4 * (i / DPT)];
@@ -187,10 +206,6 @@ __global__ void __launch_bounds__(DV / NS * 4) gdn_kernel(const __grid_constant_
       if (lane == 0) {
         qn_s[j] = rsqrtf(sq + 1e-6f) * qscale;
         kn_s[j] = rsqrtf(sk + 1e-6f);
-        const float a = __bfloat162float(row[acol]) + dtb;
-        const float sp = a > 20.f ? a : log1pf(__expf(a));
-        decay_s[j] = __expf(neg_a * sp);
-        beta_s[j] = sigmoid_f(__bfloat162float(row[bcol]));
       }
     }
     __syncthreads();
@@ -262,12 +277,12 @@ __global__ void __launch_bounds__(DV / NS * 4) gdn_kernel(const __grid_constant_
       rr_s[tid] = rsqrtf(tot / (float)DV + p.eps);
     }
     __syncthreads();
-    for (int e = tid; e < nt * CB; e += NT) {
-      const int j = e / CB, cc = e - j * CB;
-      const size_t tok = (size_t)(tile0 + j);
-      const float z = __bfloat162float(p.proj[tok * p.ld + zcol + cc]);
-      p.out[tok * p.hv * DV + vh * DV + part * CB + cc] =
-          __float2bfloat16_rn(vs[j][cc] * rr_s[j] * p.norm_w[part * CB + cc] * silu_f(z));
+#pragma unroll
+    for (int k = 0; k < ZPT; ++k) {
+      const int e = tid + k * NT, j = e / CB, cc = e - j * CB;
+      if (e < nt * CB)
+        p.out[(size_t)(tile0 + j) * p.hv * DV + vh * DV + part * CB + cc] =
+            __float2bfloat16_rn(vs[j][cc] * rr_s[j] * p.norm_w[part * CB + cc] * silu_f(zin[k]));
     }
     __syncthreads();                               // the tile buffers are reused
   }

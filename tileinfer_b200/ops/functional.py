@@ -116,6 +116,21 @@ class LinearW:
         self.KB = self.K // self.tile_k
         self.n_tiles = self.n_pad // 8
 
+    def state(self) -> dict:
+        """Everything needed to rebuild this object without the source weight (on-disk shard cache)."""
+        return {"tiles": self.tiles, "scale": self.scale, "N": self.N, "K": self.K, "n_pad": self.n_pad, "wt": self.wt}
+
+    @classmethod
+    def from_state(cls, d: dict, device="cuda") -> "LinearW":
+        w = cls.__new__(cls)
+        w.N, w.K, w.n_pad, w.wt = d["N"], d["K"], d["n_pad"], d["wt"]
+        w.tiles = d["tiles"].to(device)
+        w.scale = None if d["scale"] is None else d["scale"].to(device)
+        w.tile_k = 64 if w.wt == W_INT8 else 32
+        w.KB = w.K // w.tile_k
+        w.n_tiles = w.n_pad // 8
+        return w
+
     def dense(self) -> torch.Tensor:
         """Row-major bf16 copy [N, K] (tests and the prefill GEMM baseline)."""
         from ..models.weights import untile_int8

@@ -216,6 +216,7 @@ def add_engine_args(ap: argparse.ArgumentParser):
     ap.add_argument("--quantization", default="w8a16", choices=["w8a16", "bf16"])
     ap.add_argument("--swap-space-gb", type=float, default=0.0)
     ap.add_argument("--device", default="auto")
+    ap.add_argument("--weight-cache-dir", default=None, help="keep per-rank quantised shards here between starts")
 
 
 def engine_kwargs(args) -> dict:
@@ -223,7 +224,8 @@ def engine_kwargs(args) -> dict:
                 gpu_memory_utilization=args.gpu_memory_utilization, enforce_eager=args.enforce_eager,
                 tp_size=args.tp_size, num_scheduler_steps=args.num_scheduler_steps,
                 enable_prefix_caching=not args.no_prefix_caching, quantization=args.quantization,
-                swap_space_bytes=int(args.swap_space_gb * (1 << 30)), device=args.device)
+                swap_space_bytes=int(args.swap_space_gb * (1 << 30)), device=args.device,
+                weight_cache_dir=args.weight_cache_dir)
 
 
 def main(argv=None):
