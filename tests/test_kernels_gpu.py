@@ -272,6 +272,11 @@ def test_gdn_step_matches_recurrence(dk, hk, hv, state_bf16):
     sn2, sc2 = torch.zeros_like(snap_state), torch.zeros_like(snap_conv)
     p.state, p.conv_state, p.out, p.snap_state, p.snap_conv = st2.data_ptr(), cs2.data_ptr(), out2.data_ptr(), sn2.data_ptr(), sc2.data_ptr()
     F.gdn_step(p, S, dk, dv, state_bf16, split=True)
+    # ... and the single-pass decode kernel (it walks longer sequences too)
+    st3, cs3, out3 = state0.clone(), cs0.clone(), torch.zeros_like(out)
+    sn3, sc3 = torch.zeros_like(snap_state), torch.zeros_like(snap_conv)
+    p.state, p.conv_state, p.out, p.snap_state, p.snap_conv = st3.data_ptr(), cs3.data_ptr(), out3.data_ptr(), sn3.data_ptr(), sc3.data_ptr()
+    F.gdn_step(p, S, dk, dv, state_bf16, single=True)
     p.state, p.conv_state, p.out = state.data_ptr(), cs.data_ptr(), out.data_ptr()
     p.snap_state, p.snap_conv = snap_state.data_ptr(), snap_conv.data_ptr()
     F.gdn_step(p, S, dk, dv, state_bf16)
@@ -281,6 +286,9 @@ def test_gdn_step_matches_recurrence(dk, hk, hv, state_bf16):
     torch.testing.assert_close(state.float(), st2.float(), rtol=1e-2 if state_bf16 else 1e-5, atol=1e-3 if state_bf16 else 1e-6)
     assert torch.equal(cs, cs2) and torch.equal(snap_conv, sc2)
     torch.testing.assert_close(snap_state, sn2, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(out.float(), out3.float(), rtol=2e-2, atol=1e-2)
+    torch.testing.assert_close(state.float(), st3.float(), rtol=1e-2 if state_bf16 else 1e-4, atol=1e-3 if state_bf16 else 1e-5)
+    assert torch.equal(cs, cs3) and torch.equal(snap_conv, sc3)
     tol = dict(rtol=3e-2, atol=3e-2)
     for s in range(S):
         t0, t1, slot = int(cu[s]), int(cu[s + 1]), int(slots[s])

@@ -49,8 +49,6 @@ def test_fused_tp_matches_oracle_and_all_ranks_agree(tp):
 def test_nccl_baseline_path_tp2():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    if os.environ.get("TI_TEST_NCCL_BASELINE") != "1":
-        pytest.skip("the NCCL baseline engine path is opt-in (TI_TEST_NCCL_BASELINE=1)")
     res = _run(2, False, 29549)
     ranks = res["ranks"]
     assert all(r["greedy"] == ranks[0]["greedy"] for r in ranks)

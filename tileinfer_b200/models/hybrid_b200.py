@@ -381,7 +381,7 @@ class _StepMixin:
                     p.snap_rel, p.num_snap = ptr(x.snap_rel), x.num_snap
                     p.snap_state, p.snap_conv = ptr(x.snap_state[ig]), ptr(x.snap_conv[ig])
                 self._flush()
-                F.gdn_step(p, S, self.dk, self.dv, self.state_bf16, split=self.gdn_split and T > S)
+                F.gdn_step(p, S, self.dk, self.dv, self.state_bf16, split=self.gdn_split and T > S, single=T == S)
                 self._launches += 1
                 # the kernel writes [T, hv*dv] densely
                 mix = x.mix.view(-1)[:T * self.hv * self.dv].view(T, self.hv * self.dv)

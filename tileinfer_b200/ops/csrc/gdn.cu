@@ -46,6 +46,129 @@ template <typename ST> TI_DEVICE void st_state(ST* p, float v);
 template <> TI_DEVICE void st_state<float>(float* p, float v) { *p = v; }
 template <> TI_DEVICE void st_state<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
+// Decode form (every sequence of the step has one token): everything of a token in one pass, two block
+// barriers.  The tiled kernel below does the same arithmetic per token but stages a tile's worth of q / k / v
+// through shared memory, which costs a decode step several microseconds per layer for nothing.
+template <int DK, int DV, typename ST>
+__global__ void __launch_bounds__(DV * 4) gdn_token_kernel(const __grid_constant__ GdnParams p) {
+  constexpr int DPT = DK / 4;           // state elements per thread
+  constexpr int NCH = 2 * DK + DV;      // conv channels this block needs
+  constexpr int NW = DV * 4 / 32;
+  static_assert(NCH <= DV * 4, "one thread per conv channel");
+  __shared__ float qs[DK], ks[DK], vs[DV], red[NW];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int c = tid >> 2, dg = tid & 3;
+  const int vh = blockIdx.x, s = blockIdx.y;
+  const int kh = vh / (p.hv / p.hk);
+  // cu / slots are written by host copies that precede every kernel of the step; the recurrent state
+  // and conv history were last written one step ago: all of this may be read before pdl_wait()
+  const int t0 = p.cu ? p.cu[s] : s, t1 = p.cu ? p.cu[s + 1] : s + 1;
+  const int slot = p.slots[s];
+
+  ST* Sp = static_cast<ST*>(p.state) + ((size_t)slot * p.hv + vh) * DK * DV;
+  float S[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) S[i] = ld_state<ST>(Sp + (size_t)(dg * DPT + i) * DV + c);
+
+  // conv channel owned by this thread: column in `proj` and row of conv_w
+  __nv_bfloat16* cs = p.conv_state + ((size_t)slot * p.hv + vh) * 3 * NCH;
+  float x0 = 0.f, x1 = 0.f, x2 = 0.f, cw0 = 0.f, cw1 = 0.f, cw2 = 0.f, cw3 = 0.f;
+  int col = 0;
+  if (tid < NCH) {
+    if (tid < DK) col = kh * DK + tid;
+    else if (tid < 2 * DK) col = p.hk * DK + kh * DK + (tid - DK);
+    else col = 2 * p.hk * DK + vh * DV + (tid - 2 * DK);
+    const float4 w = *reinterpret_cast<const float4*>(p.conv_w + (size_t)col * 4);
+    cw0 = w.x; cw1 = w.y; cw2 = w.z; cw3 = w.w;
+    x0 = __bfloat162float(cs[tid]);
+    x1 = __bfloat162float(cs[NCH + tid]);
+    x2 = __bfloat162float(cs[2 * NCH + tid]);
+  }
+  const int zcol = 2 * p.hk * DK + p.hv * DV + vh * DV;
+  const int bcol = 2 * p.hk * DK + 2 * p.hv * DV + vh;
+  const int acol = bcol + p.hv;
+  const float neg_a = p.neg_a_exp[vh], dtb = p.dt_bias[vh];
+  const float nw = p.norm_w[c];
+  const float qscale = rsqrtf((float)DK);
+  pdl_trigger();
+  pdl_wait();                                    // `proj` comes from the preceding projection kernel
+
+  for (int tok = t0; tok < t1; ++tok) {
+    const __nv_bfloat16* row = p.proj + (size_t)tok * p.ld;
+    if (tid < NCH) {
+      const float x3 = __bfloat162float(row[col]);
+      const float y = silu_f(cw0 * x0 + cw1 * x1 + cw2 * x2 + cw3 * x3);
+      x0 = x1; x1 = x2; x2 = x3;
+      if (tid < DK) qs[tid] = y;
+      else if (tid < 2 * DK) ks[tid - DK] = y;
+      else vs[tid - 2 * DK] = y;
+    }
+    __syncthreads();
+    float sq = 0.f, sk = 0.f;
+    for (int i = lane; i < DK; i += 32) { sq += qs[i] * qs[i]; sk += ks[i] * ks[i]; }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    const float qn = rsqrtf(sq + 1e-6f) * qscale, kn = rsqrtf(sk + 1e-6f);
+    const float a = __bfloat162float(row[acol]) + dtb;
+    const float sp = a > 20.f ? a : log1pf(__expf(a));
+    const float decay = __expf(neg_a * sp);
+    const float beta = sigmoid_f(__bfloat162float(row[bcol]));
+
+    float kv = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) { S[i] *= decay; kv += S[i] * ks[dg * DPT + i]; }
+    kv += __shfl_xor_sync(0xffffffffu, kv, 1);
+    kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+    const float delta = (vs[c] - kv * kn) * beta;
+    const float kd = kn * delta;
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) { S[i] += ks[dg * DPT + i] * kd; o += S[i] * qs[dg * DPT + i]; }
+    o += __shfl_xor_sync(0xffffffffu, o, 1);
+    o += __shfl_xor_sync(0xffffffffu, o, 2);
+    o *= qn;
+
+    float o2 = dg == 0 ? o * o : 0.f;
+    o2 = warp_sum(o2);
+    if (lane == 0) red[warp] = o2;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) tot += red[w];
+    const float rr = rsqrtf(tot / (float)DV + p.eps);
+    if (dg == 0) {
+      const float z = __bfloat162float(row[zcol + c]);
+      p.out[(size_t)tok * p.hv * DV + vh * DV + c] = __float2bfloat16_rn(o * rr * nw * silu_f(z));
+    }
+    if (p.snap_rel != nullptr) {
+      const int done = tok - t0 + 1;
+      for (int j = 0; j < p.num_snap; ++j) {
+        if (p.snap_rel[s * p.num_snap + j] != done) continue;
+        float* dst = p.snap_state + (((size_t)s * p.num_snap + j) * p.hv + vh) * DK * DV;
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) dst[(size_t)(dg * DPT + i) * DV + c] = S[i];
+        if (tid < NCH) {
+          __nv_bfloat16* dc = p.snap_conv + (((size_t)s * p.num_snap + j) * p.hv + vh) * 3 * NCH;
+          dc[tid] = __float2bfloat16_rn(x0);
+          dc[NCH + tid] = __float2bfloat16_rn(x1);
+          dc[2 * NCH + tid] = __float2bfloat16_rn(x2);
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) st_state<ST>(Sp + (size_t)(dg * DPT + i) * DV + c, S[i]);
+  if (tid < NCH) {
+    cs[tid] = __float2bfloat16_rn(x0);
+    cs[NCH + tid] = __float2bfloat16_rn(x1);
+    cs[2 * NCH + tid] = __float2bfloat16_rn(x2);
+  }
+}
+
+
 // Tokens are processed in tiles of kTT.  Per tile: (1) every conv channel runs its window over the tile's tokens
 // (independent global loads, no synchronisation) and the per-token scalars (q/k norms, decay, beta) are worked
 // out in parallel; (2) the recurrence walks the tile token by token out of shared memory: two matrix-vector
@@ -337,13 +460,26 @@ extern "C" {
 int ti_gdn_params_size() { return (int)sizeof(ti::GdnParams); }
 
 // state_bf16: 0 = fp32 state pool, 1 = bf16.  (dk, dv) must be (128,128) or (64,64).
-// split != 0: the columns of a head go to a cluster of 4 (dv 128) or 2 (dv 64) blocks; meant for steps with long
-// sequences (prefill), where one block per head would leave most SMs idle.
+// split 1: the columns of a head go to a cluster of 4 (dv 128) or 2 (dv 64) blocks (prefill; measured slower, off
+// by default).  split 2: the single-pass kernel for steps in which every sequence has exactly one token (decode).
 int ti_gdn_step(const ti::GdnParams* p, int num_seqs, int dk, int dv, int state_bf16, int split, void* stream) {
   if (num_seqs <= 0) return 0;
   if (p->hv % p->hk) return -2;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
+  if (split == 2) {                     // one token per sequence: the single-pass decode kernel
+    dim3 grid(p->hv, num_seqs);
+    if (dk == 128 && dv == 128) {
+      if (state_bf16) e = ti::launch_kernel(ti::gdn_token_kernel<128, 128, __nv_bfloat16>, grid, dim3(512), 0, st, true, *p);
+      else e = ti::launch_kernel(ti::gdn_token_kernel<128, 128, float>, grid, dim3(512), 0, st, true, *p);
+    } else if (dk == 64 && dv == 64) {
+      if (state_bf16) e = ti::launch_kernel(ti::gdn_token_kernel<64, 64, __nv_bfloat16>, grid, dim3(256), 0, st, true, *p);
+      else e = ti::launch_kernel(ti::gdn_token_kernel<64, 64, float>, grid, dim3(256), 0, st, true, *p);
+    } else {
+      return -3;
+    }
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+  }
   if (dk == 128 && dv == 128) {
     if (split) e = state_bf16 ? ti::launch_gdn<128, 128, __nv_bfloat16, 4>(*p, num_seqs, st) : ti::launch_gdn<128, 128, float, 4>(*p, num_seqs, st);
     else e = state_bf16 ? ti::launch_gdn<128, 128, __nv_bfloat16, 1>(*p, num_seqs, st) : ti::launch_gdn<128, 128, float, 1>(*p, num_seqs, st);

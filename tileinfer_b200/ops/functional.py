@@ -358,9 +358,11 @@ def swiglu_interleaved(gu, out=None):
 
 
 # ------------------------------------------------------------------------------------ launches by params
-def gdn_step(p: GdnParams, num_seqs: int, dk: int, dv: int, state_bf16: bool, split: bool = False):
-    """split: the state columns of a head go to a cluster of blocks (prefill: few sequences, many tokens)."""
-    check(L().ti_gdn_step(ctypes.byref(p), num_seqs, dk, dv, int(state_bf16), int(split), stream()), "ti_gdn_step")
+def gdn_step(p: GdnParams, num_seqs: int, dk: int, dv: int, state_bf16: bool, split: bool = False, single: bool = False):
+    """single: every sequence has exactly one token (decode): the single-pass kernel.  split: the state columns
+    of a head go to a cluster of blocks (prefill; optional)."""
+    mode = 2 if single else int(split)
+    check(L().ti_gdn_step(ctypes.byref(p), num_seqs, dk, dv, int(state_bf16), mode, stream()), "ti_gdn_step")
 
 
 def qkv_prep(p: QkvPrepParams, T: int, D: int):
