@@ -40,12 +40,16 @@ def _print_timeline(dbg, n_ops):
     for op in range(n_ops):
         for k, nm in enumerate(("marker reached", "barrier passed", "x staged", "last unit done")):
             row(f"op{op} {nm}", 8 + 4 * op + k)
+    for op in range(min(n_ops, 2)):
+        for k, nm in enumerate(("unit popped", "first chunk arrived", "tiles done")):
+            row(f"op{op} warp0 last unit: {nm}", 24 + 4 * op + k)
     row("end", 5)
 
 
 def bench_chain(args):
     """One launch = out_proj, gate_up, down, in_proj of the 27B layer; weights rotate over copies > L2."""
-    M, H, I, KO, NI = args.M, 5120, 17408, 6144, 16480
+    tp = args.tp_shapes          # per-rank shapes of a tensor-parallel group of this size, without the collectives
+    M, H, I, KO, NI = args.M, 5120, 17408 // tp, 6144 // tp, 16480 // tp // 8 * 8
     ws = F.GemvWorkspace()
     ncopy = 3
     mk = lambda n, k: F.LinearW(torch.randn(n, k, device="cuda") * 0.05, True)
@@ -82,7 +86,7 @@ def bench_chain(args):
     torch.cuda.synchronize()
     us = e0.elapsed_time(e1) * 1e3 / args.iters
     nbytes = sum(W.nbytes() for W in sets[0])
-    print(f"chain of 4 (27B layer) M={M} stages={chains[0][0].stages}: {us:7.2f} us  {nbytes / us / 1e3:7.1f} GB/s "
+    print(f"chain of 4 (27B layer, 1/{tp} shard) M={M} stages={chains[0][0].stages} T={[p.T for p in chains[0]]}: {us:7.2f} us  {nbytes / us / 1e3:7.1f} GB/s "
           f"({nbytes / 1e6:.0f} MB)")
     if args.timeline:
         _print_timeline(dbg, 4)
@@ -92,6 +96,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--timeline", action="store_true")
     ap.add_argument("--chain", action="store_true")
+    ap.add_argument("--tp-shapes", type=int, default=1)
     ap.add_argument("--M", type=int, default=1)
     ap.add_argument("--iters", type=int, default=40)
     args = ap.parse_args()

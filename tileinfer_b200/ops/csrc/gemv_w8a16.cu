@@ -519,7 +519,9 @@ struct WarpStream {           // registers of lane 0 of each warp; queue storage
       if (!can_ticket || wr - rd >= ahead) return;
       // drawn only when the copy side has handed the whole previous unit to the TMA engine: the consumer side
       // is then still a ring's depth of chunks behind, which covers the latency of the atomic
-      const int u = p.T > 1 ? U : ns * W + atomicAdd(p.sched + 8 + op * 16, 1);
+      // (no draw at all when the static deal already covers the product: 2368 warps hitting one counter at
+      // the end of every small product cost microseconds)
+      const int u = (p.T > 1 || ns * W >= U) ? U : ns * W + atomicAdd(p.sched + 8 + op * 16, 1);
       if (u >= U) {
         sk = 0;
         opened = false;
@@ -714,6 +716,8 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
       for (int s = ws.idx - (int)cidx; s < stages; ++s) ws.next(c, widx, W, q, ring_u32, bar0, stages);
 
     const bool hi = p.M > 8;
+    const bool fine = stamp && op <= 1;           // fine-grained stamps of warp 0's last unit of products 0 and 1
+    if (fine) p0.dbg[cta * 32 + 24 + 4 * op] = globaltimer_ns();
     const int grp = unit;
     int kt0 = 0, kt1 = p.KB;
     if (p.T > 1) {
@@ -739,6 +743,7 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
       for (int tile0 = kt0; tile0 < kt1; tile0 += kTPS) {
         const int ntile = min(kTPS, kt1 - tile0);
         if (alive) alive = mbar_wait(bar0 + cst * 8, cpar, 2000000000ull, p.status);
+        if (fine && tile0 == kt0) p0.dbg[cta * 32 + 25 + 4 * op] = globaltimer_ns();
         const uint32_t sbuf = ring_u32 + cst * (kTPS * 512u) + lane * 16;
         if (WT == W_INT8) {
           const uint32_t o = (uint32_t)tile0 * 64u;
@@ -793,6 +798,7 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
         }
         if (lane == 0) ws.next(c, widx, W, q, ring_u32, bar0, stages);
       }
+      if (fine) p0.dbg[cta * 32 + 26 + 4 * op] = globaltimer_ns();
       if (WT == W_INT8) {
 #pragma unroll
         for (int b = 0; b < 4; ++b)
