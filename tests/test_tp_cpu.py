@@ -145,3 +145,70 @@ if llm.comm.rank == 0:
     g = torch.Generator().manual_seed(1)
     p = torch.randint(0, 1023, (21,), generator=g).tolist()
     assert got == _mk().generate_token_ids([p], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+
+
+def test_heartbeat_reports_silent_peer_with_fake_clock():
+    """Three ranks share an in-process store; rank 2 stops beating; the others report it after the timeout,
+    and only it."""
+    import torch.distributed as dist
+    from tileinfer_b200.parallel.watchdog import Heartbeat, PeerLostError
+    store = dist.HashStore()
+    now = [0.0]
+    lost_cb = []
+    hbs = [Heartbeat(store, r, 3, interval_s=0.1, timeout_s=1.0, clock=lambda: now[0], on_lost=lost_cb.append)
+           for r in range(3)]
+    for t in range(5):                       # everybody alive
+        now[0] = 0.2 * t
+        for h in hbs:
+            h.tick()
+    assert not any(h.lost for h in hbs)
+    for t in range(5, 14):                   # rank 2 is gone from t = 1.0 on
+        now[0] = 0.2 * t
+        hbs[0].tick()
+        hbs[1].tick()
+    assert hbs[0].lost == {2} and hbs[1].lost == {2} and sorted(lost_cb) == [2, 2]
+    with pytest.raises(PeerLostError) as e:
+        hbs[0].check()
+    assert e.value.ranks == [2]
+
+    class Broken:                            # the store itself went away: the rank that hosted it is lost
+        def set(self, *a):
+            raise RuntimeError("connection reset")
+    hb = Heartbeat(Broken(), 1, 2, store_owner=0)
+    hb.tick()
+    assert hb.lost == {0}
+
+
+def test_engine_notices_rank_that_left_between_steps(tmp_path):
+    """gloo, 2 processes: rank 1 leaves between two requests (nothing in flight); rank 0 learns of it from the
+    heartbeat on the host and refuses to start the next step instead of blocking in a collective."""
+    script = r'''
+import os, sys, time, torch
+sys.path.insert(0, %r)
+import torch.distributed as dist
+from tileinfer_b200.engine.llm import LLM
+from tileinfer_b200.engine.sampling_params import SamplingParams
+from tileinfer_b200.parallel.watchdog import PeerLostError
+llm = LLM("preset:tiny-hybrid-tp", device="cpu", quantization="bf16", num_kvcache_blocks=64, max_num_seqs=4,
+          max_model_len=512, tp_size=2, nccl_timeout=60, heartbeat_interval=0.1, heartbeat_timeout=1.0)
+sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+llm.generate_token_ids([[5, 6, 7, 8]], sp)
+dist.barrier()
+if llm.comm.rank == 1:
+    llm.watchdog.stop()
+    os._exit(0)                               # leaves with nothing in flight
+time.sleep(2.5)
+try:
+    llm.generate_token_ids([[9, 10, 11]], sp)
+    print("NOT_DETECTED", flush=True)
+except PeerLostError as e:
+    print("PEER_LOST", e.ranks, flush=True)
+os._exit(0)
+''' % ROOT
+    path = tmp_path / "hb_gloo.py"
+    path.write_text(script)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT="29537")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29537", str(path)],
+                       capture_output=True, text=True, env=env, timeout=300)
+    assert "PEER_LOST [1]" in r.stdout, (r.stdout[-500:], r.stderr[-1500:])

@@ -54,6 +54,14 @@ class LLMEngine:
         r.on_prefix_state_dropped = lambda node_id: s.prefix_cache.mark_state(node_id, False)
         self._all_seqs = {}
         self._stats = EngineStats()
+        # host-side peer watchdog (tensor parallelism): a dead rank is noticed before the next launch
+        self.watchdog = None
+        if cfg.tp_size > 1 and cfg.heartbeat_interval > 0:
+            from ..parallel.watchdog import Heartbeat, default_store
+            store = default_store()
+            if store is not None:
+                self.watchdog = Heartbeat(store, self.comm.rank, self.comm.world_size, interval_s=cfg.heartbeat_interval,
+                                          timeout_s=cfg.heartbeat_timeout).start()
 
     # ---- requests ---------------------------------------------------------
     def add_request(self, prompt, sampling_params: SamplingParams | None = None) -> Sequence:
@@ -81,6 +89,8 @@ class LLMEngine:
     # ---- stepping ---------------------------------------------------------
     def step(self) -> list:
         """One scheduling step.  Returns the sequences that finished in it."""
+        if self.watchdog is not None:
+            self.watchdog.check()                     # raises PeerLostError: no launch that would wait for a dead rank
         seqs, is_prefill = self.scheduler.schedule()
         if not seqs:
             return []

@@ -216,6 +216,8 @@ def add_engine_args(ap: argparse.ArgumentParser):
     ap.add_argument("--quantization", default="w8a16", choices=["w8a16", "bf16"])
     ap.add_argument("--swap-space-gb", type=float, default=0.0)
     ap.add_argument("--device", default="auto")
+    ap.add_argument("--heartbeat-interval", type=float, default=0.0,
+                    help="seconds between peer heartbeats under tensor parallelism (0: off)")
     ap.add_argument("--weight-cache-dir", default=None, help="keep per-rank quantised shards here between starts")
 
 
@@ -225,7 +227,7 @@ def engine_kwargs(args) -> dict:
                 tp_size=args.tp_size, num_scheduler_steps=args.num_scheduler_steps,
                 enable_prefix_caching=not args.no_prefix_caching, quantization=args.quantization,
                 swap_space_bytes=int(args.swap_space_gb * (1 << 30)), device=args.device,
-                weight_cache_dir=args.weight_cache_dir)
+                weight_cache_dir=args.weight_cache_dir, heartbeat_interval=args.heartbeat_interval)
 
 
 def main(argv=None):
