@@ -54,3 +54,16 @@ def test_nccl_baseline_path_tp2():
     assert all(r["greedy"] == ranks[0]["greedy"] for r in ranks)
     for p, o in zip(res["prompts"], ranks[0]["greedy"]):
         _near_greedy(o, p)
+
+
+def test_rank_leaving_between_steps_is_noticed_on_the_host():
+    """2 GPUs, NVLS off, plain peer stores only: a rank exits between two requests; the survivor's heartbeat
+    reports it before the next launch and its CUDA context stays usable."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, TI_TEST_MODE="leave", NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29547", os.path.join(ROOT, "tests", "tp_gpu_worker.py")],
+                       capture_output=True, text=True, env=env, timeout=240)
+    line = [l for l in r.stdout.splitlines() if l.startswith("LEAVE_RESULT")]
+    assert line and "PEER_LOST [1]" in line[0] and "context_ok=True" in line[0], (r.stdout[-800:], r.stderr[-2000:])

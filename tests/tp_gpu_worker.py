@@ -18,7 +18,39 @@ def prompt(n, seed):
     return torch.randint(0, 1023, (n,), generator=g).tolist()
 
 
+def leave_between_steps():
+    """Rank 1 leaves after a completed request (nothing of its own in flight); rank 0 must learn of it from
+    the heartbeat on the host and refuse to launch, with its CUDA context intact."""
+    import time
+    from tileinfer_b200.parallel.watchdog import PeerLostError
+    tp = int(os.environ["WORLD_SIZE"])
+    llm = LLM("preset:tiny-hybrid-tp", quantization="w8a16", tp_size=tp, num_kvcache_blocks=128, max_num_seqs=8,
+              max_model_len=512, nccl_timeout=60, heartbeat_interval=0.2, heartbeat_timeout=2.0)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    first = llm.generate_token_ids([prompt(21, 1)], sp)
+    torch.cuda.synchronize()
+    dist.barrier()
+    peer = llm.model_runner.model.peer
+    if llm.comm.rank == tp - 1:
+        llm.watchdog.stop()
+        os._exit(0)
+    time.sleep(4.0)
+    try:
+        llm.generate_token_ids([prompt(9, 2)], sp)
+        verdict = "NOT_DETECTED"
+    except PeerLostError as e:
+        verdict = f"PEER_LOST {e.ranks}"
+    ok = float(torch.ones(8, device="cuda").sum()) == 8.0 and llm.model_runner.model.peer_status() == 0
+    if llm.comm.rank == 0:
+        print(f"LEAVE_RESULT {verdict} context_ok={ok} first_len={len(first[0])}", flush=True)
+    llm.model_runner.model.graphs.clear()
+    peer.close(collective=False)
+    os._exit(0)
+
+
 def main():
+    if os.environ.get("TI_TEST_MODE") == "leave":
+        return leave_between_steps()
     import faulthandler
     faulthandler.dump_traceback_later(int(os.environ.get("TI_TEST_WATCHDOG_S", "150")), exit=True)   # a stuck rank says where
     fused = os.environ.get("TI_TEST_FUSED", "1") == "1"

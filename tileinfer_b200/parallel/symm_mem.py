@@ -94,13 +94,15 @@ class PeerComm:
     def clear_status(self):
         self.ctrl[1] = 0
 
-    def close(self):
+    def close(self, collective: bool = True):
+        """Unmaps the peers' buffers and frees the local ones.  collective=False skips the barrier between the two
+        (a peer is gone: nobody will write into the local buffers any more, and nobody can answer a barrier)."""
         lib = F.L()
         torch.cuda.synchronize()
         for q in self._mapped:
             lib.ti_ipc_close(ctypes.c_void_p(q))
         self._mapped = []
-        if self.tp > 1:
+        if self.tp > 1 and collective:
             self.comm.barrier()
         for p in self._local:
             lib.ti_symm_free(ctypes.c_void_p(p))
