@@ -37,7 +37,12 @@ struct GdnParams {
   __nv_bfloat16* snap_conv;    // [S, NS, hv, 3, 2*DK + DV]
   int ld, hk, hv, num_snap;
   float eps;
+  const int* snap_idx;         // [S, NS] index of the snapshot buffer entry of (sequence, point), or nullptr (s * NS + j)
 };
+
+TI_DEVICE size_t snap_entry(const GdnParams& p, int s, int j) {
+  return p.snap_idx != nullptr ? (size_t)p.snap_idx[s * p.num_snap + j] : (size_t)s * p.num_snap + j;
+}
 
 template <typename ST> TI_DEVICE float ld_state(const ST* p);
 template <> TI_DEVICE float ld_state<float>(const float* p) { return *p; }
@@ -145,11 +150,11 @@ __global__ void __launch_bounds__(DV * 4) gdn_token_kernel(const __grid_constant
       const int done = tok - t0 + 1;
       for (int j = 0; j < p.num_snap; ++j) {
         if (p.snap_rel[s * p.num_snap + j] != done) continue;
-        float* dst = p.snap_state + (((size_t)s * p.num_snap + j) * p.hv + vh) * DK * DV;
+        float* dst = p.snap_state + (snap_entry(p, s, j) * p.hv + vh) * DK * DV;
 #pragma unroll
         for (int i = 0; i < DPT; ++i) dst[(size_t)(dg * DPT + i) * DV + c] = S[i];
         if (tid < NCH) {
-          __nv_bfloat16* dc = p.snap_conv + (((size_t)s * p.num_snap + j) * p.hv + vh) * 3 * NCH;
+          __nv_bfloat16* dc = p.snap_conv + (snap_entry(p, s, j) * p.hv + vh) * 3 * NCH;
           dc[tid] = __float2bfloat16_rn(x0);
           dc[NCH + tid] = __float2bfloat16_rn(x1);
           dc[2 * NCH + tid] = __float2bfloat16_rn(x2);
@@ -299,7 +304,7 @@ __global__ void __launch_bounds__(DV / NS * 4) gdn_kernel(const __grid_constant_
               const int done = tile0 + j - t0 + 1;
               for (int q = 0; q < p.num_snap; ++q) {
                 if (p.snap_rel[s * p.num_snap + q] != done) continue;
-                __nv_bfloat16* dc = p.snap_conv + (((size_t)s * p.num_snap + q) * p.hv + vh) * 3 * NCH;
+                __nv_bfloat16* dc = p.snap_conv + (snap_entry(p, s, q) * p.hv + vh) * 3 * NCH;
                 dc[hch[u]] = __float2bfloat16_rn(x0[u]);
                 dc[NCH + hch[u]] = __float2bfloat16_rn(x1[u]);
                 dc[2 * NCH + hch[u]] = __float2bfloat16_rn(x2[u]);
@@ -373,7 +378,7 @@ __global__ void __launch_bounds__(DV / NS * 4) gdn_kernel(const __grid_constant_
         const int done = tile0 + j - t0 + 1;
         for (int q = 0; q < p.num_snap; ++q) {
           if (p.snap_rel[s * p.num_snap + q] != done) continue;
-          float* dst = p.snap_state + (((size_t)s * p.num_snap + q) * p.hv + vh) * DK * DV + part * CB;
+          float* dst = p.snap_state + (snap_entry(p, s, q) * p.hv + vh) * DK * DV + part * CB;
 #pragma unroll
           for (int i = 0; i < DPT / 2; ++i) {
             dst[(size_t)(dg * DPT + 2 * i) * DV + c] = S2[i].x;

@@ -36,7 +36,12 @@ constexpr int kBM = 128;          // weight rows per CTA (TMEM lanes)
 constexpr int kBK = 64;           // bytes of k per stage (one 64-byte swizzle row)
 constexpr int kStageA = kBM * kBK;                 // 8 KB of weights per stage
 constexpr int kGemmThreads = 192;
-constexpr int kGemmRingBytes = 192 * 1024;
+#ifndef TI_GEMM_RING_KB
+#define TI_GEMM_RING_KB 192
+#endif
+// bytes of operand ring per CTA.  96 lets two CTAs share an SM (TMEM: 2 x 256 columns), so that the epilogue of
+// one overlaps the main loop of the other.
+constexpr int kGemmRingBytes = TI_GEMM_RING_KB * 1024;
 // BN = tokens per CTA (TMEM columns per accumulator); BF16: bf16 weights and activations (one plane, one accumulator)
 template <int BN, bool BF16> struct GemmGeom {
   static constexpr int kStageB = BN * kBK;                         // one limb plane / the bf16 activation tile
@@ -188,7 +193,7 @@ TI_DEVICE void gemm_epilogue4(const GemmParams& p, int m, int n, float4 v) {
 }
 
 template <int BN, bool BF16>
-__global__ void __launch_bounds__(kGemmThreads, 1) gemm_w8a16_kernel(const __grid_constant__ GemmParams p) {
+__global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) gemm_w8a16_kernel(const __grid_constant__ GemmParams p) {
   using G = GemmGeom<BN, BF16>;
   constexpr int kStages = G::kStages, kStageBytes = G::kStageBytes, kStageB = G::kStageB;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -201,7 +206,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w8a16_kernel(const __gri
   __shared__ int s_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z, S = gridDim.z;
+  // token tiles vary fastest: the CTAs that run at the same time share weight tiles (read from HBM once, then L2
+  // hits) and the limb planes of all tokens stay in L2
+  const int tile_m = blockIdx.x, tile_n = blockIdx.y, split = blockIdx.z, S = gridDim.z;
   const int KB = p.K / kBK;
   const int kb0 = split * p.kb_per_split, kb1 = min(KB, kb0 + p.kb_per_split);
   constexpr uint32_t kCols = (BF16 ? 1 : 2) * BN < 32 ? 32 : (BF16 ? 1 : 2) * BN;   // TMEM allocation: a power of two >= 32
@@ -294,9 +301,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_w8a16_kernel(const __gri
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-      const unsigned prev = atomicAdd(p.tile_count + tile_m * gridDim.x + tile_n, 1u);
+      const unsigned prev = atomicAdd(p.tile_count + tile_n * gridDim.x + tile_m, 1u);
       s_last = prev + 1 == (unsigned)S;
-      if (s_last) p.tile_count[tile_m * gridDim.x + tile_n] = 0;   // ready for the next launch
+      if (s_last) p.tile_count[tile_n * gridDim.x + tile_m] = 0;   // ready for the next launch
       __threadfence();
     }
     __syncthreads();
@@ -524,7 +531,7 @@ int ti_gemm_w8a16(const void* w, const void* wscale, int n_tiles, int N, int K, 
   p.epi = epi;
   const int tiles_n = (n_tiles * 8 + ti::kBM - 1) / ti::kBM, tiles_m = (M + BN - 1) / BN;
   const int S = ti::plan_split(p, KB, tiles_n * tiles_m, M, N, ldo, part, part_bytes, tile_count, n_count);
-  dim3 grid(tiles_n, tiles_m, S);
+  dim3 grid(tiles_m, tiles_n, S);
   cudaStream_t st = (cudaStream_t)stream;
   if (BN == 32) return ti::launch_gemm<32, false>(p, grid, st);
   if (BN == 64) return ti::launch_gemm<64, false>(p, grid, st);
@@ -554,7 +561,7 @@ int ti_gemm_bf16(const void* w, int n_tiles, int N, int K, const void* x, int M,
   p.epi = epi;
   const int tiles_n = (n_tiles * 8 + ti::kBM - 1) / ti::kBM, tiles_m = (M + BN - 1) / BN;
   const int S = ti::plan_split(p, KB, tiles_n * tiles_m, M, N, ldo, part, part_bytes, tile_count, n_count);
-  dim3 grid(tiles_n, tiles_m, S);
+  dim3 grid(tiles_m, tiles_n, S);
   cudaStream_t st = (cudaStream_t)stream;
   if (BN == 32) return ti::launch_gemm<32, true>(p, grid, st);
   if (BN == 64) return ti::launch_gemm<64, true>(p, grid, st);

@@ -29,7 +29,7 @@ GEMV_UNITS_PER_WARP = int(os.environ.get("TI_GEMV_UPW", "4"))
 class GdnParams(ctypes.Structure):
     _fields_ = [("proj", _P), ("conv_w", _P), ("neg_a_exp", _P), ("dt_bias", _P), ("norm_w", _P), ("state", _P),
                 ("conv_state", _P), ("slots", _P), ("cu", _P), ("out", _P), ("snap_rel", _P), ("snap_state", _P),
-                ("snap_conv", _P), ("ld", _I), ("hk", _I), ("hv", _I), ("num_snap", _I), ("eps", _F)]
+                ("snap_conv", _P), ("ld", _I), ("hk", _I), ("hv", _I), ("num_snap", _I), ("eps", _F), ("snap_idx", _P)]
 
 
 class QkvPrepParams(ctypes.Structure):
