@@ -549,3 +549,42 @@ def test_gemv_rowpar_handoff_to_next_product_emulated_ranks(tp, M):
         torch.testing.assert_close(hs[r].float(), ref_h, rtol=2e-2, atol=4e-2)
         torch.testing.assert_close(projs[r].float(), ref_p, rtol=3e-2, atol=6e-2)
         assert torch.equal(hs[r], hs[0]) and torch.equal(projs[r], projs[0])
+
+
+@pytest.mark.parametrize("state_bf16", [False, True])
+def test_gdn_decode_many_sequences_staged(state_bf16):
+    """64 single-token sequences x 6 heads: the decode kernel walks several sequences per block with the state
+    staged through shared memory (bulk copies, inputs fetched one sequence ahead).  Must equal the tiled kernel."""
+    F = _F()
+    torch.manual_seed(1)
+    dk = dv = 128
+    hk, hv, S = 2, 6, 64
+    nch, kd, vd = 2 * dk + dv, hk * dk, hv * dv
+    ld = 2 * kd + 2 * vd + 2 * hv + 6
+    proj = torch.randn(S, ld, device="cuda").to(BF16)
+    conv_w = torch.randn(2 * kd + vd, 4, device="cuda") * 0.5
+    neg = (-(torch.randn(hv, device="cuda") * 0.5).exp()).contiguous()
+    dt_bias = torch.randn(hv, device="cuda") * 0.5
+    norm_w = 1 + 0.1 * torch.randn(dv, device="cuda")
+    slots = torch.randperm(S + 3, device="cuda")[:S].to(torch.int32)
+    sdt = BF16 if state_bf16 else torch.float32
+    state0 = (torch.randn(S + 3, hv, dk, dv, device="cuda") * 0.1).to(sdt)
+    cs0 = torch.randn(S + 3, hv, 3, nch, device="cuda").to(BF16)
+    outs = []
+    for single in (True, False):
+        state, cs = state0.clone(), cs0.clone()
+        out = torch.zeros(S, vd, dtype=BF16, device="cuda")
+        p = F.GdnParams()
+        p.proj, p.conv_w, p.neg_a_exp = proj.data_ptr(), conv_w.data_ptr(), neg.data_ptr()
+        p.dt_bias, p.norm_w = dt_bias.data_ptr(), norm_w.data_ptr()
+        p.state, p.conv_state, p.slots, p.out = state.data_ptr(), cs.data_ptr(), slots.data_ptr(), out.data_ptr()
+        p.ld, p.hk, p.hv, p.eps = ld, hk, hv, 1e-6
+        F.gdn_step(p, S, dk, dv, state_bf16, single=single)
+        torch.cuda.synchronize()
+        outs.append((out, state, cs))
+    (o1, s1, c1), (o2, s2, c2) = outs
+    torch.testing.assert_close(o1.float(), o2.float(), rtol=2e-2, atol=1e-2)
+    torch.testing.assert_close(s1.float(), s2.float(), rtol=1e-2 if state_bf16 else 1e-4, atol=1e-3 if state_bf16 else 1e-5)
+    assert torch.equal(c1, c2)
+    untouched = [i for i in range(S + 3) if i not in set(slots.tolist())]
+    assert torch.equal(s1[untouched], state0[untouched])

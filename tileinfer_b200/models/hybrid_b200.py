@@ -492,7 +492,7 @@ class _RunMixin:
         qg_seq, qg_tok0, qg_ntok = self._fill_ctx(None, batch)
         nq = len(qg_seq)
         max_blocks = max(len(b) for b in batch.block_tables)
-        nsplit = 1 if nq * self.hkv >= 148 else max(1, min(32, -(-296 // (nq * self.hkv))))
+        nsplit = 1 if nq * self.hkv >= 148 else max(1, min(32, -(-1184 // (nq * self.hkv))))
         x = self._alloc_ctx(T, S, max_blocks, nq, nsplit)
         x.ids.copy_(batch.input_ids, non_blocking=True)
         x.positions.copy_(batch.positions.to(torch.int32), non_blocking=True)
@@ -559,7 +559,7 @@ class _RunMixin:
         if g is not None:
             return g
         dev = self.dev
-        nsplit = max(1, min(32, -(-296 // (B * self.hkv))))
+        nsplit = max(1, min(32, -(-1184 // (B * self.hkv))))
         base = self.graphs.get((B, 1))
         g = _Ctx()
         if base is not None:      # same bucket, other k: share the input tensors

@@ -17,6 +17,8 @@
 //
 // Conv history layout: [slot][v-head][3][2*DK + DV]; every v-head keeps its own copy of the q/k
 // history of the key head it shares, so blocks never write memory another block reads.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace ti {
@@ -54,125 +56,215 @@ template <> TI_DEVICE void st_state<__nv_bfloat16>(__nv_bfloat16* p, float v) { 
 // Decode form (every sequence of the step has one token): everything of a token in one pass, two block
 // barriers.  The tiled kernel below does the same arithmetic per token but stages a tile's worth of q / k / v
 // through shared memory, which costs a decode step several microseconds per layer for nothing.
-template <int DK, int DV, typename ST>
-__global__ void __launch_bounds__(DV * 4) gdn_token_kernel(const __grid_constant__ GdnParams p) {
+// STAGED (large decode batches): a block walks several sequences of its v-head.  The 64 KB state of the NEXT
+// sequence is fetched into shared memory by a bulk copy while the current one is being worked on, and the updated
+// state goes back through shared memory with a bulk store, so a block is not idle for a memory round trip per
+// sequence (one block per SM fits; with direct loads that was 21 serialised waves at batch 64).
+TI_DEVICE void bulk_s2g(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+  asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+}
+TI_DEVICE void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
+TI_DEVICE void bulk_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
+
+template <int DK, int DV, typename ST, bool STAGED>
+__global__ void __launch_bounds__(DV * 4) gdn_token_kernel(const __grid_constant__ GdnParams p, int num_seqs) {
   constexpr int DPT = DK / 4;           // state elements per thread
   constexpr int NCH = 2 * DK + DV;      // conv channels this block needs
   constexpr int NW = DV * 4 / 32;
+  constexpr uint32_t kStateBytes = DK * DV * sizeof(ST);
   static_assert(NCH <= DV * 4, "one thread per conv channel");
   __shared__ float qs[DK], ks[DK], vs[DV], red[NW];
+  __shared__ __align__(8) unsigned long long full_bar[2];
+  extern __shared__ __align__(128) uint8_t stage_raw[];      // STAGED: two state buffers
+  ST* sbuf0 = reinterpret_cast<ST*>(stage_raw);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int c = tid >> 2, dg = tid & 3;
-  const int vh = blockIdx.x, s = blockIdx.y;
+  const int vh = blockIdx.x;
   const int kh = vh / (p.hv / p.hk);
-  // cu / slots are written by host copies that precede every kernel of the step; the recurrent state
-  // and conv history were last written one step ago: all of this may be read before pdl_wait()
-  const int t0 = p.cu ? p.cu[s] : s, t1 = p.cu ? p.cu[s + 1] : s + 1;
-  const int slot = p.slots[s];
-
-  ST* Sp = static_cast<ST*>(p.state) + ((size_t)slot * p.hv + vh) * DK * DV;
-  float S[DPT];
-#pragma unroll
-  for (int i = 0; i < DPT; ++i) S[i] = ld_state<ST>(Sp + (size_t)(dg * DPT + i) * DV + c);
-
-  // conv channel owned by this thread: column in `proj` and row of conv_w
-  __nv_bfloat16* cs = p.conv_state + ((size_t)slot * p.hv + vh) * 3 * NCH;
-  float x0 = 0.f, x1 = 0.f, x2 = 0.f, cw0 = 0.f, cw1 = 0.f, cw2 = 0.f, cw3 = 0.f;
-  int col = 0;
-  if (tid < NCH) {
-    if (tid < DK) col = kh * DK + tid;
-    else if (tid < 2 * DK) col = p.hk * DK + kh * DK + (tid - DK);
-    else col = 2 * p.hk * DK + vh * DV + (tid - 2 * DK);
-    const float4 w = *reinterpret_cast<const float4*>(p.conv_w + (size_t)col * 4);
-    cw0 = w.x; cw1 = w.y; cw2 = w.z; cw3 = w.w;
-    x0 = __bfloat162float(cs[tid]);
-    x1 = __bfloat162float(cs[NCH + tid]);
-    x2 = __bfloat162float(cs[2 * NCH + tid]);
-  }
   const int zcol = 2 * p.hk * DK + p.hv * DV + vh * DV;
   const int bcol = 2 * p.hk * DK + 2 * p.hv * DV + vh;
   const int acol = bcol + p.hv;
   const float neg_a = p.neg_a_exp[vh], dtb = p.dt_bias[vh];
   const float nw = p.norm_w[c];
   const float qscale = rsqrtf((float)DK);
-  pdl_trigger();
-  pdl_wait();                                    // `proj` comes from the preceding projection kernel
+  int col = 0;
+  float cw0 = 0.f, cw1 = 0.f, cw2 = 0.f, cw3 = 0.f;
+  if (tid < NCH) {
+    if (tid < DK) col = kh * DK + tid;
+    else if (tid < 2 * DK) col = p.hk * DK + kh * DK + (tid - DK);
+    else col = 2 * p.hk * DK + vh * DV + (tid - 2 * DK);
+    const float4 w = *reinterpret_cast<const float4*>(p.conv_w + (size_t)col * 4);
+    cw0 = w.x; cw1 = w.y; cw2 = w.z; cw3 = w.w;
+  }
+  auto state_ptr = [&](int seq) { return static_cast<ST*>(p.state) + ((size_t)p.slots[seq] * p.hv + vh) * DK * DV; };
+  if (STAGED) {
+    if (tid == 0) {
+      mbar_init(smem_u32(&full_bar[0]), 1);
+      mbar_init(smem_u32(&full_bar[1]), 1);
+      fence_mbar_init();
+      // the recurrent state was last written one step ago: it may be fetched before pdl_wait()
+      mbar_expect_tx(smem_u32(&full_bar[0]), kStateBytes);
+      bulk_g2s(smem_u32(sbuf0), state_ptr(blockIdx.y), kStateBytes, smem_u32(&full_bar[0]));
+    }
+    __syncthreads();
+  }
 
-  for (int tok = t0; tok < t1; ++tok) {
-    const __nv_bfloat16* row = p.proj + (size_t)tok * p.ld;
+  // STAGED also fetches the NEXT sequence's inputs (conv history, projection row entries) one item ahead, so that
+  // an item's critical path holds no global round trip.  (STAGED is used for single-token sequences only.)
+  struct Inputs { float x0, x1, x2, x3, a, b, z; };
+  auto fetch = [&](int seq) {
+    Inputs in{0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const int tokn = p.cu ? p.cu[seq] : seq;
+    const __nv_bfloat16* rown = p.proj + (size_t)tokn * p.ld;
+    const __nv_bfloat16* csn = p.conv_state + ((size_t)p.slots[seq] * p.hv + vh) * 3 * NCH;
     if (tid < NCH) {
-      const float x3 = __bfloat162float(row[col]);
-      const float y = silu_f(cw0 * x0 + cw1 * x1 + cw2 * x2 + cw3 * x3);
-      x0 = x1; x1 = x2; x2 = x3;
-      if (tid < DK) qs[tid] = y;
-      else if (tid < 2 * DK) ks[tid - DK] = y;
-      else vs[tid - 2 * DK] = y;
+      in.x0 = __bfloat162float(csn[tid]);
+      in.x1 = __bfloat162float(csn[NCH + tid]);
+      in.x2 = __bfloat162float(csn[2 * NCH + tid]);
+      in.x3 = __bfloat162float(rown[col]);
     }
-    __syncthreads();
-    float sq = 0.f, sk = 0.f;
-    for (int i = lane; i < DK; i += 32) { sq += qs[i] * qs[i]; sk += ks[i] * ks[i]; }
-    sq = warp_sum(sq);
-    sk = warp_sum(sk);
-    const float qn = rsqrtf(sq + 1e-6f) * qscale, kn = rsqrtf(sk + 1e-6f);
-    const float a = __bfloat162float(row[acol]) + dtb;
-    const float sp = a > 20.f ? a : log1pf(__expf(a));
-    const float decay = __expf(neg_a * sp);
-    const float beta = sigmoid_f(__bfloat162float(row[bcol]));
+    in.a = __bfloat162float(rown[acol]);
+    in.b = __bfloat162float(rown[bcol]);
+    in.z = __bfloat162float(rown[zcol + c]);
+    return in;
+  };
+  Inputs cur{0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, nxt = cur;
 
-    float kv = 0.f;
-#pragma unroll
-    for (int i = 0; i < DPT; ++i) { S[i] *= decay; kv += S[i] * ks[dg * DPT + i]; }
-    kv += __shfl_xor_sync(0xffffffffu, kv, 1);
-    kv += __shfl_xor_sync(0xffffffffu, kv, 2);
-    const float delta = (vs[c] - kv * kn) * beta;
-    const float kd = kn * delta;
-    float o = 0.f;
-#pragma unroll
-    for (int i = 0; i < DPT; ++i) { S[i] += ks[dg * DPT + i] * kd; o += S[i] * qs[dg * DPT + i]; }
-    o += __shfl_xor_sync(0xffffffffu, o, 1);
-    o += __shfl_xor_sync(0xffffffffu, o, 2);
-    o *= qn;
-
-    float o2 = dg == 0 ? o * o : 0.f;
-    o2 = warp_sum(o2);
-    if (lane == 0) red[warp] = o2;
-    __syncthreads();
-    float tot = 0.f;
-#pragma unroll
-    for (int w = 0; w < NW; ++w) tot += red[w];
-    const float rr = rsqrtf(tot / (float)DV + p.eps);
-    if (dg == 0) {
-      const float z = __bfloat162float(row[zcol + c]);
-      p.out[(size_t)tok * p.hv * DV + vh * DV + c] = __float2bfloat16_rn(o * rr * nw * silu_f(z));
+  int k = 0;
+  for (int s = blockIdx.y; s < num_seqs; s += gridDim.y, ++k) {
+    // cu / slots are written by host copies that precede every kernel of the step; the recurrent state
+    // and conv history were last written one step ago: all of this may be read before pdl_wait()
+    const int t0 = p.cu ? p.cu[s] : s, t1 = p.cu ? p.cu[s + 1] : s + 1;
+    const int slot = p.slots[s];
+    ST* Sp = static_cast<ST*>(p.state) + ((size_t)slot * p.hv + vh) * DK * DV;
+    ST* sb = sbuf0 + (size_t)(k & 1) * DK * DV;
+    if (STAGED && tid == 0 && s + (int)gridDim.y < num_seqs) {
+      // next sequence -> the other buffer, once the bulk store that last read that buffer is done with it
+      bulk_store_wait_read();
+      const uint32_t bar = smem_u32(&full_bar[(k + 1) & 1]);
+      mbar_expect_tx(bar, kStateBytes);
+      bulk_g2s(smem_u32(sbuf0 + (size_t)((k + 1) & 1) * DK * DV), state_ptr(s + gridDim.y), kStateBytes, bar);
     }
-    if (p.snap_rel != nullptr) {
-      const int done = tok - t0 + 1;
-      for (int j = 0; j < p.num_snap; ++j) {
-        if (p.snap_rel[s * p.num_snap + j] != done) continue;
-        float* dst = p.snap_state + (snap_entry(p, s, j) * p.hv + vh) * DK * DV;
+    float S[DPT];
+    if (!STAGED) {
 #pragma unroll
-        for (int i = 0; i < DPT; ++i) dst[(size_t)(dg * DPT + i) * DV + c] = S[i];
-        if (tid < NCH) {
-          __nv_bfloat16* dc = p.snap_conv + (snap_entry(p, s, j) * p.hv + vh) * 3 * NCH;
-          dc[tid] = __float2bfloat16_rn(x0);
-          dc[NCH + tid] = __float2bfloat16_rn(x1);
-          dc[2 * NCH + tid] = __float2bfloat16_rn(x2);
-        }
+      for (int i = 0; i < DPT; ++i) S[i] = ld_state<ST>(Sp + (size_t)(dg * DPT + i) * DV + c);
+    }
+    // conv channel owned by this thread
+    __nv_bfloat16* cs = p.conv_state + ((size_t)slot * p.hv + vh) * 3 * NCH;
+    float x0 = 0.f, x1 = 0.f, x2 = 0.f;
+    if (!STAGED || k == 0) {
+      if (tid < NCH) {
+        x0 = __bfloat162float(cs[tid]);
+        x1 = __bfloat162float(cs[NCH + tid]);
+        x2 = __bfloat162float(cs[2 * NCH + tid]);
       }
     }
-    __syncthreads();
-  }
-
+    if (k == 0) {
+      pdl_trigger();
+      pdl_wait();                                  // `proj` comes from the preceding projection kernel
+    }
+    if (STAGED) {
+      if (k == 0) {
+        cur = fetch(s);
+        cur.x0 = x0; cur.x1 = x1; cur.x2 = x2;
+      } else {
+        cur = nxt;
+      }
+      x0 = cur.x0; x1 = cur.x1; x2 = cur.x2;
+      if (s + (int)gridDim.y < num_seqs) nxt = fetch(s + gridDim.y);
+    }
+    if (STAGED) {
+      mbar_wait(smem_u32(&full_bar[k & 1]), (uint32_t)((k >> 1) & 1), 2000000000ull, nullptr);
 #pragma unroll
-  for (int i = 0; i < DPT; ++i) st_state<ST>(Sp + (size_t)(dg * DPT + i) * DV + c, S[i]);
-  if (tid < NCH) {
-    cs[tid] = __float2bfloat16_rn(x0);
-    cs[NCH + tid] = __float2bfloat16_rn(x1);
-    cs[2 * NCH + tid] = __float2bfloat16_rn(x2);
-  }
-}
+      for (int i = 0; i < DPT; ++i) S[i] = ld_state<ST>(sb + (size_t)(dg * DPT + i) * DV + c);
+    }
 
+    for (int tok = t0; tok < t1; ++tok) {
+      const __nv_bfloat16* row = p.proj + (size_t)tok * p.ld;
+      if (tid < NCH) {
+        const float x3 = STAGED ? cur.x3 : __bfloat162float(row[col]);
+        const float y = silu_f(cw0 * x0 + cw1 * x1 + cw2 * x2 + cw3 * x3);
+        x0 = x1; x1 = x2; x2 = x3;
+        if (tid < DK) qs[tid] = y;
+        else if (tid < 2 * DK) ks[tid - DK] = y;
+        else vs[tid - 2 * DK] = y;
+      }
+      __syncthreads();
+      float sq = 0.f, sk = 0.f;
+      for (int i = lane; i < DK; i += 32) { sq += qs[i] * qs[i]; sk += ks[i] * ks[i]; }
+      sq = warp_sum(sq);
+      sk = warp_sum(sk);
+      const float qn = rsqrtf(sq + 1e-6f) * qscale, kn = rsqrtf(sk + 1e-6f);
+      const float a = (STAGED ? cur.a : __bfloat162float(row[acol])) + dtb;
+      const float sp = a > 20.f ? a : log1pf(__expf(a));
+      const float decay = __expf(neg_a * sp);
+      const float beta = sigmoid_f(STAGED ? cur.b : __bfloat162float(row[bcol]));
+
+      float kv = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) { S[i] *= decay; kv += S[i] * ks[dg * DPT + i]; }
+      kv += __shfl_xor_sync(0xffffffffu, kv, 1);
+      kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+      const float delta = (vs[c] - kv * kn) * beta;
+      const float kd = kn * delta;
+      float o = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) { S[i] += ks[dg * DPT + i] * kd; o += S[i] * qs[dg * DPT + i]; }
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      o *= qn;
+
+      float o2 = dg == 0 ? o * o : 0.f;
+      o2 = warp_sum(o2);
+      if (lane == 0) red[warp] = o2;
+      __syncthreads();
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) tot += red[w];
+      const float rr = rsqrtf(tot / (float)DV + p.eps);
+      if (dg == 0) {
+        const float z = STAGED ? cur.z : __bfloat162float(row[zcol + c]);
+        p.out[(size_t)tok * p.hv * DV + vh * DV + c] = __float2bfloat16_rn(o * rr * nw * silu_f(z));
+      }
+      if (p.snap_rel != nullptr) {
+        const int done = tok - t0 + 1;
+        for (int j = 0; j < p.num_snap; ++j) {
+          if (p.snap_rel[s * p.num_snap + j] != done) continue;
+          float* dst = p.snap_state + (snap_entry(p, s, j) * p.hv + vh) * DK * DV;
+#pragma unroll
+          for (int i = 0; i < DPT; ++i) dst[(size_t)(dg * DPT + i) * DV + c] = S[i];
+          if (tid < NCH) {
+            __nv_bfloat16* dc = p.snap_conv + (snap_entry(p, s, j) * p.hv + vh) * 3 * NCH;
+            dc[tid] = __float2bfloat16_rn(x0);
+            dc[NCH + tid] = __float2bfloat16_rn(x1);
+            dc[2 * NCH + tid] = __float2bfloat16_rn(x2);
+          }
+        }
+      }
+      __syncthreads();
+    }
+
+    if (STAGED) {
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) st_state<ST>(sb + (size_t)(dg * DPT + i) * DV + c, S[i]);
+      fence_proxy_async();                         // generic-proxy writes -> visible to the bulk store
+      __syncthreads();
+      if (tid == 0) bulk_s2g(Sp, smem_u32(sb), kStateBytes);
+    } else {
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) st_state<ST>(Sp + (size_t)(dg * DPT + i) * DV + c, S[i]);
+    }
+    if (tid < NCH) {
+      cs[tid] = __float2bfloat16_rn(x0);
+      cs[NCH + tid] = __float2bfloat16_rn(x1);
+      cs[2 * NCH + tid] = __float2bfloat16_rn(x2);
+    }
+  }
+  if (STAGED && tid == 0) bulk_store_wait_all();   // shared memory must outlive the stores that read it
+}
 
 // Tokens are processed in tiles of kTT.  Per tile: (1) every conv channel runs its window over the tile's tokens
 // (independent global loads, no synchronisation) and the per-token scalars (q/k norms, decay, beta) are worked
@@ -432,6 +524,18 @@ __global__ void __launch_bounds__(DV / NS * 4) gdn_kernel(const __grid_constant_
   if (NS > 1) cluster_sync_all();                  // nobody leaves while a neighbour may still read its partial sums
 }
 
+template <int DK, int DV, typename ST, bool STAGED>
+static cudaError_t launch_token(const GdnParams& p, int num_seqs, dim3 grid, cudaStream_t st) {
+  auto k = gdn_token_kernel<DK, DV, ST, STAGED>;
+  const size_t smem = STAGED ? 2 * (size_t)DK * DV * sizeof(ST) : 0;
+  static bool configured = false;
+  if (STAGED && !configured) {
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    configured = true;
+  }
+  return launch_kernel(k, grid, dim3(DV * 4), smem, st, true, p, num_seqs);
+}
+
 // Launch with programmatic stream serialization and, for NS > 1, clusters of NS blocks along x.
 template <int DK, int DV, typename ST, int NS>
 static cudaError_t launch_gdn(const GdnParams& p, int num_seqs, cudaStream_t st) {
@@ -473,13 +577,20 @@ int ti_gdn_step(const ti::GdnParams* p, int num_seqs, int dk, int dv, int state_
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
   if (split == 2) {                     // one token per sequence: the single-pass decode kernel
-    dim3 grid(p->hv, num_seqs);
+    // more (head, sequence) pairs than two waves of SMs: blocks walk several sequences with staged state
+    const bool staged = (long long)p->hv * num_seqs > 2 * 148;
+    const int gy = staged ? std::max(1, 148 / p->hv) : num_seqs;
+    dim3 grid(p->hv, gy);
     if (dk == 128 && dv == 128) {
-      if (state_bf16) e = ti::launch_kernel(ti::gdn_token_kernel<128, 128, __nv_bfloat16>, grid, dim3(512), 0, st, true, *p);
-      else e = ti::launch_kernel(ti::gdn_token_kernel<128, 128, float>, grid, dim3(512), 0, st, true, *p);
+      if (staged) e = state_bf16 ? ti::launch_token<128, 128, __nv_bfloat16, true>(*p, num_seqs, grid, st)
+                                 : ti::launch_token<128, 128, float, true>(*p, num_seqs, grid, st);
+      else e = state_bf16 ? ti::launch_token<128, 128, __nv_bfloat16, false>(*p, num_seqs, grid, st)
+                          : ti::launch_token<128, 128, float, false>(*p, num_seqs, grid, st);
     } else if (dk == 64 && dv == 64) {
-      if (state_bf16) e = ti::launch_kernel(ti::gdn_token_kernel<64, 64, __nv_bfloat16>, grid, dim3(256), 0, st, true, *p);
-      else e = ti::launch_kernel(ti::gdn_token_kernel<64, 64, float>, grid, dim3(256), 0, st, true, *p);
+      if (staged) e = state_bf16 ? ti::launch_token<64, 64, __nv_bfloat16, true>(*p, num_seqs, grid, st)
+                                 : ti::launch_token<64, 64, float, true>(*p, num_seqs, grid, st);
+      else e = state_bf16 ? ti::launch_token<64, 64, __nv_bfloat16, false>(*p, num_seqs, grid, st)
+                          : ti::launch_token<64, 64, float, false>(*p, num_seqs, grid, st);
     } else {
       return -3;
     }
