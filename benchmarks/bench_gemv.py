@@ -40,6 +40,8 @@ def _print_timeline(dbg, n_ops):
     for op in range(n_ops):
         for k, nm in enumerate(("marker reached", "barrier passed", "x staged", "last unit done")):
             row(f"op{op} {nm}", 8 + 4 * op + k)
+    for op in range(1, min(n_ops, 4)):
+        row(f"all warps of the CTA at barrier before op{op}", 1 + op)
     for op in range(min(n_ops, 2)):
         for k, nm in enumerate(("unit popped", "first chunk arrived", "tiles done")):
             row(f"op{op} warp0 last unit: {nm}", 24 + 4 * op + k)

@@ -53,7 +53,8 @@ struct GemvParams {
   int stages;                    // depth of the per-warp weight ring (1..8)
   int T;                         // team size (1, 2, 4, 8 or 16 warps of a CTA share a unit, each a k-slice)
   unsigned long long* dbg;       // optional [ncta][32] globaltimer stamps of warp 0 (profiling aid): 0 start, 1 ring
-                                 // primed, 5 end; per product op at 8 + 4*op: marker reached, barrier passed, x staged, last unit done
+                                 // primed, 2..4 all warps of the CTA reached the barrier before product 1..3, 5 end; per product op at 8 + 4*op:
+                                 // marker reached, barrier passed, x staged, last unit done
   int* sched;                    // dynamic scheduling state: [0] launches finished, [1] CTAs finished, [8 + 3*16] tickets
   int tps;                       // 512-byte tiles per ring stage (4, 8 or 16)
   int xmode, epi;                // XGLOBAL | XNORM ; EPI_*
@@ -590,9 +591,10 @@ struct WarpStream {           // registers of lane 0 of each warp; queue storage
 
 // Grid-wide barrier between chained products.  All CTAs of the launch are resident (one per SM), the
 // counter is reset by the last CTA of the launch.  The wait is bounded like every other wait here.
-TI_DEVICE void grid_barrier(int* counter, int target, unsigned* status) {
+TI_DEVICE void grid_barrier(int* counter, int target, unsigned* status, unsigned long long* arrived = nullptr) {
   __syncthreads();
   if (threadIdx.x == 0) {
+    if (arrived != nullptr) *arrived = globaltimer_ns();   // every warp of this CTA is done with the product
     __threadfence();
     atomicAdd(counter, 1);
     const unsigned long long t0 = globaltimer_ns();
@@ -696,7 +698,7 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
         rowpar_reduce(c.op[op - 1], 0, 1);
         __syncthreads();
       } else if (op > 0) {
-        grid_barrier(p0.sched + 2, ++nbar * ncta, p0.status);
+        grid_barrier(p0.sched + 2, ++nbar * ncta, p0.status, p0.dbg != nullptr && op <= 3 ? p0.dbg + cta * 32 + 1 + op : nullptr);   // stamps 2..4
       } else {
         __syncthreads();
       }
