@@ -466,24 +466,46 @@ TI_DEVICE void stage_bf16_norm(const GemvParams& p, __nv_bfloat16* xs, int xs_st
 // memory behind a named barrier and the first warp of the team adds them in slice order and runs the epilogue.
 // Team units are dealt statically, unit u to team u mod (number of teams).
 TI_DEVICE int num_units(const GemvParams& p) { return (p.n_tiles + p.R - 1) / p.R; }
-// k-slice [kt0, kt0 + run) of team member j
-TI_DEVICE void team_slice(const GemvParams& p, int j, int& kt0, int& run) {
-  const int base = p.KB / p.T, rem = p.KB - base * p.T;
-  kt0 = j * base + min(j, rem);
-  run = base + (j < rem ? 1 : 0);
-}
 #define TI_UNIT_END (-1)
 constexpr int kUnitMask = (1 << 26) - 1;
 TI_DEVICE int pack_unit(int op, int unit) { return (op << 26) | unit; }
 // queue entry that opens product `op`: every warp sees it (and takes part in the grid barrier and the
 // activation staging of that product) whether or not it gets any unit of the product
 TI_DEVICE int pack_begin(int op) { return (op << 26) | kUnitMask; }
-// Units k*W + widx for k < num_static are assigned statically (no atomics: they can be queued before the
-// kernel may look at mutable state); the rest of a product's units go through the ticket counter, which
-// evens out warps that fell behind.
-TI_DEVICE int num_static(const GemvParams& p, int W) { return max(1, num_units(p) / (2 * W)); }
+// Units k*W + widx for k < ns are assigned statically (no atomics: they can be queued before the kernel may
+// look at mutable state); the rest of a product's units go through the ticket counter, which evens out warps
+// that fell behind.
+// Per-warp, per-product scheduling constants, worked out once at kernel start (they hold integer divisions that
+// would otherwise be redone by lane 0 for every unit, with the other lanes of the warp and the warp's issue slots
+// waiting; with the short units of tensor-parallel shards that was a third of a product's time).
+enum { TB_U = 0, TB_WD, TB_NS, TB_WIDX, TB_MEMBER, TB_BASE, TB_REM, TB_T, TB_N };
+TI_DEVICE void fill_op_table(const ChainParams& c, int warp, int cta, int ncta, int* tb) {
+  const int W = ncta * kWarps, widx = warp * ncta + cta;
+  for (int op = 0; op < c.n_ops; ++op) {
+    const GemvParams& p = c.op[op];
+    const int U = num_units(p), T = p.T;
+    const int Wd = T > 1 ? W / T : W;
+    int* t = tb + op * TB_N;
+    t[TB_U] = U;
+    t[TB_WD] = Wd;
+    t[TB_NS] = T > 1 ? (U + Wd - 1) / Wd : max(1, U / (2 * W));
+    t[TB_WIDX] = T > 1 ? (warp / T) * ncta + cta : widx;
+    t[TB_MEMBER] = T > 1 ? warp % T : 0;
+    t[TB_BASE] = p.KB / T;
+    t[TB_REM] = p.KB - (p.KB / T) * T;
+    t[TB_T] = T;
+  }
+}
+// k-slice [kt0, kt0 + run) of this warp in product `op` (the whole k range outside team mode)
+TI_DEVICE void my_slice(const int* tb, int op, int& kt0, int& run) {
+  const int* t = tb + op * TB_N;
+  const int j = t[TB_MEMBER], base = t[TB_BASE], rem = t[TB_REM];
+  kt0 = j * base + min(j, rem);
+  run = base + (j < rem ? 1 : 0);
+}
 
 struct WarpStream {           // registers of lane 0 of each warp; queue storage in shared memory
+  const int* tb;              // this warp's table of scheduling constants
   // scheduling side
   int op, sk, wr, rd;
   bool sdone, can_ticket, opened;
@@ -498,12 +520,9 @@ struct WarpStream {           // registers of lane 0 of each warp; queue storage
   TI_DEVICE void schedule(const ChainParams& c, int widx, int W, volatile int* q, int ahead) {
     while (!sdone && wr - rd < kCQ - 2) {
       const GemvParams& p = c.op[op];
-      const int U = num_units(p);
       // team mode: the "worker" is the team, and every unit is static
-      const int ncta = W / kWarps;
-      const int Wd = p.T > 1 ? W / p.T : W;
-      const int wd = p.T > 1 ? (widx / ncta / p.T) * ncta + widx % ncta : widx;
-      const int ns = p.T > 1 ? (U + Wd - 1) / Wd : num_static(p, W);
+      const int* t = tb + op * TB_N;
+      const int U = t[TB_U], Wd = t[TB_WD], wd = t[TB_WIDX], ns = t[TB_NS];
       if (!opened) {
         opened = true;
         push(q, pack_begin(op));
@@ -522,7 +541,7 @@ struct WarpStream {           // registers of lane 0 of each warp; queue storage
       // is then still a ring's depth of chunks behind, which covers the latency of the atomic
       // (no draw at all when the static deal already covers the product: 2368 warps hitting one counter at
       // the end of every small product cost microseconds)
-      const int u = (p.T > 1 || ns * W >= U) ? U : ns * W + atomicAdd(p.sched + 8 + op * 16, 1);
+      const int u = (t[TB_T] > 1 || ns * W >= U) ? U : ns * W + atomicAdd(p.sched + 8 + op * 16, 1);
       if (u >= U) {
         sk = 0;
         opened = false;
@@ -552,8 +571,8 @@ struct WarpStream {           // registers of lane 0 of each warp; queue storage
       const GemvParams& p = c.op[e >> 26];
       // one run of tiles per row tile of the unit; outside team mode the runs are adjacent in memory
       const int grp = unit;
-      int kt0 = 0, run = p.KB;
-      if (p.T > 1) team_slice(p, (widx / (W / kWarps)) % p.T, kt0, run);
+      int kt0, run;
+      my_slice(tb, e >> 26, kt0, run);
       const int rn = min(p.R, p.n_tiles - grp * p.R);
       left = rn * run;
       row_left = run;
@@ -634,7 +653,12 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
   volatile int* q = reinterpret_cast<volatile int*>(after_ring + kWarps * stages * 8) + warp * kCQ;
   float4* tscr = reinterpret_cast<float4*>(after_ring + kWarps * (stages * 8 + kCQ * 4));   // [2][kWarps][32], team mode
 
+  __shared__ int optab[kWarps][kMaxChain * TB_N];
+  int* tb = optab[warp];
+  if (lane == 0) fill_op_table(c, warp, cta, ncta, tb);
+  __syncwarp();
   WarpStream ws;
+  ws.tb = tb;
   ws.op = ws.sk = ws.wr = ws.rd = 0;
   ws.sdone = ws.can_ticket = ws.opened = false;
   ws.cs = ws.idx = ws.left = ws.row_left = ws.kb_row = 0;
@@ -657,6 +681,7 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
 
   unsigned cidx = 0;                            // chunks consumed by this warp so far
   uint32_t cst = 0, cpar = 0;                   // ring stage / mbarrier phase of the next chunk to consume
+  unsigned tcount = 0;                          // team exchanges of this warp in the current product
   int cur_op = -1, nbar = 0;                    // nbar: grid barriers passed (the same sequence in every CTA)
   bool alive = true;
   float* scratch = reinterpret_cast<float*>(smem + x_bytes - 2048);
@@ -687,6 +712,7 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
     const GemvParams& p = c.op[op];
     if (unit == kUnitMask) {
       cur_op = op;
+      tcount = 0;
       if (stamp) p0.dbg[cta * 32 + 8 + 4 * op] = globaltimer_ns();
       if (lane == 0)                              // start streaming this product's first unit while waiting
         for (int s = ws.idx - (int)cidx; s < stages; ++s) ws.next(c, widx, W, q, ring_u32, bar0, stages);
@@ -721,11 +747,9 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
     const bool fine = stamp && op <= 1;           // fine-grained stamps of warp 0's last unit of products 0 and 1
     if (fine) p0.dbg[cta * 32 + 24 + 4 * op] = globaltimer_ns();
     const int grp = unit;
-    int kt0 = 0, kt1 = p.KB;
-    if (p.T > 1) {
-      team_slice(p, warp % p.T, kt0, kt1);
-      kt1 += kt0;
-    }
+    int kt0, kt1;
+    my_slice(tb, op, kt0, kt1);
+    kt1 += kt0;
     const int rn = min(p.R, p.n_tiles - grp * p.R);
     // rows of the staged activations this lane feeds to the MMA (rows >= M are clamped: their results
     // are never written)
@@ -809,9 +833,9 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
       if (p.T > 1) {
         // partial sums of the team meet in shared memory (two alternating slots: the barrier of exchange n+1
         // orders the leader's reads of slot n before anybody's writes of exchange n+2)
-        // (the slot is the parity of the team's unit count WITHIN this product: teams of different sizes in
+        // (the slot is the parity of the team's exchange count WITHIN this product: teams of different sizes in
         // consecutive products are made of warps with different histories)
-        const int slot = (unit / (W / p.T) * p.R + r) & 1;
+        const int slot = (int)(tcount++ & 1u);
         float4* ex = tscr + (size_t)slot * kWarps * 32;
         ex[warp * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
         const int team = warp / p.T;
@@ -902,7 +926,7 @@ static int prepare(ChainParams& c, int wt) {
     xb = std::max(xb, op_x_bytes(c.op[i], wt));
   }
   c.x_bytes = xb;
-  if (smem_bytes(c) > 227 * 1024) return -4;
+  if (smem_bytes(c) > 227 * 1024 - 4096) return -4;      // 4 KB are static (queues' tables, reduction scratch)
   return 0;
 }
 
@@ -913,7 +937,7 @@ static int launch(const ChainParams& c, int ncta, cudaStream_t st, const ChainPa
   if (dev_list == nullptr) {
     auto k = gemv_kernel<WT>;
     if (!configured) {
-      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 4096);
       configured = true;
     }
     cudaError_t e = launch_kernel(k, dim3(ncta), dim3(kThreads), sm, st, true, c);
@@ -921,7 +945,7 @@ static int launch(const ChainParams& c, int ncta, cudaStream_t st, const ChainPa
   } else {
     auto k = gemv_kernel_ranks<WT>;
     if (!configured_ranks) {
-      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 4096);
       configured_ranks = true;
     }
     void* args[] = {(void*)&dev_list, (void*)&ncta};

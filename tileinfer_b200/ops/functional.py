@@ -158,6 +158,7 @@ def x_smem_bytes(wt: int, xmode: int, M: int, K: int, kslice: int) -> int:
 
 
 PART_BYTES = 0
+SMEM_LIMIT = 227 * 1024 - 4096      # dynamic shared memory of the GEMV kernel (4 KB of the 227 are static)
 GEMV_TPS = int(os.environ.get("TI_GEMV_TPS", "8"))       # must match the -DTI_GEMV_TPS the library was built with
 _RING_CHOICES = tuple((GEMV_TPS, s) for s in range(48 // GEMV_TPS, 0, -1))
 
@@ -170,7 +171,7 @@ def plan_gemv(wt: int, xmode: int, M: int, n_tiles: int, KB: int, ncta: int = NU
     xb = x_smem_bytes(wt, xmode, M, KB * tk, KB * tk)
     R = 2 if n_tiles >= 8 * ncta * GEMV_WARPS else 1
     for tps, stages in _RING_CHOICES:
-        if xb + PART_BYTES + GEMV_WARPS * (stages * (tps * 512 + 8) + 64) <= 227 * 1024:
+        if xb + PART_BYTES + GEMV_WARPS * (stages * (tps * 512 + 8) + 64) <= SMEM_LIMIT:
             return R, tps, stages
     return None
 
@@ -284,7 +285,7 @@ def make_chain(params: list) -> ChainParams:
     tps, stages = min((p.tps * p.stages, p.tps, p.stages) for p in params)[1:]
     # team mode needs its exchange buffer next to the rings: give up ring stages for it, or, failing that, teams
     xb = max(getattr(p, "_xb", 0) for p in params)
-    while any(p.T > 1 for p in params) and xb + TEAM_BYTES + GEMV_WARPS * (stages * (tps * 512 + 8) + 64) > 227 * 1024:
+    while any(p.T > 1 for p in params) and xb + TEAM_BYTES + GEMV_WARPS * (stages * (tps * 512 + 8) + 64) > SMEM_LIMIT:
         if stages > 1:
             stages -= 1
         else:
