@@ -90,6 +90,9 @@ class _ModelBase:
         self._pending, self._pending_wt = [], 0
         self.chain = os.environ.get("TI_GEMV_CHAIN", "1") != "0"
         self.ll_handoff = os.environ.get("TI_LL_HANDOFF", "1") == "1"
+        # every CTA then reads the packets of all ranks (tp x 40 KB per row): worth it for two ranks (measured +2 %),
+        # more L2 traffic than the grid-wide collect + barrier it replaces for more
+        self.ll_handoff_max_tp = int(os.environ.get("TI_LL_HANDOFF_MAX_TP", "2"))
         self.gdn_split = os.environ.get("TI_GDN_SPLIT", "0") == "1"   # prefill: a head's columns over a 4-block cluster
         self.gemm_min_rows = int(os.environ.get("TI_GEMM_MIN_ROWS", "8"))    # more rows than this: tcgen05 GEMM
 
@@ -311,7 +314,7 @@ class _StepMixin:
             # the product that consumes an all-reduced row-parallel output collects the packets itself (same launch)
             prev = self._pending[-1] if self._pending else None
             xll = (self.ll_handoff and prev is not None and M <= step and self.chain and prev.epi == EPI_ROWPAR
-                   and prev.tp > 1 and prev.M == m and prev.out == x.data_ptr() and prev.N == W.K
+                   and 1 < prev.tp <= self.ll_handoff_max_tp and prev.M == m and prev.out == x.data_ptr() and prev.N == W.K
                    and x.stride(0) == W.K and xmode == XNORM and self._pending_wt == W.wt
                    and len(self._pending) < F.MAX_CHAIN)
             p = F.make_gemv_params(
