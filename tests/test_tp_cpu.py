@@ -212,3 +212,22 @@ os._exit(0)
                         "--master-addr", "127.0.0.1", "--master-port", "29537", str(path)],
                        capture_output=True, text=True, env=env, timeout=300)
     assert "PEER_LOST [1]" in r.stdout, (r.stdout[-500:], r.stderr[-1500:])
+
+
+def test_full_vocab_gather_baseline_matches_candidate_exchange():
+    """The measuring baseline (every rank gathers whole logit rows, top-k over the full vocabulary) must pick the
+    same tokens as the default path (per-rank top-k, exchange of the k candidates)."""
+    prompts = [_prompt(21, 1), _prompt(40, 2)]
+    greedy = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    sampled = SamplingParams(temperature=0.9, top_k=8, max_tokens=6, ignore_eos=True)
+
+    def rank_fn(comm):
+        a = _mk(comm, 2)
+        b = _mk(comm, 2, baseline_full_vocab_gather=True)
+        assert b.model_runner.sampler.full_vocab_gather
+        return (a.generate_token_ids(prompts, greedy), a.generate_token_ids(prompts, sampled),
+                b.generate_token_ids(prompts, greedy), b.generate_token_ids(prompts, sampled))
+    results, errors, _ = run_ranks(2, rank_fn, timeout_s=120)
+    assert errors == [None] * 2, errors
+    for g1, s1, g2, s2 in results:
+        assert g1 == g2 and s1 == s2

@@ -43,6 +43,7 @@ class Config:
     prefix_state_stride: int = 256     # DeltaNet state snapshots at stride * 2^j prompt tokens
     gdn_state_dtype: str = "fp32"      # recurrent-state pool dtype on the GPU: "fp32" | "bf16"
     fused_collectives: bool = True     # peer-memory fused TP kernels (False: NCCL baseline path)
+    baseline_full_vocab_gather: bool = False   # sampling baseline: all-gather the whole logit rows (measurement only)
     heartbeat_interval: float = 0.0    # seconds between peer heartbeats under tensor parallelism (0: watchdog off)
     heartbeat_timeout: float = 10.0    # a peer silent for this long is reported lost before the next step
     weight_cache_dir: str = None       # on-disk cache of per-rank quantised shards

@@ -69,7 +69,8 @@ class ModelRunner:
             src = make_weight_source(self.mc, cfg.weights, cfg.model, device="cpu")
             self.model = TorchHybridModel(self.mc, src, quant=cfg.quantization if cfg.quantization == "w8a16" else "none",
                                           tp=self.tp_size, rank=self.tp_rank, comm=self.comm)
-        self.sampler = Sampler(self.comm, self.model.vocab_start, cfg.eos, seed=0)
+        self.sampler = Sampler(self.comm, self.model.vocab_start, cfg.eos, seed=0,
+                               full_vocab_gather=cfg.baseline_full_vocab_gather)
         return self.model
 
     def allocate_kv_cache(self):
@@ -221,7 +222,8 @@ class ModelRunner:
         sample_rows = [i for i, s in enumerate(seqs) if s.num_cached_tokens + s.num_scheduled_tokens >= s.num_tokens]
         sample_seqs = [seqs[i] for i in sample_rows]
         fast = getattr(self.model, "forward_and_sample", None)
-        if fast is not None and sample_rows and not self.sampler.needs_full_logits(sample_seqs):
+        if (fast is not None and sample_rows and not self.sampler.needs_full_logits(sample_seqs)
+                and not self.sampler.full_vocab_gather):
             # GPU path: lm_head + per-rank top-k (+ candidate exchange) run as kernels
             k = self.sampler.num_candidates(sample_seqs)
             vals, idx = fast(batch, sample_rows, k)

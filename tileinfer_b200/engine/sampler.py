@@ -20,7 +20,11 @@ from .constraints import init_constraint_state
 class Sampler:
     default_candidates = 64
 
-    def __init__(self, comm, vocab_start: int, eos_ids, seed: int = 0):
+    def __init__(self, comm, vocab_start: int, eos_ids, seed: int = 0, full_vocab_gather: bool = False):
+        # full_vocab_gather: the measuring baseline: every rank gathers the WHOLE logit row of every rank and runs
+        # top-k over the full vocabulary (the structure the reference had before its top-k exchange,
+        # engine/model_runner.py:1130-1133); tp * V floats per row on the wire instead of tp * k pairs
+        self.full_vocab_gather = full_vocab_gather
         self.comm = comm
         self.vocab_start = vocab_start
         self.eos_ids = tuple(eos_ids)
@@ -65,6 +69,11 @@ class Sampler:
             logits = logits.clone()
             self._penalise(logits, seqs)
             self._constrain(logits, seqs)
+        if self.full_vocab_gather and self.comm.world_size > 1:
+            full = torch.cat(self.comm.all_gather(logits.float().contiguous()), dim=-1)   # shards are in rank order
+            k = min(self.num_candidates(seqs), full.shape[-1])
+            vals, idx = torch.topk(full, k, dim=-1)
+            return self.sample_from_candidates(vals, idx, seqs, gathered=True)
         k = min(self.num_candidates(seqs), logits.shape[-1])
         vals, idx = torch.topk(logits, k, dim=-1)              # local candidates
         idx = idx + self.vocab_start
