@@ -188,3 +188,25 @@ def test_sampling_is_seeded_and_respects_top_k():
     assert a != greedy or True      # usually differs; never an error
     seq_status = SequenceStatus.FINISHED
     assert seq_status.name == "FINISHED"
+
+
+def test_gemv_planner_choices():
+    """Host-side planning of the decode GEMV (pure Python): ring depth that fits beside the staged activations,
+    team size for products with few row tiles, rows per launch."""
+    from tileinfer_b200.ops import functional as F
+    # 27B layer shapes, one row: (row tiles, k tiles)
+    assert F.plan_team(4352, 80, 1) == 1          # gate_up: more units than warps -> warp-owned units
+    assert F.plan_team(2060, 80, 1) == 1          # in_proj: 0.87 units per warp is enough
+    assert F.plan_team(640, 272, 1) == 16         # down: few row tiles, long k -> the whole CTA shares a unit
+    assert F.plan_team(640, 96, 1) == 2           # out_proj: slices must stay >= 16 tiles
+    assert F.plan_team(544, 80, 1) == 4 and F.plan_team(258, 80, 1) == 4      # 1/8 tensor-parallel shards
+    assert F.plan_team(640, 272, 1, team=1) == 1
+    R, tps, stages = F.plan_gemv(F.W_INT8, F.XNORM, 1, 4352, 80)
+    assert (R, tps) == (1, 8) and stages == 3
+    assert F.plan_gemv(F.W_INT8, F.XGLOBAL, 1, 640, 272)[2] == 2              # K = 17408: x takes 37 KB
+    assert F.plan_gemv(F.W_INT8, F.XNORM, 16, 4352, 80) is None               # 16 rows of K = 5120 do not fit
+    assert F.max_rows(F.W_INT8, F.XNORM, 5120) == 12 and F.max_rows(F.W_INT8, F.XGLOBAL, 17408) == 4
+    for m in (1, 4, 12):
+        xb = F.x_smem_bytes(F.W_INT8, F.XNORM, m, 5120, 5120)
+        _, tps, st = F.plan_gemv(F.W_INT8, F.XNORM, m, 4352, 80)
+        assert xb + F.GEMV_WARPS * (st * (tps * 512 + 8) + 64) <= F.SMEM_LIMIT
