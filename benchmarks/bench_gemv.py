@@ -64,11 +64,12 @@ def bench_chain(args):
     nw = torch.zeros(H, dtype=torch.bfloat16, device="cuda")
     dbg = torch.zeros(148 * 32, dtype=torch.int64, device="cuda")
     chains = []
+    tm = [int(t) for t in args.teams.split(",")] if args.teams else [None] * 4
     for Wo, Wgu, Wd, Wi in sets:
-        ps = [F.make_gemv_params(Wo, x, h1, M, xmode=F.XGLOBAL, epi=F.EPI_ROWPAR, resid=h0, ws=ws),
-              F.make_gemv_params(Wgu, h1, act, M, xmode=F.XNORM, epi=F.EPI_SWIGLU, norm_w=nw, ws=ws),
-              F.make_gemv_params(Wd, act, h2, M, xmode=F.XGLOBAL, epi=F.EPI_ROWPAR, resid=h1, ws=ws),
-              F.make_gemv_params(Wi, h2, proj, M, xmode=F.XNORM, epi=F.EPI_STORE, norm_w=nw, ws=ws)]
+        ps = [F.make_gemv_params(Wo, x, h1, M, xmode=F.XGLOBAL, epi=F.EPI_ROWPAR, resid=h0, ws=ws, team=tm[0]),
+              F.make_gemv_params(Wgu, h1, act, M, xmode=F.XNORM, epi=F.EPI_SWIGLU, norm_w=nw, ws=ws, team=tm[1]),
+              F.make_gemv_params(Wd, act, h2, M, xmode=F.XGLOBAL, epi=F.EPI_ROWPAR, resid=h1, ws=ws, team=tm[2]),
+              F.make_gemv_params(Wi, h2, proj, M, xmode=F.XNORM, epi=F.EPI_STORE, norm_w=nw, ws=ws, team=tm[3])]
         if args.timeline:
             ps[0].dbg = dbg.data_ptr()
         chains.append(ps)
@@ -99,6 +100,7 @@ def main():
     ap.add_argument("--timeline", action="store_true")
     ap.add_argument("--chain", action="store_true")
     ap.add_argument("--tp-shapes", type=int, default=1)
+    ap.add_argument("--teams", default=None, help="team sizes of the four chained products, e.g. 2,2,16,1 (default: planner)")
     ap.add_argument("--M", type=int, default=1)
     ap.add_argument("--iters", type=int, default=40)
     args = ap.parse_args()
