@@ -181,8 +181,7 @@ TEAM_BYTES = 2 * GEMV_WARPS * 32 * 16      # exchange buffer of team mode (must 
 
 def plan_team(n_tiles: int, KB: int, R: int, team: int | None = None, ncta: int = NUM_SMS) -> int:
     """Team size T for a product: how many warps of a CTA share one unit, each streaming a slice of k.
-    A product with fewer units than warps would leave warps (and the bytes they keep in flight) idle; T is
-    then the power of two that fills the grid's teams best, units being dealt round-robin to teams.
+    A product with fewer units than warps would leave warps (and the bytes they keep in flight) idle.
     `team` (or TI_GEMV_T) forces a size."""
     if team is None and "TI_GEMV_T" in os.environ:
         team = int(os.environ["TI_GEMV_T"])
@@ -192,14 +191,15 @@ def plan_team(n_tiles: int, KB: int, R: int, team: int | None = None, ncta: int 
     W = ncta * GEMV_WARPS
     if U >= 0.8 * W:
         return 1
-    best, best_eff = 1, U / W
+    # the smallest team that puts at least half of the grid's warps to work, with slices of two ring stages or
+    # more (measured on the 27B layer: down with T = 2 / 8 / 16 -> chain of 90.9 / 91.8 / 95.9 us)
+    best = 1
     for T in (2, 4, 8, 16):
-        if T > GEMV_WARPS or KB < 16 * T:      # slices shorter than two ring stages are latency-bound
+        if T > GEMV_WARPS or KB < 16 * T:
             break
-        nt = W // T
-        eff = U / (-(-U // nt) * nt)
-        if eff > best_eff + 0.05:
-            best, best_eff = T, eff
+        best = T
+        if U * T >= 0.5 * W:
+            break
     return best
 
 
