@@ -399,6 +399,87 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __
   }
 }
 
+// The same for rows of up to 512 * 5 * 8 = 20480 elements in ONE pass: every thread keeps its (up to five) 16-byte
+// chunks of the row in registers between the statistics and the quantisation, so the row is read once.
+__global__ void __launch_bounds__(512) quant_rows_fast_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
+                                                              const __nv_bfloat16* __restrict__ norm_w, float eps, int K,
+                                                              int8_t* __restrict__ xh, uint8_t* __restrict__ xl,
+                                                              float* __restrict__ xscale) {
+  __shared__ float red[16], red2[16];
+  const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const __nv_bfloat16* row = x + (size_t)m * ldx;
+  const int nchunk = K >> 3;
+  float v[5][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 5; ++j) {
+    const int c = tid + j * 512;
+    uint4 q = make_uint4(0, 0, 0, 0);
+    if (c < nchunk) q = *reinterpret_cast<const uint4*>(row + (size_t)c * 8);
+    const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[j][2 * i] = bf16lo(w4[i]);
+      v[j][2 * i + 1] = bf16hi(w4[i]);
+      ss += v[j][2 * i] * v[j][2 * i] + v[j][2 * i + 1] * v[j][2 * i + 1];
+    }
+  }
+  if (norm_w != nullptr) {
+    uint4 nwv[5];
+#pragma unroll
+    for (int j = 0; j < 5; ++j) {
+      const int c = tid + j * 512;
+      nwv[j] = c < nchunk ? *reinterpret_cast<const uint4*>(norm_w + (size_t)c * 8) : make_uint4(0, 0, 0, 0);
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < 16; ++w) tot += red[w];
+    const float rr = rsqrtf(tot / (float)K + eps);
+#pragma unroll
+    for (int j = 0; j < 5; ++j) {
+      const uint32_t n4[4] = {nwv[j].x, nwv[j].y, nwv[j].z, nwv[j].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[j][2 * i] = round_bf16(v[j][2 * i] * rr * (1.f + bf16lo(n4[i])));
+        v[j][2 * i + 1] = round_bf16(v[j][2 * i + 1] * rr * (1.f + bf16hi(n4[i])));
+      }
+    }
+  }
+  float mx = 0.f;
+#pragma unroll
+  for (int j = 0; j < 5; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[j][i]));
+  mx = warp_max(mx);
+  if (lane == 0) red2[warp] = mx;
+  __syncthreads();
+  float a = 0.f;
+#pragma unroll
+  for (int w = 0; w < 16; ++w) a = fmaxf(a, red2[w]);
+  int e = (int)((__float_as_uint(a) >> 23) & 0xffu) - 127;
+  e = max(e, -100);
+  if (!(a < 3.0e38f)) e = 127;
+  const float qs = exp2f((float)(14 - e));
+  if (tid == 0) xscale[m] = exp2f((float)(e - 14));
+#pragma unroll
+  for (int j = 0; j < 5; ++j) {
+    const int c = tid + j * 512;
+    if (c >= nchunk) continue;
+    uint32_t hw[2] = {0, 0}, lw[2] = {0, 0};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int q = max(-32768, min(32767, __float2int_rn(v[j][i] * qs)));
+      hw[i >> 2] |= (uint32_t)((q >> 8) & 0xff) << (8 * (i & 3));
+      lw[i >> 2] |= (uint32_t)(q & 0xff) << (8 * (i & 3));
+    }
+    *reinterpret_cast<uint2*>(xh + (size_t)m * K + (size_t)c * 8) = make_uint2(hw[0], hw[1]);
+    *reinterpret_cast<uint2*>(xl + (size_t)m * K + (size_t)c * 8) = make_uint2(lw[0], lw[1]);
+  }
+}
+
 // The driver entry point is resolved at run time, so the library also loads on machines without a driver.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -497,8 +578,14 @@ extern "C" {
 int ti_quant_rows(const void* x, int ldx, const void* norm_w, float eps, int M, int K, void* xh, void* xl, void* xscale,
                   void* stream) {
   if (M <= 0) return 0;
-  ti::quant_rows_kernel<<<M, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)norm_w,
-                                                             eps, K, (int8_t*)xh, (uint8_t*)xl, (float*)xscale);
+  const bool aligned = (K % 8 == 0) && (ldx % 8 == 0) && (((uintptr_t)x | (uintptr_t)xh | (uintptr_t)xl) % 16 == 0) &&
+                       (norm_w == nullptr || (uintptr_t)norm_w % 16 == 0);
+  if (aligned && K <= 512 * 5 * 8)
+    ti::quant_rows_fast_kernel<<<M, 512, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)norm_w,
+                                                                    eps, K, (int8_t*)xh, (uint8_t*)xl, (float*)xscale);
+  else
+    ti::quant_rows_kernel<<<M, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)norm_w,
+                                                               eps, K, (int8_t*)xh, (uint8_t*)xl, (float*)xscale);
   return (int)cudaGetLastError();
 }
 
