@@ -588,3 +588,73 @@ def test_gdn_decode_many_sequences_staged(state_bf16):
     assert torch.equal(c1, c2)
     untouched = [i for i in range(S + 3) if i not in set(slots.tolist())]
     assert torch.equal(s1[untouched], state0[untouched])
+
+
+@pytest.mark.parametrize("D,hq,hkv", [(256, 6, 1), (128, 4, 2), (64, 2, 1), (256, 3, 1)])
+def test_attn_prefill_tcgen05(D, hq, hkv):
+    """Prefill attention on tcgen05 against fp32 softmax attention: a 4096-token prompt from scratch, a 300-token
+    chunk that continues an 8192-token cached prefix, and a short prompt (partial query tile); scattered pages."""
+    F = _F()
+    torch.manual_seed(3)
+    G = hq // hkv
+    ctx0, lens = [0, 8192, 0], [4096, 300, 70]
+    S, T = 3, sum(lens)
+    need = [(c + n + 15) // 16 for c, n in zip(ctx0, lens)]
+    nb = sum(need) + 7
+    perm = torch.randperm(nb).tolist()
+    tables, o = [], 0
+    for n in need:
+        tables.append(perm[o:o + n]); o += n
+    maxb = max(need)
+    bt = torch.zeros(S, maxb, dtype=torch.int32)
+    for s in range(S):
+        bt[s, :need[s]] = torch.tensor(tables[s], dtype=torch.int32)
+    bt = bt.cuda()
+    kcache = torch.zeros(nb, hkv, 16, D, dtype=BF16, device="cuda")
+    vcache = torch.zeros(nb, hkv, D, 16, dtype=BF16, device="cuda")
+    Ks, Vs = [], []
+    for s in range(S):
+        L = ctx0[s] + lens[s]
+        K = torch.randn(L, hkv, D, device="cuda").to(BF16)
+        V = torch.randn(L, hkv, D, device="cuda").to(BF16)
+        Ks.append(K); Vs.append(V)
+        Lp = need[s] * 16
+        Kp = torch.zeros(Lp, hkv, D, dtype=BF16, device="cuda"); Kp[:L] = K
+        Vp = torch.zeros(Lp, hkv, D, dtype=BF16, device="cuda"); Vp[:L] = V
+        idx = torch.tensor(tables[s], device="cuda")
+        kcache[idx] = Kp.view(need[s], 16, hkv, D).permute(0, 2, 1, 3)
+        vcache[idx] = Vp.view(need[s], 16, hkv, D).permute(0, 2, 3, 1)
+    q = (3.0 * torch.randn(T, hq, D, device="cuda")).to(BF16)        # peaky softmax: outputs of order 1
+    ld = hq * 2 * D
+    proj = torch.randn(T, ld, device="cuda").to(BF16)
+    positions = torch.tensor(sum([list(range(c, c + n)) for c, n in zip(ctx0, lens)], []), dtype=torch.int32, device="cuda")
+    tiles, t = [], 0
+    for s, n in enumerate(lens):
+        for a in range(t, t + n, 128):
+            tiles.append((ctx0[s] + (a - t) + min(128, t + n - a), s, a, min(128, t + n - a)))
+        t += n
+    tiles.sort(reverse=True)
+    tiles.append((0, 0, 0, 0))                         # a padding tile is skipped
+    tl = torch.tensor([[x[1] for x in tiles], [x[2] for x in tiles], [x[3] for x in tiles]], dtype=torch.int32, device="cuda")
+    out = torch.zeros(T, hq * D, dtype=BF16, device="cuda")
+    st = torch.zeros(4, dtype=torch.int32, device="cuda")
+    F._STATUS = st
+    F.attn_prefill(q, kcache, vcache, nb, bt, positions, tl, proj, out, hq=hq, hkv=hkv, D=D, max_blocks=maxb, ld=ld)
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0, "a bounded wait inside the kernel ran out"
+    t = 0
+    for s, n in enumerate(lens):
+        pos = positions[t:t + n].long()
+        K, V = Ks[s].float(), Vs[s].float()
+        qq = q[t:t + n].float().reshape(n, hkv, G, D)
+        gate = proj[t:t + n].float().reshape(n, hq, 2 * D)[..., D:].reshape(n, hq * D)
+        ref = torch.empty(n, hq * D, device="cuda")
+        for a in range(0, n, 512):
+            b = min(n, a + 512)
+            sc = torch.einsum("tkgd,lkd->tkgl", qq[a:b], K) * D ** -0.5
+            mask = torch.arange(K.shape[0], device="cuda")[None] > pos[a:b, None]
+            pr = torch.softmax(sc.masked_fill(mask[:, None, None], float("-inf")), -1)
+            ref[a:b] = torch.einsum("tkgl,lkd->tkgd", pr, V).reshape(b - a, hq * D) * torch.sigmoid(gate[a:b])
+        assert ref.abs().mean() > 0.05
+        torch.testing.assert_close(out[t:t + n].float(), ref, rtol=2e-2, atol=1.5e-2)
+        t += n

@@ -210,3 +210,32 @@ def test_gemv_planner_choices():
         xb = F.x_smem_bytes(F.W_INT8, F.XNORM, m, 5120, 5120)
         _, tps, st = F.plan_gemv(F.W_INT8, F.XNORM, m, 4352, 80)
         assert xb + F.GEMV_WARPS * (st * (tps * 512 + 8) + 64) <= F.SMEM_LIMIT
+
+
+def test_prefix_hit_under_memory_pressure_does_not_crash():
+    """6 KV blocks: 4 hold a cached prefix (cache-only references), 2 belong to a running sequence.  A new request
+    that matches the cached prefix needs one more block than exist once the prefix blocks are pinned by the hit:
+    the request must stay in the waiting queue (or fall back to eviction), never raise from the allocator."""
+    from tileinfer_b200.engine.config import Config
+    from tileinfer_b200.engine.scheduler import Scheduler
+    cfg = Config("preset:tiny-hybrid", device="cpu", num_kvcache_blocks=6, max_num_seqs=4, max_model_len=512)
+    Sequence.block_size = 16
+    sch = Scheduler(cfg)
+    bm, pc = sch.block_manager, sch.prefix_cache
+    shared = _prompt(64, 90)
+    blocks = [bm._take() for _ in range(4)]
+    chain = pc.insert(shared, blocks, 4)
+    pc.mark_state(chain[-1].node_id)
+    for b in blocks:
+        bm.decref(b)                                   # the producer is gone: cache-only references
+    running = Sequence(_prompt(30, 91))
+    bm.allocate(running)                               # the two remaining free blocks
+    assert bm.num_free_blocks == 0 and pc.num_evictable() == 4
+    new = Sequence(shared + _prompt(40, 92))           # 104 tokens = 7 blocks: 4 shared + 3 more, none free
+    ok = sch._allocate_blocks_for_new_seq(new)         # used to raise RuntimeError('out of KV blocks')
+    assert ok is False and new.block_table == []
+    assert all(bm.ref_count[b] == 1 for b in blocks)   # references given back, cache entries intact
+    assert pc.num_evictable() == 4
+    # a request that fits after evicting part of the cached prefix still gets blocks
+    small = Sequence(shared[:32] + _prompt(8, 93))     # 40 tokens = 3 blocks
+    assert sch._allocate_blocks_for_new_seq(small) and len(small.block_table) == 3

@@ -183,13 +183,17 @@ class Scheduler:
         bm = self.block_manager
         if self.enable_prefix_caching and seq.num_completion_tokens == 0:
             chain, n = self.prefix_cache.find_longest_prefix(seq.token_ids, seq.num_tokens - 1)
-            if chain and bm.can_allocate(seq, num_shared=len(chain)):
-                if self.on_prefix_hit is None or self.on_prefix_hit(seq, chain[-1].node_id, n):
-                    bm.share_blocks(seq, [c.block_id for c in chain])
+            if chain:
+                # Take the chain's references BEFORE the capacity check: once shared, these blocks are no longer
+                # evictable, so they must not be counted among the blocks the remainder of the prompt may take.
+                bm.share_blocks(seq, [c.block_id for c in chain])
+                if bm.can_append(seq) and (self.on_prefix_hit is None
+                                           or self.on_prefix_hit(seq, chain[-1].node_id, n)):
                     bm.allocate_extra(seq)
                     seq.num_cached_tokens = n
                     seq.prefix_restore_key = chain[-1].node_id
                     return True
+                bm.deallocate(seq)          # give the references back; the cache still holds its own
         if bm.can_allocate(seq):
             bm.allocate(seq)
             return True

@@ -63,6 +63,7 @@ _l.register("ti_qkv_prep_params_size", _I, [])
 _l.register("ti_attn_params_size", _I, [])
 _l.register("ti_qkv_prep", _I, [ctypes.POINTER(QkvPrepParams), _I, _I, _P])
 _l.register("ti_attn_paged", _I, [ctypes.POINTER(AttnParams), _I, _P])
+_l.register("ti_attn_prefill", _I, [_P, _I, _P, _P, _I, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P])
 _l.register("ti_topk_params_size", _I, [])
 _l.register("ti_topk", _I, [ctypes.POINTER(TopkParams), _P])
 _l.register("ti_symm_alloc", _I, [ctypes.POINTER(_P), ctypes.c_size_t])
@@ -372,6 +373,17 @@ def qkv_prep(p: QkvPrepParams, T: int, D: int):
 
 def attn_paged(p: AttnParams, D: int):
     check(L().ti_attn_paged(ctypes.byref(p), D, stream()), "ti_attn_paged")
+
+
+def attn_prefill(q, kcache, vcache, num_blocks, block_tables, positions, tiles, gate_src, out, *, hq, hkv, D,
+                 max_blocks, ld):
+    """Causal GQA attention of prefill query tiles on the tcgen05 tensor cores (ops/csrc/attn_prefill.cu).
+    `tiles`: int32 [3, n] = (sequence, first flat token, tokens <= 128) per tile, longest KV first."""
+    n = tiles.shape[1]
+    scale = D ** -0.5 * 1.4426950408889634
+    check(L().ti_attn_prefill(ptr(q), q.shape[0], ptr(kcache), ptr(vcache), num_blocks, ptr(block_tables), ptr(positions),
+                              ptr(tiles[0]), ptr(tiles[1]), ptr(tiles[2]), n, ptr(gate_src), ptr(out), hq, hkv,
+                              max_blocks, ld, scale, D, status_ptr(), stream()), "ti_attn_prefill")
 
 
 def topk(p: TopkParams):
