@@ -658,3 +658,80 @@ def test_attn_prefill_tcgen05(D, hq, hkv):
         assert ref.abs().mean() > 0.05
         torch.testing.assert_close(out[t:t + n].float(), ref, rtol=2e-2, atol=1.5e-2)
         t += n
+
+
+def test_logits_edit_kernel():
+    """Repetition penalty on listed ids followed by the additive row (bias / -inf mask), rows without a slot untouched."""
+    F = _F()
+    torch.manual_seed(5)
+    M, V, R, PC = 5, 20000, 8, 512
+    logits = torch.randn(M, V, device="cuda")
+    ref = logits.clone()
+    slot = torch.tensor([-1, 2, 0, -1, 5], dtype=torch.int32, device="cuda")
+    add = torch.zeros(R, V, device="cuda")
+    add[2, ::3] = float("-inf"); add[2, 7] = 4.0
+    add[5] = torch.randn(V, device="cuda")
+    add_valid = torch.tensor([0, 0, 1, 0, 0, 1, 0, 0], dtype=torch.int32, device="cuda")
+    pen_ids = torch.zeros(R, PC, dtype=torch.int32, device="cuda")
+    pen_cnt = torch.zeros(R, dtype=torch.int32, device="cuda")
+    pen_rp = torch.ones(R, device="cuda")
+    ids0 = torch.sort(torch.randperm(V)[:300]).values.int().cuda()
+    ids5 = torch.sort(torch.randperm(V)[:PC]).values.int().cuda()
+    pen_ids[0, :300] = ids0; pen_cnt[0] = 300; pen_rp[0] = 1.3
+    pen_ids[5] = ids5; pen_cnt[5] = PC; pen_rp[5] = 2.0
+    p = F.EditParams()
+    p.logits, p.row_slot, p.add_rows, p.add_valid = logits.data_ptr(), slot.data_ptr(), add.data_ptr(), add_valid.data_ptr()
+    p.pen_ids, p.pen_cnt, p.pen_rp = pen_ids.data_ptr(), pen_cnt.data_ptr(), pen_rp.data_ptr()
+    p.M, p.V, p.ld, p.pen_cap, p.chunk = M, V, V, PC, 8192
+    F.logits_edit(p)
+    torch.cuda.synchronize()
+    v = ref[2, ids0.long()]; ref[2, ids0.long()] = torch.where(v > 0, v / 1.3, v * 1.3)       # row 2 -> slot 0: penalty only
+    ref[1] += add[2]                                                                          # row 1 -> slot 2: add only
+    v = ref[4, ids5.long()]; ref[4, ids5.long()] = torch.where(v > 0, v / 2.0, v * 2.0)       # row 4 -> slot 5: both
+    ref[4] += add[5]
+    assert torch.equal(torch.isinf(logits), torch.isinf(ref))
+    torch.testing.assert_close(torch.nan_to_num(logits, neginf=-1e9), torch.nan_to_num(ref, neginf=-1e9), rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("n_cand", [1, 4, 64, 512])
+def test_sample_kernel_matches_host_sampler(n_cand):
+    """The device draw picks the token the host sampler picks for the same candidates and the same uniform numbers
+    (greedy rows, temperature, top-k, top-p; candidate lists with empty entries and ties)."""
+    from tileinfer_b200.engine.sampler import Sampler
+    from tileinfer_b200.parallel.comm import SingleComm
+    F = _F()
+    torch.manual_seed(7)
+    M = 24
+
+    class S:
+        pass
+    seqs = []
+    for i in range(M):
+        s = S()
+        s.temperature = [0.0, 0.7, 1.0, 1.5][i % 4]
+        s.top_k = [-1, 1, 5, 50][(i // 4) % 4]
+        s.top_p = [1.0, 0.9, 0.5][i % 3]
+        s.repetition_penalty, s.constraint, s.token_ids = 1.0, None, [1]
+        seqs.append(s)
+    vals = torch.randn(M, n_cand) * 3
+    idx = torch.stack([torch.randperm(100000)[:n_cand] for _ in range(M)]).int()
+    if n_cand >= 4:
+        vals[:, -1] = float("-inf"); idx[:, -1] = -1                  # an empty entry
+        vals[:, 1] = vals[:, 0]                                        # a tie: the smaller id wins
+    host, dev = Sampler(SingleComm(), 0, (), seed=3), Sampler(SingleComm(), 0, (), seed=3)
+    want = host.sample_from_candidates(vals.clone(), idx.clone().long(), seqs, gathered=True)
+    spec = dev.device_spec(seqs, [])
+    dv, di = vals.cuda(), idx.cuda()
+    fpar = torch.tensor([spec["temperature"], spec["top_p"], spec["u"]], dtype=torch.float32, device="cuda")
+    topk = torch.tensor(spec["top_k"], dtype=torch.int32, device="cuda")
+    out = torch.full((M + 1,), -7, dtype=torch.int32, device="cuda")
+    status = torch.tensor([9], dtype=torch.int32, device="cuda")
+    p = F.SampleParams()
+    p.cand_val, p.cand_idx, p.temperature, p.top_p, p.u, p.top_k = dv.data_ptr(), di.data_ptr(), fpar[0].data_ptr(), fpar[1].data_ptr(), fpar[2].data_ptr(), topk.data_ptr()
+    p.out_tok, p.status_src, p.M, p.n_cand = out.data_ptr(), status.data_ptr(), M, n_cand
+    F.sample(p)
+    got = out.cpu().tolist()
+    assert got[M] == 9                                                 # the status word rides along
+    # the draw is a float computation: allow the rare row where the uniform number lands within 1e-5 of a CDF step
+    diff = [i for i in range(M) if got[i] != want[i]]
+    assert len(diff) <= 1, (diff, got, want)

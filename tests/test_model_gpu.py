@@ -115,3 +115,35 @@ def test_weight_shard_cache_round_trip(tmp_path):
     finally:
         B200HybridModel._build_shards = keep
     assert a == b
+
+
+def test_edited_requests_stay_on_the_device_path_and_match_the_host_sampler():
+    """Repetition penalty, logit bias, allow-list and a regex grammar: the device path (logit-edit kernel + top-k +
+    sample kernel inside the CUDA graph) must produce the tokens of the host path (full logits to the CPU)."""
+    from tileinfer_b200.engine.llm import LLM
+    from tileinfer_b200.engine.sampling_params import SamplingParams
+    llm = LLM("preset:tiny-hybrid", quantization="w8a16", num_kvcache_blocks=128, max_num_seqs=8, max_model_len=512)
+    model = llm.model_runner.model
+    prompts = [_prompt(20, 31), _prompt(33, 32), _prompt(9, 33)]
+    params = [SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True, repetition_penalty=1.5),
+              SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True, logit_bias={65: 2.0, 66: 1.5},
+                             bad_token_ids=[67]),
+              SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, guided_regex="[a-c]+")]
+    steps0 = model.host_steps
+    dev = llm.generate_token_ids(prompts, params)
+    assert model.host_steps > steps0
+    keep = model.EDIT_SLOTS
+    model.EDIT_SLOTS = -1                      # no row qualifies: everything takes the host path
+    try:
+        host = llm.generate_token_ids(prompts, params)
+    finally:
+        model.EDIT_SLOTS = keep
+    assert dev == host
+    text = "".join(chr(t) for t in dev[2])
+    assert text and set(text) <= set("abc")
+    # sampled requests draw the same tokens on both paths (same seeded uniform numbers, same candidates)
+    sp = SamplingParams(temperature=0.9, top_k=40, top_p=0.95, max_tokens=12, ignore_eos=True)
+    a = LLM("preset:tiny-hybrid", quantization="w8a16", num_kvcache_blocks=128, max_num_seqs=8, max_model_len=512)
+    b = LLM("preset:tiny-hybrid", quantization="w8a16", num_kvcache_blocks=128, max_num_seqs=8, max_model_len=512)
+    b.model_runner.model.EDIT_SLOTS = -1
+    assert a.generate_token_ids([prompts[0]], sp) == b.generate_token_ids([prompts[0]], sp)

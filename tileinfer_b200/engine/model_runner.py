@@ -71,6 +71,7 @@ class ModelRunner:
                                           tp=self.tp_size, rank=self.tp_rank, comm=self.comm)
         self.sampler = Sampler(self.comm, self.model.vocab_start, cfg.eos, seed=0,
                                full_vocab_gather=cfg.baseline_full_vocab_gather)
+        self.sampler._v_local = getattr(self.model, "v_local", self.mc.vocab_size // self.tp_size)
         return self.model
 
     def allocate_kv_cache(self):
@@ -222,14 +223,18 @@ class ModelRunner:
         sample_rows = [i for i, s in enumerate(seqs) if s.num_cached_tokens + s.num_scheduled_tokens >= s.num_tokens]
         sample_seqs = [seqs[i] for i in sample_rows]
         fast = getattr(self.model, "forward_and_sample", None)
-        if (fast is not None and sample_rows and not self.sampler.needs_full_logits(sample_seqs)
-                and not self.sampler.full_vocab_gather):
-            # GPU path: lm_head + per-rank top-k (+ candidate exchange) run as kernels
-            k = self.sampler.num_candidates(sample_seqs)
-            vals, idx = fast(batch, sample_rows, k)
+        k = self.sampler.num_candidates(sample_seqs) if sample_rows else 1
+        edits = self.sampler.edit_rows(sample_seqs) if sample_rows else []
+        if (fast is not None and sample_rows and not self.sampler.full_vocab_gather
+                and k <= self.sampler.max_device_candidates and len(edits) <= self.model.EDIT_SLOTS):
+            # GPU path: lm_head, logit edits, per-rank top-k (+ candidate exchange) and the draw itself run as
+            # kernels; what comes back is the chosen token id per row and the peer status word
+            spec = self.sampler.device_spec(sample_seqs, edits)
+            toks = fast(batch, sample_rows, k, spec)
             self._collect_snapshots(seqs)
-            toks = self.sampler.sample_from_candidates(vals, idx, sample_seqs, gathered=True)
         else:
+            # host path: more than 64 candidates or more edited rows than the device buffers hold, the
+            # full-vocabulary-gather baseline, and the CPU executor
             hidden = self.model.forward(batch)
             self._collect_snapshots(seqs)
             toks = []

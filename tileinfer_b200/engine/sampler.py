@@ -30,6 +30,7 @@ class Sampler:
         self.eos_ids = tuple(eos_ids)
         self.gen = torch.Generator(device="cpu")
         self.gen.manual_seed(seed)
+        self._v_local = 0               # size of this rank's vocabulary shard (set by the runner)
 
     # ---- logits editing ---------------------------------------------------
     def _penalise(self, logits: torch.Tensor, seqs):
@@ -51,6 +52,43 @@ class Sampler:
                 continue
             init_constraint_state(seq)
             seq.constraint.apply(logits[i], seq.constraint_state, self.vocab_start, self.eos_ids)
+
+    max_device_candidates = 64      # the top-k kernels keep at most 64 candidates per rank
+
+    def edit_rows(self, seqs) -> list:
+        """Indices of the sequences whose logits are edited before the top-k (penalty, bias, masks, grammar)."""
+        return [i for i, s in enumerate(seqs) if s.repetition_penalty != 1.0 or s.constraint is not None]
+
+    def device_spec(self, seqs, edit_rows) -> dict:
+        """Everything the device sampler needs for one step, built on the host: per-row temperature / top-k /
+        top-p, one uniform number per sampling row drawn from the generator every rank seeds alike (drawn in
+        row order, only for rows that sample, exactly as `sample_from_candidates` does), and for edited rows
+        the additive logit row (what the constraint does to a row of zeros: 0, a bias, or -inf) and the
+        sorted rank-local ids that get the repetition penalty."""
+        n = len(seqs)
+        rows = [i for i, s in enumerate(seqs) if s.temperature > 0 and s.top_k != 1]
+        u = [0.0] * n
+        if rows:
+            draw = torch.rand(len(rows), 1, generator=self.gen)
+            for j, i in enumerate(rows):
+                u[i] = float(draw[j, 0])
+        edits = []
+        for i in edit_rows:
+            seq = seqs[i]
+            add = pen = None
+            if seq.constraint is not None:
+                init_constraint_state(seq)
+                add = torch.zeros(self.v_local(seq), dtype=torch.float32)
+                seq.constraint.apply(add, seq.constraint_state, self.vocab_start, self.eos_ids)
+            if seq.repetition_penalty != 1.0:
+                ids = torch.tensor(sorted(set(seq.token_ids)), dtype=torch.int32) - self.vocab_start
+                pen = ids[(ids >= 0) & (ids < self.v_local(seq))]
+            edits.append((i, add, pen, seq.repetition_penalty))
+        return {"temperature": [s.temperature for s in seqs], "top_k": [s.top_k for s in seqs],
+                "top_p": [s.top_p for s in seqs], "u": u, "edits": edits}
+
+    def v_local(self, seq=None) -> int:
+        return self._v_local
 
     def needs_full_logits(self, seqs) -> bool:
         return any(s.repetition_penalty != 1.0 or s.constraint is not None for s in seqs)

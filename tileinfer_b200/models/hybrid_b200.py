@@ -22,8 +22,8 @@ import os
 import torch
 
 from ..ops import functional as F
-from ..ops.functional import (EPI_F32, EPI_ROWPAR, EPI_STORE, EPI_SWIGLU, XGLOBAL, XNORM, AttnParams, GdnParams,
-                              GemvWorkspace, LinearW, QkvPrepParams, TopkParams, ptr)
+from ..ops.functional import (EPI_F32, EPI_ROWPAR, EPI_STORE, EPI_SWIGLU, XGLOBAL, XNORM, AttnParams, EditParams,
+                              GdnParams, GemvWorkspace, LinearW, QkvPrepParams, SampleParams, TopkParams, ptr)
 from .config import ModelConfig
 from .weights import ShardSpec, shard_layer
 
@@ -584,12 +584,18 @@ class _RunMixin:
         g.logits = torch.zeros(B, self.v_local, dtype=torch.float32, device=dev)
         g.topk = self._make_topk(g.logits, B, k)
         g.k = k
+        g.samp = self._make_sampler_state(g.logits, B, g.topk)
+        fused_sample = self.tp == 1 or self.peer is not None
 
         def body():
             cur = self._run_layers(x)
             self._lm_head(cur, g.logits, B)
+            F.logits_edit(g.samp.edit)                 # rows without an edit slot leave at once
             F.topk(g.topk.params)
-            self._launches += 2
+            self._launches += 3
+            if fused_sample:
+                F.sample(g.samp.sample)
+                self._launches += 1
 
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -619,7 +625,90 @@ class _RunMixin:
         self.graphs[key] = g
         return g
 
-    def _decode_graph_step(self, batch, k: int):
+    # ------------------------------------------------------------------ sampling on the device
+    EDIT_SLOTS = 8          # rows of a step that may carry logit edits (penalty, bias, masks, grammar)
+    PEN_CAP = 8192          # penalised token ids per row
+
+    def _edit_buffers(self):
+        """Device buffers of the logit-edit kernel, shared by all graphs and eager steps (stable addresses)."""
+        e = getattr(self, "_edit", None)
+        if e is None:
+            dev, R = self.dev, self.EDIT_SLOTS
+            e = self._edit = _Ctx()
+            e.add_rows = torch.zeros(R, self.v_local, dtype=torch.float32, device=dev)
+            e.meta = torch.zeros(3, R, dtype=torch.int32, device=dev)          # add_valid | pen_cnt | pen_rp (float bits)
+            e.pen_ids = torch.zeros(R, self.PEN_CAP, dtype=torch.int32, device=dev)
+            e.h_meta = torch.zeros(3, R, dtype=torch.int32).pin_memory()
+            e.h_pen = torch.zeros(R, self.PEN_CAP, dtype=torch.int32).pin_memory()
+            e.h_add = torch.zeros(R, self.v_local, dtype=torch.float32).pin_memory()
+        return e
+
+    def _make_sampler_state(self, logits, n, topk_state):
+        """Parameter blocks of the edit and sample kernels for `n` rows whose candidates `topk_state` produces."""
+        dev, e = self.dev, self._edit_buffers()
+        t = _Ctx()
+        t.fpar = torch.zeros(3, n, dtype=torch.float32, device=dev)            # temperature | top_p | u
+        t.ipar = torch.full((2, n), -1, dtype=torch.int32, device=dev)         # top_k | edit slot
+        t.h_fpar = torch.zeros(3, n, dtype=torch.float32).pin_memory()
+        t.h_ipar = torch.full((2, n), -1, dtype=torch.int32).pin_memory()
+        t.tok = torch.zeros(n + 1, dtype=torch.int32, device=dev)
+        t.h_tok = torch.zeros(n + 1, dtype=torch.int32).pin_memory()
+        ep = EditParams()
+        ep.logits, ep.row_slot, ep.add_rows = ptr(logits), ptr(t.ipar[1]), ptr(e.add_rows)
+        ep.add_valid, ep.pen_cnt, ep.pen_rp, ep.pen_ids = ptr(e.meta[0]), ptr(e.meta[1]), ptr(e.meta[2]), ptr(e.pen_ids)
+        ep.M, ep.V, ep.ld, ep.pen_cap, ep.chunk = n, self.v_local, logits.stride(0), self.PEN_CAP, 8192
+        t.edit = ep
+        sp = SampleParams()
+        sp.cand_val, sp.cand_idx = ptr(topk_state.out_val), ptr(topk_state.out_idx)
+        sp.temperature, sp.top_p, sp.u, sp.top_k = ptr(t.fpar[0]), ptr(t.fpar[1]), ptr(t.fpar[2]), ptr(t.ipar[0])
+        sp.out_tok, sp.status_src = ptr(t.tok), self.ctrl.data_ptr() + 4
+        sp.M, sp.n_cand = n, topk_state.out_val.shape[1]
+        t.sample = sp
+        return t
+
+    def _upload_sampling(self, t, n, spec):
+        """Host -> device copies of a step's sampling parameters and logit edits (pinned staging, asynchronous)."""
+        hf, hi = t.h_fpar, t.h_ipar
+        hf[0].zero_()                                   # padding rows: greedy
+        hi[1].fill_(-1)
+        hf[0, :n] = torch.tensor(spec["temperature"], dtype=torch.float32)
+        hf[1, :n] = torch.tensor(spec["top_p"], dtype=torch.float32)
+        hf[2, :n] = torch.tensor(spec["u"], dtype=torch.float32)
+        hi[0, :n] = torch.tensor(spec["top_k"], dtype=torch.int32)
+        edits = spec.get("edits") or []
+        if edits:
+            e = self._edit_buffers()
+            assert len(edits) <= self.EDIT_SLOTS
+            for slot, (row, add, pen, rp) in enumerate(edits):
+                hi[1, row] = slot
+                e.h_meta[0, slot] = 0 if add is None else 1
+                if add is not None:
+                    e.h_add[slot].copy_(add)
+                    e.add_rows[slot].copy_(e.h_add[slot], non_blocking=True)
+                cnt = 0 if pen is None else min(len(pen), self.PEN_CAP)
+                e.h_meta[1, slot] = cnt
+                e.h_meta[2, slot] = torch.tensor([float(rp)], dtype=torch.float32).view(torch.int32)[0]
+                if cnt:
+                    e.h_pen[slot, :cnt] = pen[:cnt]
+                    e.pen_ids[slot, :cnt].copy_(e.h_pen[slot, :cnt], non_blocking=True)
+            e.meta.copy_(e.h_meta, non_blocking=True)
+        t.fpar.copy_(hf, non_blocking=True)
+        t.ipar.copy_(hi, non_blocking=True)
+
+    def _read_tokens(self, t, n) -> list:
+        """The step's only device -> host copy: n token ids and the communicator's status word."""
+        t.h_tok.copy_(t.tok, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        status = int(t.h_tok[t.tok.shape[0] - 1])
+        if status != 0 and self.peer is not None:
+            from ..parallel.watchdog import PeerLostError
+            err = PeerLostError([])
+            err.args = (f"a bounded wait on a tensor-parallel peer ran out (device status word {status:#x}): "
+                        "the tokens of this step are discarded",)
+            raise err
+        return t.h_tok[:n].tolist()
+
+    def _decode_graph_step(self, batch, k: int, spec=None):
         n = batch.num_seqs
         B = next(b for b in self.buckets if b >= n)
         g = self._get_graph(B, k)
@@ -644,30 +733,59 @@ class _RunMixin:
         x.slots.copy_(h["slots"], non_blocking=True)
         x.block_tables.copy_(bt, non_blocking=True)
         x.qg.copy_(qg, non_blocking=True)
+        if spec is not None:
+            self._upload_sampling(g.samp, n, spec)
         if self.peer is not None:
             self.peer.tick()
         g.graph.replay()
         self.host_steps += 1
         return g.topk.out_val[:n], g.topk.out_idx[:n]
 
+    def _default_spec(self, n):
+        return {"temperature": [0.0] * n, "top_k": [1] * n, "top_p": [1.0] * n, "u": [0.0] * n, "edits": []}
+
     @torch.no_grad()
-    def forward_and_sample(self, batch, sample_rows, k: int):
-        """Runs the step and returns the top-k candidates (values, global token ids) of the rows that
-        sample, already gathered over the tensor-parallel group: ([n, tp*k], [n, tp*k])."""
+    def forward_and_sample(self, batch, sample_rows, k: int, spec=None):
+        """Runs the step and samples on the device.  Returns one token id per sampling row (a list of ints; the
+        same on every tensor-parallel rank).  `spec`: per-row temperature / top_k / top_p / u lists and `edits`,
+        a list of (row, additive logit row or None, sorted penalised local ids or None, penalty).  The step's only
+        device -> host copy is the token ids plus the peer status word; a non-zero status raises PeerLostError."""
+        assert k <= 64, "more than 64 candidates: use forward() + logits() + the host sampler"
         k = 1 if k <= 1 else 64
-        decode_only = batch.cu_seqlens[-1] == batch.num_seqs and len(sample_rows) == batch.num_seqs
+        n = len(sample_rows)
+        if spec is None:
+            spec = self._default_spec(n)
+        fused = self.tp == 1 or self.peer is not None        # candidates of all ranks are on this device after top-k
+        decode_only = batch.cu_seqlens[-1] == batch.num_seqs and n == batch.num_seqs
         if decode_only and self.graphs and batch.num_seqs <= self.buckets[-1] \
                 and max(len(b) for b in batch.block_tables) <= self.graph_max_blocks:
-            vals, idx = self._decode_graph_step(batch, k)
+            vals, idx = self._decode_graph_step(batch, k, spec)
+            if fused:
+                g = self.graphs[(next(b for b in self.buckets if b >= n), k)]
+                return self._read_tokens(g.samp, n)
         else:
             hidden = self.forward(batch)
             rows = torch.tensor(sample_rows, dtype=torch.long, device=self.dev)
             lg = self.logits(hidden[rows])
-            vals, idx = self._topk_rows(lg, len(sample_rows), k)
-        if self.peer is None and self.tp > 1:
+            if spec.get("edits"):
+                t0 = _Ctx()
+                t0.out_val = t0.out_idx = torch.empty(n, 1, device=self.dev)
+                st = self._make_sampler_state(lg, n, t0)
+                self._upload_sampling(st, n, spec)
+                F.logits_edit(st.edit)
+                self._launches += 1
+            vals, idx = self._topk_rows(lg, n, k)
+        if not fused:
             vals = torch.cat(self.comm.all_gather(vals.contiguous()), dim=-1)
             idx = torch.cat(self.comm.all_gather(idx.contiguous()), dim=-1)
-        return vals, idx
+        t1 = _Ctx()
+        t1.out_val, t1.out_idx = vals.contiguous(), idx.contiguous()
+        st = self._make_sampler_state(t1.out_val, n, t1)
+        spec = dict(spec, edits=[])                    # edits were applied before the top-k
+        self._upload_sampling(st, n, spec)
+        F.sample(st.sample)
+        self._launches += 1
+        return self._read_tokens(st, n)
 
     def peer_status(self) -> int:
         return int(self.ctrl[1].item())

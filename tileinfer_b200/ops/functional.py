@@ -53,6 +53,20 @@ class TopkParams(ctypes.Structure):
                 ("vocab_start", _I), ("tp", _I), ("rank", _I), ("order", _I), ("m_cap", _I)]
 
 
+class EditParams(ctypes.Structure):
+    _fields_ = [("logits", _P), ("row_slot", _P), ("add_rows", _P), ("add_valid", _P), ("pen_ids", _P), ("pen_cnt", _P),
+                ("pen_rp", _P), ("M", _I), ("V", _I), ("ld", _I), ("pen_cap", _I), ("chunk", _I)]
+
+
+class SampleParams(ctypes.Structure):
+    _fields_ = [("cand_val", _P), ("cand_idx", _P), ("temperature", _P), ("top_k", _P), ("top_p", _P), ("u", _P),
+                ("out_tok", _P), ("status_src", _P), ("M", _I), ("n_cand", _I)]
+
+
+_l.register("ti_edit_params_size", _I, [])
+_l.register("ti_sample_params_size", _I, [])
+_l.register("ti_logits_edit", _I, [ctypes.POINTER(EditParams), _P])
+_l.register("ti_sample", _I, [ctypes.POINTER(SampleParams), _P])
 _l.register("ti_embed", _I, [_P, _P, _P, _I, _I, _I, _P, _P])
 _l.register("ti_rmsnorm", _I, [_P, _P, _P, _P, _P, _I, _I, _F, _I, _P])
 _l.register("ti_act_mul", _I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P])
@@ -87,7 +101,8 @@ def L():
     lib = _l.lib()
     if not _checked:
         for fn, st in (("ti_gdn_params_size", GdnParams), ("ti_qkv_prep_params_size", QkvPrepParams),
-                       ("ti_attn_params_size", AttnParams), ("ti_topk_params_size", TopkParams)):
+                       ("ti_attn_params_size", AttnParams), ("ti_topk_params_size", TopkParams),
+                       ("ti_edit_params_size", EditParams), ("ti_sample_params_size", SampleParams)):
             if getattr(lib, fn)() != ctypes.sizeof(st):
                 raise RuntimeError(f"{st.__name__} layout mismatch between Python and CUDA")
         _checked = True
@@ -384,6 +399,14 @@ def attn_prefill(q, kcache, vcache, num_blocks, block_tables, positions, tiles, 
     check(L().ti_attn_prefill(ptr(q), q.shape[0], ptr(kcache), ptr(vcache), num_blocks, ptr(block_tables), ptr(positions),
                               ptr(tiles[0]), ptr(tiles[1]), ptr(tiles[2]), n, ptr(gate_src), ptr(out), hq, hkv,
                               max_blocks, ld, scale, D, status_ptr(), stream()), "ti_attn_prefill")
+
+
+def logits_edit(p: EditParams):
+    check(L().ti_logits_edit(ctypes.byref(p), stream()), "ti_logits_edit")
+
+
+def sample(p: SampleParams):
+    check(L().ti_sample(ctypes.byref(p), stream()), "ti_sample")
 
 
 def topk(p: TopkParams):
