@@ -254,6 +254,7 @@ class _Ctx:
     snap_conv = None
     num_snap = 0
     cu = None
+    tiles = None            # [3, n] query tiles of the tcgen05 prefill attention (sequence, first token, tokens)
 
 
 class _StepMixin:
@@ -412,7 +413,13 @@ class _StepMixin:
                 a.ld, a.num_qg = x.proj.stride(0), x.num_qg
                 a.scale_log2e = self.D ** -0.5 * 1.4426950408889634
                 F.attn_paged(a, self.D)
-                self._launches += 3
+                self._launches += 3 if x.num_qg else 1
+                if x.tiles is not None:
+                    # sequences with many tokens in this step: 128-row query tiles on the tcgen05 tensor cores
+                    F.attn_prefill(x.qbuf, self.kv[ia, 0], self.kv[ia, 1], self.num_blocks, x.block_tables, x.positions,
+                                   x.tiles, x.proj, mix, hq=self.hq, hkv=self.hkv, D=self.D, max_blocks=x.max_blocks,
+                                   ld=x.proj.stride(0))
+                    self._launches += 1
                 self._rowpar(L.o, mix, cur, nxt, T)
                 ia += 1
             cur, nxt = nxt, cur
@@ -474,16 +481,26 @@ class _RunMixin:
         return torch.cat([t.out_val for t in outs]), torch.cat([t.out_idx for t in outs])
 
     # ------------------------------------------------------------------ eager variable-length step
+    PREFILL_ATTN_MIN_TOKENS = 16      # sequences with at least this many tokens in a step use the tcgen05 attention
+
     def _fill_ctx(self, x: _Ctx, batch, host=None):
-        """Copies the batch description into the device tensors of `x`."""
+        """Work lists of the two attention kernels: query groups of one or two tokens for the split-KV kernel
+        (decode tokens, short chunks) and 128-token query tiles, longest context first, for the tcgen05 kernel."""
         S, T = batch.num_seqs, batch.cu_seqlens[-1]
         gt = self._tokens_per_group()
-        qg_seq, qg_tok0, qg_ntok = [], [], []
+        qg_seq, qg_tok0, qg_ntok, tiles = [], [], [], []
         for s in range(S):
             t0, t1 = batch.cu_seqlens[s], batch.cu_seqlens[s + 1]
+            if t1 - t0 >= self.PREFILL_ATTN_MIN_TOKENS:
+                start = batch.context_lens[s] - (t1 - t0)
+                for a in range(t0, t1, 128):
+                    n = min(128, t1 - a)
+                    tiles.append((start + (a - t0) + n, s, a, n))
+                continue
             for a in range(t0, t1, gt):
                 qg_seq.append(s); qg_tok0.append(a); qg_ntok.append(min(gt, t1 - a))
-        return qg_seq, qg_tok0, qg_ntok
+        tiles.sort(reverse=True)
+        return qg_seq, qg_tok0, qg_ntok, tiles
 
     @torch.no_grad()
     def forward(self, batch):
@@ -492,10 +509,10 @@ class _RunMixin:
         into the lm_head kernel)."""
         dev = self.dev
         S, T = batch.num_seqs, batch.cu_seqlens[-1]
-        qg_seq, qg_tok0, qg_ntok = self._fill_ctx(None, batch)
+        qg_seq, qg_tok0, qg_ntok, tiles = self._fill_ctx(None, batch)
         nq = len(qg_seq)
         max_blocks = max(len(b) for b in batch.block_tables)
-        nsplit = 1 if nq * self.hkv >= 148 else max(1, min(32, -(-1184 // (nq * self.hkv))))
+        nsplit = 1 if nq * self.hkv >= 148 else max(1, min(32, -(-1184 // (max(nq, 1) * self.hkv))))
         x = self._alloc_ctx(T, S, max_blocks, nq, nsplit)
         x.ids.copy_(batch.input_ids, non_blocking=True)
         x.positions.copy_(batch.positions.to(torch.int32), non_blocking=True)
@@ -506,7 +523,11 @@ class _RunMixin:
         for s, b in enumerate(batch.block_tables):
             bt[s, :len(b)] = torch.tensor(b, dtype=torch.int32)
         x.block_tables.copy_(bt, non_blocking=True)
-        x.qg.copy_(torch.tensor([qg_seq, qg_tok0, qg_ntok], dtype=torch.int32), non_blocking=True)
+        if nq:
+            x.qg.copy_(torch.tensor([qg_seq, qg_tok0, qg_ntok], dtype=torch.int32), non_blocking=True)
+        if tiles and self.cfg.num_attn_layers:
+            x.tiles = torch.tensor([[t[1] for t in tiles], [t[2] for t in tiles], [t[3] for t in tiles]],
+                                   dtype=torch.int32).to(dev, non_blocking=True)
         snaps = []
         if batch.snapshot_at and any(batch.snapshot_at):
             ns = max(len(p) for p in batch.snapshot_at)
