@@ -735,3 +735,107 @@ def test_sample_kernel_matches_host_sampler(n_cand):
     # the draw is a float computation: allow the rare row where the uniform number lands within 1e-5 of a CDF step
     diff = [i for i in range(M) if got[i] != want[i]]
     assert len(diff) <= 1, (diff, got, want)
+
+
+@pytest.mark.parametrize("dk,hk,hv,state_bf16", [(128, 2, 6, False), (64, 4, 8, False), (128, 2, 4, True)])
+def test_gdn_chunked_matches_recurrence(dk, hk, hv, state_bf16):
+    """Chunk-parallel (WY) DeltaNet prefill against the fp32 token-serial rule and against the serial kernel:
+    sequences of 1 .. 300 tokens in one flattened batch, non-zero initial state and conv history, snapshots at
+    block-aligned points inside and at the end of chunks."""
+    from tileinfer_b200.models.reference_cpu import gdn_recurrent, l2norm, rmsnorm, softplus20
+    F = _F()
+    torch.manual_seed(0)
+    dv = dk
+    lens = [1, 7, 33, 200, 64, 300]
+    S, T = len(lens), sum(lens)
+    nch = 2 * dk + dv
+    kd, vd = hk * dk, hv * dv
+    ld = 2 * kd + 2 * vd + 2 * hv + 6
+    proj = (torch.randn(T, ld, device="cuda")).to(BF16)
+    conv_w = torch.randn(2 * kd + vd, 4, device="cuda") * 0.5
+    A_log = torch.randn(hv, device="cuda") * 0.5
+    dt_bias = torch.randn(hv, device="cuda") * 0.5
+    norm_w = 1 + 0.1 * torch.randn(dv, device="cuda")
+    nslots = 8
+    slots = torch.tensor([2, 0, 3, 5, 7, 6], dtype=torch.int32, device="cuda")
+    sdt = BF16 if state_bf16 else torch.float32
+    state = (torch.randn(nslots, hv, dk, dv, device="cuda") * 0.1).to(sdt)
+    hist = (torch.randn(nslots, 3, 2 * kd + vd, device="cuda")).to(BF16)
+    rep = hv // hk
+    cs = torch.zeros(nslots, hv, 3, nch, dtype=BF16, device="cuda")
+    for vh in range(hv):
+        kh = vh // rep
+        cs[:, vh, :, :dk] = hist[:, :, kh * dk:(kh + 1) * dk]
+        cs[:, vh, :, dk:2 * dk] = hist[:, :, kd + kh * dk:kd + (kh + 1) * dk]
+        cs[:, vh, :, 2 * dk:] = hist[:, :, 2 * kd + vh * dv:2 * kd + (vh + 1) * dv]
+    state0, cs0 = state.clone(), cs.clone()
+    cu_l = [0]
+    for n in lens:
+        cu_l.append(cu_l[-1] + n)
+    cu = torch.tensor(cu_l, dtype=torch.int32, device="cuda")
+    # snapshot points (relative token counts): none, none, 16 and 32, 48 and 192, 64, 80 and 288
+    snap_pts = [[], [], [16, 32], [48, 192], [64], [80, 288]]
+    NS = 2
+    snap_rel = torch.zeros(S, NS, dtype=torch.int32)
+    snap_idx = torch.zeros(S, NS, dtype=torch.int32)
+    ent = 0
+    for s, pts in enumerate(snap_pts):
+        for j, r in enumerate(pts):
+            snap_rel[s, j], snap_idx[s, j] = r, ent
+            ent += 1
+    snap_state = torch.zeros(ent, hv, dk, dv, device="cuda")
+    snap_conv = torch.zeros(ent, hv, 3, nch, dtype=BF16, device="cuda")
+    rel_d, idx_d = snap_rel.cuda(), snap_idx.cuda()
+    neg = (-A_log.exp()).contiguous()
+
+    # ---- serial kernel (exact recurrence) on copies
+    st1, cs1, out1 = state0.clone(), cs0.clone(), torch.zeros(T, vd, dtype=BF16, device="cuda")
+    sn1, sc1 = torch.zeros_like(snap_state), torch.zeros_like(snap_conv)
+    p = F.GdnParams()
+    p.proj, p.conv_w, p.neg_a_exp, p.dt_bias, p.norm_w = proj.data_ptr(), conv_w.data_ptr(), neg.data_ptr(), dt_bias.data_ptr(), norm_w.data_ptr()
+    p.state, p.conv_state, p.slots, p.cu, p.out = st1.data_ptr(), cs1.data_ptr(), slots.data_ptr(), cu.data_ptr(), out1.data_ptr()
+    p.snap_rel, p.snap_idx, p.snap_state, p.snap_conv, p.num_snap = rel_d.data_ptr(), idx_d.data_ptr(), sn1.data_ptr(), sc1.data_ptr(), NS
+    p.ld, p.hk, p.hv, p.eps = ld, hk, hv, 1e-6
+    F.gdn_step(p, S, dk, dv, state_bf16)
+
+    # ---- chunked kernels
+    out = torch.zeros(T, vd, dtype=BF16, device="cuda")
+    ck, seq_ck = F.gdn_chunk_table(cu_l, snap_rel.tolist(), snap_idx.tolist())
+    assert int(ck[2].sum()) == T and int(ck[2].max()) <= 64
+    ck, seq_ck = ck.cuda(), seq_ck.cuda()
+    c = F.GdnChunkParams()
+    c.proj, c.conv_w, c.neg_a_exp, c.dt_bias, c.norm_w = proj.data_ptr(), conv_w.data_ptr(), neg.data_ptr(), dt_bias.data_ptr(), norm_w.data_ptr()
+    c.state, c.conv_state, c.slots, c.cu, c.out = state.data_ptr(), cs.data_ptr(), slots.data_ptr(), cu.data_ptr(), out.data_ptr()
+    c.snap_rel, c.snap_idx, c.snap_state, c.snap_conv, c.num_snap = rel_d.data_ptr(), idx_d.data_ptr(), snap_state.data_ptr(), snap_conv.data_ptr(), NS
+    c.ck_seq, c.ck_tok0, c.ck_ntok, c.ck_snap, c.seq_ck, c.nc = ck[0].data_ptr(), ck[1].data_ptr(), ck[2].data_ptr(), ck[3].data_ptr(), seq_ck.data_ptr(), ck.shape[1]
+    ws = F.GdnChunkWorkspace("cuda").get(ck.shape[1] * hv, dk, dv)
+    c.wf, c.qf, c.mf, c.kf, c.u, c.gamma = (b.data_ptr() for b in ws)
+    c.ld, c.hk, c.hv, c.eps = ld, hk, hv, 1e-6
+    F.gdn_chunked(c, S, T, dk, dv, state_bf16)
+    torch.cuda.synchronize()
+
+    # conv history and conv snapshots are copies of raw inputs: bit-equal to the serial kernel's
+    assert torch.equal(cs, cs1) and torch.equal(snap_conv, sc1)
+    tol = dict(rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(out.float(), out1.float(), **tol)
+    torch.testing.assert_close(state.float(), st1.float(), rtol=3e-2, atol=1e-2)
+    torch.testing.assert_close(snap_state, sn1, rtol=3e-2, atol=1e-2)
+    # and against the fp32 reference of the rule itself
+    for s in range(S):
+        t0, t1, slot = cu_l[s], cu_l[s + 1], int(slots[s])
+        raw = proj[t0:t1, :2 * kd + vd].float()
+        seq = torch.cat([hist[slot].float(), raw], 0)
+        conv = torch.nn.functional.silu((seq.unfold(0, 4, 1) * conv_w[None]).sum(-1))
+        Tn = t1 - t0
+        q = l2norm(conv[:, :kd].reshape(Tn, hk, dk)).repeat_interleave(rep, 1) * dk ** -0.5
+        k = l2norm(conv[:, kd:2 * kd].reshape(Tn, hk, dk)).repeat_interleave(rep, 1)
+        v = conv[:, 2 * kd:].reshape(Tn, hv, dv)
+        z = proj[t0:t1, 2 * kd + vd:2 * kd + 2 * vd].float().reshape(Tn, hv, dv)
+        b = proj[t0:t1, 2 * kd + 2 * vd:2 * kd + 2 * vd + hv].float()
+        a = proj[t0:t1, 2 * kd + 2 * vd + hv:2 * kd + 2 * vd + 2 * hv].float()
+        g = -A_log.exp()[None] * softplus20(a + dt_bias[None])
+        o, Sn = gdn_recurrent(q, k, v, g, torch.sigmoid(b), state0[slot].float())
+        ref = rmsnorm(o, norm_w, 1e-6, one_plus=False) * torch.nn.functional.silu(z)
+        torch.testing.assert_close(out[t0:t1].float(), ref.reshape(Tn, vd), **tol)
+        torch.testing.assert_close(state[slot].float(), Sn, rtol=3e-2, atol=1e-2)
+    assert torch.equal(state[1], state0[1]) and torch.equal(cs[1], cs0[1])      # an unused slot stays untouched

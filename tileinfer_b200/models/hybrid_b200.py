@@ -23,7 +23,7 @@ import torch
 
 from ..ops import functional as F
 from ..ops.functional import (EPI_F32, EPI_ROWPAR, EPI_STORE, EPI_SWIGLU, XGLOBAL, XNORM, AttnParams, EditParams,
-                              GdnParams, GemvWorkspace, LinearW, QkvPrepParams, SampleParams, TopkParams, ptr)
+                              GdnChunkParams, GdnParams, GemvWorkspace, LinearW, QkvPrepParams, SampleParams, TopkParams, ptr)
 from .config import ModelConfig
 from .weights import ShardSpec, shard_layer
 
@@ -94,6 +94,9 @@ class _ModelBase:
         # more L2 traffic than the grid-wide collect + barrier it replaces for more
         self.ll_handoff_max_tp = int(os.environ.get("TI_LL_HANDOFF_MAX_TP", "2"))
         self.gdn_split = os.environ.get("TI_GDN_SPLIT", "0") == "1"   # prefill: a head's columns over a 4-block cluster
+        # steps in which some sequence has at least this many tokens use the chunk-parallel DeltaNet kernels
+        self.gdn_chunk_min_tokens = int(os.environ.get("TI_GDN_CHUNK_MIN", "32"))
+        self.gdn_ws = F.GdnChunkWorkspace(dev)
         self.gemm_min_rows = int(os.environ.get("TI_GEMM_MIN_ROWS", "8"))    # more rows than this: tcgen05 GEMM
 
     # ------------------------------------------------------------------ weights: build / on-disk shard cache
@@ -255,6 +258,8 @@ class _Ctx:
     num_snap = 0
     cu = None
     tiles = None            # [3, n] query tiles of the tcgen05 prefill attention (sequence, first token, tokens)
+    ck = None               # [4, nc] chunk table of the chunked DeltaNet prefill (None: token-serial kernel)
+    seq_ck = None
 
 
 class _StepMixin:
@@ -386,8 +391,21 @@ class _StepMixin:
                     p.snap_rel, p.snap_idx, p.num_snap = ptr(x.snap_rel), ptr(x.snap_idx), x.num_snap
                     p.snap_state, p.snap_conv = ptr(x.snap_state[ig]), ptr(x.snap_conv[ig])
                 self._flush()
-                F.gdn_step(p, S, self.dk, self.dv, self.state_bf16, split=self.gdn_split and T > S, single=T == S)
-                self._launches += 1
+                if x.ck is not None:
+                    # prefill: chunk-parallel gated delta rule on the tensor cores
+                    c = GdnChunkParams()
+                    for f in ("proj", "conv_w", "neg_a_exp", "dt_bias", "norm_w", "state", "conv_state", "slots", "cu",
+                              "out", "snap_rel", "snap_idx", "snap_state", "snap_conv", "ld", "hk", "hv", "num_snap", "eps"):
+                        setattr(c, f, getattr(p, f))
+                    c.ck_seq, c.ck_tok0, c.ck_ntok, c.ck_snap = ptr(x.ck[0]), ptr(x.ck[1]), ptr(x.ck[2]), ptr(x.ck[3])
+                    c.seq_ck, c.nc = ptr(x.seq_ck), x.ck.shape[1]
+                    ws = self.gdn_ws.get(c.nc * self.hv, self.dk, self.dv)
+                    c.wf, c.qf, c.mf, c.kf, c.u, c.gamma = (ptr(b) for b in ws)
+                    F.gdn_chunked(c, S, T, self.dk, self.dv, self.state_bf16)
+                    self._launches += 4
+                else:
+                    F.gdn_step(p, S, self.dk, self.dv, self.state_bf16, split=self.gdn_split and T > S, single=T == S)
+                    self._launches += 1
                 # the kernel writes [T, hv*dv] densely
                 mix = x.mix.view(-1)[:T * self.hv * self.dv].view(T, self.hv * self.dv)
                 self._rowpar(L.out, mix, cur, nxt, T)
@@ -543,6 +561,13 @@ class _RunMixin:
             x.snap_rel, x.snap_idx, x.num_snap = rel.to(dev), idx.to(dev), ns
             x.snap_state = torch.empty(ng, len(snaps), self.hv, self.dk, self.dv, dtype=torch.float32, device=dev)
             x.snap_conv = torch.empty(ng, len(snaps), self.hv, 3, self.nch, dtype=BF16, device=dev)
+        lens = [b - a for a, b in zip(batch.cu_seqlens[:-1], batch.cu_seqlens[1:])]
+        if self.cfg.num_gdn_layers and self.gdn_chunk_min_tokens > 0 and max(lens) >= self.gdn_chunk_min_tokens:
+            rel_l = ent_l = None
+            if snaps:
+                rel_l, ent_l = rel.tolist(), idx.tolist()
+            ck, seq_ck = F.gdn_chunk_table(batch.cu_seqlens, rel_l, ent_l)
+            x.ck, x.seq_ck = ck.to(dev, non_blocking=True), seq_ck.to(dev, non_blocking=True)
         cur = self._run_layers(x)
         last = torch.tensor([c - 1 for c in batch.cu_seqlens[1:]], dtype=torch.long, device=dev)
         hidden = cur[last]

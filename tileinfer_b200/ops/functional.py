@@ -32,6 +32,14 @@ class GdnParams(ctypes.Structure):
                 ("snap_conv", _P), ("ld", _I), ("hk", _I), ("hv", _I), ("num_snap", _I), ("eps", _F), ("snap_idx", _P)]
 
 
+class GdnChunkParams(ctypes.Structure):
+    _fields_ = [("proj", _P), ("conv_w", _P), ("neg_a_exp", _P), ("dt_bias", _P), ("norm_w", _P), ("state", _P),
+                ("conv_state", _P), ("slots", _P), ("cu", _P), ("out", _P), ("snap_rel", _P), ("snap_idx", _P),
+                ("snap_state", _P), ("snap_conv", _P), ("ck_seq", _P), ("ck_tok0", _P), ("ck_ntok", _P), ("ck_snap", _P),
+                ("seq_ck", _P), ("wf", _P), ("qf", _P), ("mf", _P), ("kf", _P), ("u", _P), ("gamma", _P),
+                ("ld", _I), ("hk", _I), ("hv", _I), ("num_snap", _I), ("nc", _I), ("eps", _F)]
+
+
 class QkvPrepParams(ctypes.Structure):
     _fields_ = [("proj", _P), ("q_norm", _P), ("k_norm", _P), ("positions", _P), ("slot_mapping", _P),
                 ("q_out", _P), ("kcache", _P), ("vcache", _P), ("ld", _I), ("hq", _I), ("hkv", _I),
@@ -73,6 +81,9 @@ _l.register("ti_act_mul", _I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P])
 _l.register("ti_swiglu_interleaved", _I, [_P, _P, _I, _I, _I, _I, _P])
 _l.register("ti_gdn_params_size", _I, [])
 _l.register("ti_gdn_step", _I, [ctypes.POINTER(GdnParams), _I, _I, _I, _I, _I, _P])
+_l.register("ti_gdn_chunk_params_size", _I, [])
+_l.register("ti_gdn_chunk_ws_bytes", _I, [_I, _I, _I])
+_l.register("ti_gdn_chunked", _I, [ctypes.POINTER(GdnChunkParams), _I, _I, _I, _I, _I, _P])
 _l.register("ti_qkv_prep_params_size", _I, [])
 _l.register("ti_attn_params_size", _I, [])
 _l.register("ti_qkv_prep", _I, [ctypes.POINTER(QkvPrepParams), _I, _I, _P])
@@ -100,7 +111,7 @@ def L():
     global _checked
     lib = _l.lib()
     if not _checked:
-        for fn, st in (("ti_gdn_params_size", GdnParams), ("ti_qkv_prep_params_size", QkvPrepParams),
+        for fn, st in (("ti_gdn_params_size", GdnParams), ("ti_gdn_chunk_params_size", GdnChunkParams), ("ti_qkv_prep_params_size", QkvPrepParams),
                        ("ti_attn_params_size", AttnParams), ("ti_topk_params_size", TopkParams),
                        ("ti_edit_params_size", EditParams), ("ti_sample_params_size", SampleParams)):
             if getattr(lib, fn)() != ctypes.sizeof(st):
@@ -380,6 +391,55 @@ def gdn_step(p: GdnParams, num_seqs: int, dk: int, dv: int, state_bf16: bool, sp
     of a head go to a cluster of blocks (prefill; optional)."""
     mode = 2 if single else int(split)
     check(L().ti_gdn_step(ctypes.byref(p), num_seqs, dk, dv, int(state_bf16), mode, stream()), "ti_gdn_step")
+
+
+GDN_CHUNK = 64
+
+
+def gdn_chunk_table(cu_seqlens, snapshot_rel=None, snapshot_entry=None):
+    """Chunk table of the chunked DeltaNet prefill: every sequence is cut into chunks of at most 64 tokens that
+    also end wherever a state snapshot is wanted.  `snapshot_rel[s]`: token counts (relative to the start of the
+    step) after which sequence s snapshots, `snapshot_entry[s]`: the entries of the snapshot buffers.
+    Returns int32 tensors (ck [4, nc] = sequence | first flat token | tokens | snapshot entry or -1, seq_ck [S+1])."""
+    seq, tok0, ntok, snap, seq_ck = [], [], [], [], [0]
+    for s in range(len(cu_seqlens) - 1):
+        t0, t1 = cu_seqlens[s], cu_seqlens[s + 1]
+        pts = {}
+        if snapshot_rel is not None:
+            for r, e in zip(snapshot_rel[s], snapshot_entry[s]):
+                if 0 < r <= t1 - t0:
+                    pts[r] = e
+        cuts = sorted(set(range(GDN_CHUNK, t1 - t0, GDN_CHUNK)) | set(pts) | {t1 - t0})
+        # chunks never straddle a snapshot point; between two cuts they are at most 64 tokens long
+        a = 0
+        for c in cuts:
+            while a < c:
+                n = min(GDN_CHUNK, c - a)
+                seq.append(s); tok0.append(t0 + a); ntok.append(n)
+                a += n
+                snap.append(pts.get(a, -1))
+        seq_ck.append(len(seq))
+    return torch.tensor([seq, tok0, ntok, snap], dtype=torch.int32), torch.tensor(seq_ck, dtype=torch.int32)
+
+
+class GdnChunkWorkspace:
+    """Fragment-order operands of the scan kernel for up to `nc * hv` (chunk, head) pairs; grows on demand."""
+
+    def __init__(self, device):
+        self.device, self.cap, self.bufs = device, 0, None
+
+    def get(self, n_items: int, dk: int, dv: int):
+        if n_items > self.cap or self.bufs is None or self.key != (dk, dv):
+            lib = L()
+            sizes = [lib.ti_gdn_chunk_ws_bytes(dk, dv, i) for i in range(6)]
+            cap = max(n_items, 2 * self.cap)
+            self.bufs = [torch.empty(cap * sz, dtype=torch.uint8, device=self.device) for sz in sizes]
+            self.cap, self.key = cap, (dk, dv)
+        return self.bufs
+
+
+def gdn_chunked(p: GdnChunkParams, num_seqs: int, T: int, dk: int, dv: int, state_bf16: bool):
+    check(L().ti_gdn_chunked(ctypes.byref(p), num_seqs, T, dk, dv, int(state_bf16), stream()), "ti_gdn_chunked")
 
 
 def qkv_prep(p: QkvPrepParams, T: int, D: int):
