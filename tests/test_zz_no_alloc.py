@@ -37,6 +37,10 @@ def test_static_scratch_topk_matches_regular_entry_twice():
     torch.manual_seed(7)
     stream = torch.cuda.current_stream().cuda_stream
     cases = [(5, 31040, 50, 1000), (16, 248320, 64, 0), (1, 1024, 1, 3)]
+    # tensors that earlier tests left in reference cycles must not be released in the middle of the measurement
+    import gc
+    gc.collect()
+    torch.cuda.synchronize()
     for rows, vocab, k, start in cases:
         logits = torch.randn(rows, vocab, device="cuda")
         out_val = torch.empty(rows, k, dtype=torch.float32, device="cuda")
@@ -44,12 +48,16 @@ def test_static_scratch_topk_matches_regular_entry_twice():
         for call in range(2):                      # two calls in a row share the static scratch
             if call == 1:
                 logits = torch.randn(rows, vocab, device="cuda")
-            used_before = torch.cuda.memory_allocated()
-            rc = lib.ti_topk_static(logits.data_ptr(), rows, vocab, logits.stride(0), k, start, out_val.data_ptr(),
-                                    out_idx.data_ptr(), stream)
-            assert rc == 0, lib.ti_topk_static_error(rc)
-            torch.cuda.synchronize()
-            assert torch.cuda.memory_allocated() == used_before
+            gc.disable()
+            try:
+                used_before = torch.cuda.memory_allocated()
+                rc = lib.ti_topk_static(logits.data_ptr(), rows, vocab, logits.stride(0), k, start, out_val.data_ptr(),
+                                        out_idx.data_ptr(), stream)
+                assert rc == 0, lib.ti_topk_static_error(rc)
+                torch.cuda.synchronize()
+                assert torch.cuda.memory_allocated() == used_before
+            finally:
+                gc.enable()
             ref_val, ref_idx = _reference_entry(logits, k, start)
             torch.cuda.synchronize()
             torch.testing.assert_close(out_val, ref_val, rtol=0, atol=0)

@@ -167,7 +167,7 @@ class _ModelBase:
         os.replace(tmp, path)
 
     def _load_shards(self, path: str):
-        blob = torch.load(path, map_location="cpu", weights_only=False)
+        blob = torch.load(path, map_location="cpu", weights_only=True)
         if blob.get("format") != 1 or len(blob["layers"]) != self.cfg.num_layers:
             raise RuntimeError(f"{path}: not a shard cache of this model")
         dev = self.dev
@@ -393,15 +393,15 @@ class _StepMixin:
                 self._flush()
                 if x.ck is not None:
                     # prefill: chunk-parallel gated delta rule on the tensor cores
-                    c = GdnChunkParams()
+                    cp = GdnChunkParams()
                     for f in ("proj", "conv_w", "neg_a_exp", "dt_bias", "norm_w", "state", "conv_state", "slots", "cu",
                               "out", "snap_rel", "snap_idx", "snap_state", "snap_conv", "ld", "hk", "hv", "num_snap", "eps"):
-                        setattr(c, f, getattr(p, f))
-                    c.ck_seq, c.ck_tok0, c.ck_ntok, c.ck_snap = ptr(x.ck[0]), ptr(x.ck[1]), ptr(x.ck[2]), ptr(x.ck[3])
-                    c.seq_ck, c.nc = ptr(x.seq_ck), x.ck.shape[1]
-                    ws = self.gdn_ws.get(c.nc * self.hv, self.dk, self.dv)
-                    c.wf, c.qf, c.mf, c.kf, c.u, c.gamma = (ptr(b) for b in ws)
-                    F.gdn_chunked(c, S, T, self.dk, self.dv, self.state_bf16)
+                        setattr(cp, f, getattr(p, f))
+                    cp.ck_seq, cp.ck_tok0, cp.ck_ntok, cp.ck_snap = ptr(x.ck[0]), ptr(x.ck[1]), ptr(x.ck[2]), ptr(x.ck[3])
+                    cp.seq_ck, cp.nc = ptr(x.seq_ck), x.ck.shape[1]
+                    ws = self.gdn_ws.get(cp.nc * self.hv, self.dk, self.dv)
+                    cp.wf, cp.qf, cp.mf, cp.kf, cp.u, cp.gamma = (ptr(b) for b in ws)
+                    F.gdn_chunked(cp, S, T, self.dk, self.dv, self.state_bf16)
                     self._launches += 4
                 else:
                     F.gdn_step(p, S, self.dk, self.dv, self.state_bf16, split=self.gdn_split and T > S, single=T == S)
@@ -530,7 +530,7 @@ class _RunMixin:
         qg_seq, qg_tok0, qg_ntok, tiles = self._fill_ctx(None, batch)
         nq = len(qg_seq)
         max_blocks = max(len(b) for b in batch.block_tables)
-        nsplit = 1 if nq * self.hkv >= 148 else max(1, min(32, -(-1184 // (max(nq, 1) * self.hkv))))
+        nsplit = 1 if nq * self.hkv >= F.NUM_SMS else max(1, min(32, -(-8 * F.NUM_SMS // (max(nq, 1) * self.hkv))))
         x = self._alloc_ctx(T, S, max_blocks, nq, nsplit)
         x.ids.copy_(batch.input_ids, non_blocking=True)
         x.positions.copy_(batch.positions.to(torch.int32), non_blocking=True)
@@ -608,7 +608,7 @@ class _RunMixin:
         if g is not None:
             return g
         dev = self.dev
-        nsplit = max(1, min(32, -(-1184 // (B * self.hkv))))
+        nsplit = max(1, min(32, -(-8 * F.NUM_SMS // (B * self.hkv))))
         base = self.graphs.get((B, 1))
         g = _Ctx()
         if base is not None:      # same bucket, other k: share the input tensors

@@ -40,6 +40,7 @@ struct GdnParams {
   int ld, hk, hv, num_snap;
   float eps;
   const int* snap_idx;         // [S, NS] index of the snapshot buffer entry of (sequence, point), or nullptr (s * NS + j)
+  unsigned* status;            // error bits (a bounded wait that ran out); may be nullptr
 };
 
 TI_DEVICE size_t snap_entry(const GdnParams& p, int s, int j) {
@@ -177,7 +178,8 @@ __global__ void __launch_bounds__(DV * 4) gdn_token_kernel(const __grid_constant
       if (s + (int)gridDim.y < num_seqs) nxt = fetch(s + gridDim.y);
     }
     if (STAGED) {
-      mbar_wait(smem_u32(&full_bar[k & 1]), (uint32_t)((k >> 1) & 1), 2000000000ull, nullptr);
+      // an expired wait is reported in the status word (the state then read is whatever the buffer holds)
+      mbar_wait(smem_u32(&full_bar[k & 1]), (uint32_t)((k >> 1) & 1), 2000000000ull, p.status);
 #pragma unroll
       for (int i = 0; i < DPT; ++i) S[i] = ld_state<ST>(sb + (size_t)(dg * DPT + i) * DV + c);
     }

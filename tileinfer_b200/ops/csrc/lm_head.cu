@@ -11,6 +11,8 @@
 // k best by repeated block-wide arg-max.  Stage 2: one block per row merges chunks*k candidates the
 // same way, then (tp > 1) stores its k winners as tagged packets into every peer's buffer and waits,
 // bounded, for the peers' packets.
+#include <mutex>
+
 #include "common.cuh"
 #include "topk_static.h"
 
@@ -169,7 +171,8 @@ static __device__ __align__(256) int g_topk_static_idx[TI_TOPK_STATIC_MAX_ENTRIE
 constexpr int kMaxDevices = 64;
 static float* g_static_val_ptr[kMaxDevices];
 static int* g_static_idx_ptr[kMaxDevices];
-static bool g_static_ready[kMaxDevices];
+static std::once_flag g_static_once[kMaxDevices];      // the first calls of two threads on one device do not race
+static cudaError_t g_static_err[kMaxDevices];
 }  // namespace ti
 
 extern "C" {
@@ -182,6 +185,7 @@ const char* ti_topk_static_error(int code) {
     case -3: return "vocab must be in [1, 524288] and ld >= vocab";
     case -4: return "null pointer argument";
     case -5: return "more than 64 CUDA devices are not supported";
+    case -6: return "logits, out_val and out_idx must be device memory of the CURRENT device (the scratch is per device)";
     default: return code > 0 ? "CUDA error (value is a cudaError_t)" : "unknown error";
   }
 }
@@ -205,13 +209,23 @@ int ti_topk_static(const float* logits, int rows, int vocab, int ld, int k, int 
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= ti::kMaxDevices) return -5;
-  if (!ti::g_static_ready[dev]) {
-    e = cudaGetSymbolAddress((void**)&ti::g_static_val_ptr[dev], ti::g_topk_static_val);
-    if (e != cudaSuccess) return (int)e;
-    e = cudaGetSymbolAddress((void**)&ti::g_static_idx_ptr[dev], ti::g_topk_static_idx);
-    if (e != cudaSuccess) return (int)e;
-    ti::g_static_ready[dev] = true;
+  // the scratch belongs to the current device: inputs and outputs must live there too (a kernel on this device
+  // would otherwise combine another GPU's buffers with this GPU's scratch)
+  const void* ptrs[3] = {logits, out_val, out_idx};
+  for (const void* q : ptrs) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, q) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return -6;
+    }
+    if (at.type == cudaMemoryTypeDevice && at.device != dev) return -6;
   }
+  std::call_once(ti::g_static_once[dev], [dev] {
+    cudaError_t r = cudaGetSymbolAddress((void**)&ti::g_static_val_ptr[dev], ti::g_topk_static_val);
+    if (r == cudaSuccess) r = cudaGetSymbolAddress((void**)&ti::g_static_idx_ptr[dev], ti::g_topk_static_idx);
+    ti::g_static_err[dev] = r;
+  });
+  if (ti::g_static_err[dev] != cudaSuccess) return (int)ti::g_static_err[dev];
   ti::TopkParams p = {};
   p.logits = logits;
   p.ws_val = ti::g_static_val_ptr[dev];
@@ -230,8 +244,7 @@ int ti_topk_static(const float* logits, int rows, int vocab, int ld, int k, int 
   e = ti::launch_kernel(ti::topk_stage1_kernel, dim3(rows, chunks), dim3(256), 0, st, false, p);
   if (e != cudaSuccess) return (int)e;
   e = ti::launch_kernel(ti::topk_stage2_kernel, dim3(rows), dim3(256), 0, st, false, p);
-  if (e != cudaSuccess) return (int)e;
-  return (int)cudaGetLastError();
+  return (int)e;                         // the launch results only: no stale error of an unrelated earlier call
 }
 
 }  // extern "C"

@@ -16,8 +16,12 @@
 // overwrites every entry it later reads), but two calls that overlap on the GPU (different streams, or a
 // second thread) corrupt each other: serialise them.
 //
+// Device ownership: the scratch is per GPU.  The CURRENT device of the calling thread must own `logits`, both
+// outputs and the stream; a device pointer of another GPU is rejected with code -6.
+//
 // First call on a device: it resolves the device address of the scratch array (one cudaGetSymbolAddress,
-// no allocation).  Make that first call outside any stream capture.
+// no allocation; guarded so that two threads may make it at the same time).  Make that first call outside any
+// stream capture.
 #pragma once
 
 #define TI_TOPK_STATIC_MAX_ROWS 16

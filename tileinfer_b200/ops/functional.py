@@ -19,7 +19,21 @@ _I, _P, _F = ctypes.c_int, ctypes.c_void_p, ctypes.c_float
 XGLOBAL, XNORM = 0, 1
 EPI_STORE, EPI_SWIGLU, EPI_ROWPAR, EPI_F32 = 0, 1, 2, 3
 W_INT8, W_BF16 = 0, 1
-NUM_SMS = 148
+
+
+def _device_sm_count() -> int:
+    """Streaming multiprocessors of the current GPU (148 on a B200; the fallback when no GPU is visible).  The
+    persistent GEMV launches one CTA per SM and its grid barrier needs every CTA resident, so the grid must follow
+    the device, not a constant."""
+    try:
+        if torch.cuda.is_available():
+            return int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+    except Exception:
+        pass
+    return 148
+
+
+NUM_SMS = _device_sm_count()
 GEMV_WARPS = int(os.environ.get("TI_GEMV_WARPS", "16"))   # must match the -DTI_GEMV_WARPS the library was built with
 GEMV_TPS = int(os.environ.get("TI_GEMV_TPS", "8"))            # 512-byte tiles per ring stage
 GEMV_MAX_STAGES = int(os.environ.get("TI_GEMV_STAGES", "6"))
@@ -29,7 +43,7 @@ GEMV_UNITS_PER_WARP = int(os.environ.get("TI_GEMV_UPW", "4"))
 class GdnParams(ctypes.Structure):
     _fields_ = [("proj", _P), ("conv_w", _P), ("neg_a_exp", _P), ("dt_bias", _P), ("norm_w", _P), ("state", _P),
                 ("conv_state", _P), ("slots", _P), ("cu", _P), ("out", _P), ("snap_rel", _P), ("snap_state", _P),
-                ("snap_conv", _P), ("ld", _I), ("hk", _I), ("hv", _I), ("num_snap", _I), ("eps", _F), ("snap_idx", _P)]
+                ("snap_conv", _P), ("ld", _I), ("hk", _I), ("hv", _I), ("num_snap", _I), ("eps", _F), ("snap_idx", _P), ("status", _P)]
 
 
 class GdnChunkParams(ctypes.Structure):
@@ -390,6 +404,8 @@ def gdn_step(p: GdnParams, num_seqs: int, dk: int, dv: int, state_bf16: bool, sp
     """single: every sequence has exactly one token (decode): the single-pass kernel.  split: the state columns
     of a head go to a cluster of blocks (prefill; optional)."""
     mode = 2 if single else int(split)
+    if not p.status:
+        p.status = status_ptr()
     check(L().ti_gdn_step(ctypes.byref(p), num_seqs, dk, dv, int(state_bf16), mode, stream()), "ti_gdn_step")
 
 

@@ -90,12 +90,8 @@ class Service:
     def stream(self, prompt: str, sp: SamplingParams):
         with self.lock:
             self._announce(prompt, sp)
-            seqs_before = set(self.llm._all_seqs)
-            last = None
             for _, text, done in self.llm.generate_stream([prompt], sp):
                 yield text, done
-                last = done
-            del seqs_before, last
 
 
 def make_handler(svc: Service):
