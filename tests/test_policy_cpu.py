@@ -197,9 +197,10 @@ def test_gemv_planner_choices():
     # 27B layer shapes, one row: (row tiles, k tiles)
     assert F.plan_team(4352, 80, 1) == 1          # gate_up: more units than warps -> warp-owned units
     assert F.plan_team(2060, 80, 1) == 1          # in_proj: 0.87 units per warp is enough
-    assert F.plan_team(640, 272, 1) == 2          # down: few row tiles -> two warps share a unit
-    assert F.plan_team(640, 96, 1) == 2           # out_proj
-    assert F.plan_team(544, 80, 1) == 4 and F.plan_team(258, 80, 1) == 4      # 1/8 tensor-parallel shards
+    assert F.plan_team(640, 272, 1) == 3          # down: few row tiles -> three warps share a unit (five teams per CTA)
+    assert F.plan_team(640, 96, 1) == 3           # out_proj
+    assert F.plan_team(544, 80, 1) == 4 and F.plan_team(258, 80, 1) == 8      # 1/8 tensor-parallel shards
+    assert F.plan_team(640, 12, 1) == 1           # k too short to share
     assert F.plan_team(640, 272, 1, team=1) == 1
     R, tps, stages = F.plan_gemv(F.W_INT8, F.XNORM, 1, 4352, 80)
     assert (R, tps) == (1, 8) and stages == 3

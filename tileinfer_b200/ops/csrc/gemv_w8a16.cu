@@ -51,7 +51,7 @@ struct GemvParams {
   int tp, rank, order, m_cap;
   float eps;
   int stages;                    // depth of the per-warp weight ring (1..8)
-  int T;                         // team size (1, 2, 4, 8 or 16 warps of a CTA share a unit, each a k-slice)
+  int T;                         // team size (1..16 adjacent warps of a CTA share a unit, each a k-slice)
   unsigned long long* dbg;       // optional [ncta][32] globaltimer stamps of warp 0 (profiling aid): 0 start, 1 ring
                                  // primed, 2..4 all warps of the CTA reached the barrier before product 1..3, 5 end; per product op at 8 + 4*op:
                                  // marker reached, barrier passed, x staged, last unit done
@@ -484,11 +484,15 @@ TI_DEVICE void fill_op_table(const ChainParams& c, int warp, int cta, int ncta, 
   for (int op = 0; op < c.n_ops; ++op) {
     const GemvParams& p = c.op[op];
     const int U = num_units(p), T = p.T;
-    const int Wd = T > 1 ? W / T : W;
+    // team mode: a CTA holds kWarps / T whole teams (any T up to kWarps; the warps left over when T does not
+    // divide kWarps take no unit of this product)
+    const int tpc = kWarps / T;
+    const int Wd = T > 1 ? tpc * ncta : W;
+    const bool active = T == 1 || warp < tpc * T;
     int* t = tb + op * TB_N;
-    t[TB_U] = U;
+    t[TB_U] = active ? U : 0;
     t[TB_WD] = Wd;
-    t[TB_NS] = T > 1 ? (U + Wd - 1) / Wd : max(1, U / (2 * W));
+    t[TB_NS] = !active ? 0 : (T > 1 ? (U + Wd - 1) / Wd : max(1, U / (2 * W)));
     t[TB_WIDX] = T > 1 ? (warp / T) * ncta + cta : widx;
     t[TB_MEMBER] = T > 1 ? warp % T : 0;
     t[TB_BASE] = p.KB / T;
@@ -900,8 +904,7 @@ static int check(const GemvParams& p, int wt) {
   if (p.M < 1 || p.M > 16 || p.N < 2 || (p.N & 1) || p.K % tk || p.KB * tk != p.K) return -2;
   if (p.R < 1 || p.R > kMaxR || p.n_tiles < 1 || p.n_tiles >= (1 << 26)) return -3;
   if (p.S != 1 || p.kb_per_split != p.KB) return -6;
-  if (p.T != 1 && p.T != 2 && p.T != 4 && p.T != 8 && p.T != 16) return -6;
-  if (p.T > kWarps || p.KB < p.T) return -6;
+  if (p.T < 1 || p.T > kWarps || p.KB < p.T) return -6;
   if ((p.n_tiles + p.R - 1) / p.R >= kUnitMask) return -3;
   if (p.tps != kTPS) return -7;
   if (p.sched == nullptr || p.stages < 1 || p.stages > kMaxStages) return -7;

@@ -221,9 +221,15 @@ TEAM_BYTES = 2 * GEMV_WARPS * 32 * 16      # exchange buffer of team mode (must 
 
 
 def plan_team(n_tiles: int, KB: int, R: int, team: int | None = None, ncta: int = NUM_SMS) -> int:
-    """Team size T for a product: how many warps of a CTA share one unit, each streaming a slice of k.
+    """Team size T for a product: how many adjacent warps of a CTA share one unit, each streaming a slice of k.
     A product with fewer units than warps would leave warps (and the bytes they keep in flight) idle.
-    `team` (or TI_GEMV_T) forces a size."""
+    `team` (or TI_GEMV_T) forces a size.
+
+    Cost model (in 512-byte tiles a warp streams one after the other): a CTA holds GEMV_WARPS // T whole teams,
+    the units are dealt to the teams in waves, a unit costs ceil(KB / T) tiles per warp plus a fixed part (team
+    exchange and epilogue, about six tiles' worth).  Measured on the 27B layer at one row (chain of the four layer
+    products): out_proj / down with T = 2 -> 91.4 us, T = 3 -> 87.5 us, T = 5 or 16 -> 90-95 us; the half shards
+    of a 2-way tensor-parallel group 60.7 -> 58.2 us."""
     if team is None and "TI_GEMV_T" in os.environ:
         team = int(os.environ["TI_GEMV_T"])
     U = -(-n_tiles // R)
@@ -232,15 +238,15 @@ def plan_team(n_tiles: int, KB: int, R: int, team: int | None = None, ncta: int 
     W = ncta * GEMV_WARPS
     if U >= 0.8 * W:
         return 1
-    # the smallest team that puts at least half of the grid's warps to work, with slices of two ring stages or
-    # more (measured on the 27B layer: down with T = 2 / 8 / 16 -> chain of 90.9 / 91.8 / 95.9 us)
-    best = 1
-    for T in (2, 4, 8, 16):
-        if T > GEMV_WARPS or KB < 16 * T:
+    fixed = 6
+    best, best_cost = 1, -(-U // W) * (KB + fixed)
+    for T in range(2, GEMV_WARPS + 1):
+        if KB < 8 * T:                       # a slice shorter than one ring stage is all overhead
             break
-        best = T
-        if U * T >= 0.5 * W:
-            break
+        teams = (GEMV_WARPS // T) * ncta
+        cost = -(-U // teams) * (-(-KB // T) + fixed)
+        if cost < 0.97 * best_cost:          # near-ties go to the smaller team
+            best, best_cost = T, cost
     return best
 
 
