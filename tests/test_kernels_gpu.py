@@ -853,3 +853,55 @@ def test_gdn_chunked_matches_recurrence(dk, hk, hv, state_bf16):
         close(out[t0:t1], ref.reshape(Tn, vd), 3e-2)
         close(state[slot].transpose(-1, -2), Sn.transpose(-1, -2), 1e-2)
     assert torch.equal(state[1], state0[1]) and torch.equal(cs[1], cs0[1])      # an unused slot stays untouched
+
+
+@pytest.mark.parametrize("M,N,tp", [(40, 384, 2), (300, 5120, 4), (17, 1024, 8)])
+def test_ar_rows_fused_allreduce_residual_norm_quant(M, N, tp):
+    """The many-row all-reduce kernel with emulated ranks on one GPU (plain peer loads; the flags of all ranks are set
+    beforehand, so nothing waits): sum of the ranks' bf16 partials + residual, then the consumer's prologue, against
+    torch and against the stand-alone quantisation kernel run on the reduced rows."""
+    F = _F()
+    torch.manual_seed(11)
+
+    class Comm:
+        pass
+    comm = Comm()
+    comm.tp, comm.rank = tp, 1
+    parts = [(torch.randn(M, N, device="cuda") * 2).to(BF16) for _ in range(tp)]
+    flags = torch.full((64,), 7 * 65536 + 500, dtype=torch.int32, device="cuda")      # already ahead of every tag used here
+    ctrl = torch.tensor([7, 0, 0, 0], dtype=torch.int32, device="cuda")               # step counter 7, status 0
+    comm.part_ptrs = [[p.data_ptr() for p in parts], [p.data_ptr() for p in parts]]
+    comm.part_mc = [0, 0]
+    comm.flag_ptrs = [flags.data_ptr()] * tp
+    comm.step_ptr, comm.status_ptr, comm.timeout_ns = ctrl.data_ptr(), ctrl.data_ptr() + 4, 10 ** 9
+    resid = torch.randn(M, N, device="cuda").to(BF16)
+    nw = (torch.randn(N, device="cuda") * 0.1).to(BF16)
+    want_h = (sum(p.float() for p in parts) + resid.float()).to(BF16)
+    # mode 0
+    h = torch.zeros(M, N, dtype=BF16, device="cuda")
+    F.ar_rows(comm, 0, M, N, resid, h, order=3)
+    torch.cuda.synchronize()
+    assert torch.equal(h, want_h) and int(ctrl[1]) == 0
+    # mode 1: limbs of RMSNorm(h) == what the stand-alone kernel makes of the reduced rows
+    h1 = torch.zeros_like(h)
+    limbs = F.Limbs(M, N, "cuda")
+    F.ar_rows(comm, 1, M, N, resid, h1, order=4, mode=F.AR_LIMBS, norm_w=nw, limbs=limbs)
+    ref = F.quant_rows(want_h, norm_w=nw)
+    torch.cuda.synchronize()
+    assert torch.equal(h1, want_h)
+    assert torch.equal(limbs.hi, ref.hi) and torch.equal(limbs.lo, ref.lo) and torch.equal(limbs.scale, ref.scale)
+    # mode 2: normalised bf16 rows
+    h2 = torch.zeros_like(h)
+    xn = torch.zeros(M, N, dtype=BF16, device="cuda")
+    F.ar_rows(comm, 0, M, N, resid, h2, order=5, mode=F.AR_BF16, norm_w=nw, xn=xn)
+    torch.cuda.synchronize()
+    hf = want_h.float()
+    want_n = (hf * torch.rsqrt((hf * hf).mean(-1, keepdim=True) + 1e-6) * (1 + nw.float())).to(BF16)
+    torch.testing.assert_close(xn.float(), want_n.float(), rtol=1e-2, atol=1e-2)
+    # a flag that never arrives: the wait runs out, the status word says so, the context survives
+    flags.zero_()
+    comm.timeout_ns = 2 * 10 ** 6
+    F.ar_rows(comm, 0, min(M, 4), N, resid, h2, order=6)
+    torch.cuda.synchronize()
+    assert int(ctrl[1]) & 1 == 1
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0

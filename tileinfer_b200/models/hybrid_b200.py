@@ -74,7 +74,12 @@ class _ModelBase:
         self.peer = None
         if tp > 1 and self.fused:
             from ..parallel.symm_mem import PeerComm
-            self.peer = PeerComm(comm, self.H, m_cap=64)
+            rows = 0
+            if config is not None:
+                rows = max(int(config.max_num_batched_tokens), int(config.max_num_seqs), 64)
+            self.peer = PeerComm(comm, self.H, m_cap=64, ar_rows=rows)
+        self._ar_pending = None            # a many-row all-reduce whose result nobody has consumed yet
+        self.ar_min_rows = int(os.environ.get("TI_AR_MIN_ROWS", "16"))   # more rows than this: GEMM + fused all-reduce
         self.ctrl = self.peer.ctrl if self.peer is not None else torch.zeros(4, dtype=torch.int32, device=dev)
         self.step_ptr = self.ctrl.data_ptr()
         self.block_size = 16
@@ -308,6 +313,12 @@ class _StepMixin:
 
     def _gemv(self, W: LinearW, x, out, M, *, xmode, epi, norm_w=None, resid=None, ldo=None):
         """y = x W^T in row chunks of 16; counts launches; assigns collective order numbers."""
+        pend = self._ar_pending
+        if pend is not None:
+            if (pend["out"].data_ptr() == x.data_ptr() and pend["M"] == M and xmode == XNORM and M > self.gemm_min_rows
+                    and (W.wt == F.W_BF16 or epi != EPI_F32) and x.stride(0) == W.K):
+                return self._gemm_after_ar(W, x, out, M, epi=epi, norm_w=norm_w, resid=resid)
+            self._ar_flush()
         if M > self.gemm_min_rows and (W.wt == F.W_BF16 or epi != EPI_F32) and not (epi == EPI_ROWPAR and self.tp > 1):
             return self._gemm(W, x, out, M, epi=epi, norm_w=norm_w if xmode == XNORM else None, resid=resid)
         step = F.max_rows(W.wt, xmode, W.K)
@@ -338,6 +349,33 @@ class _StepMixin:
                 F.gemv_launch(p, W.wt, xmode, epi)
                 self._launches += 1
 
+    def _gemm_after_ar(self, W: LinearW, x, out, M, *, epi, norm_w, resid):
+        """The product that consumes an all-reduced row-parallel output: ONE kernel sums the ranks' partials over
+        NVLink, adds the residual, writes the new residual stream `x`, and runs this product's prologue (RMSNorm,
+        then int8 limb planes or bf16) on the rows while they are still in registers; then the tcgen05 GEMM."""
+        pend, self._ar_pending = self._ar_pending, None
+        self._flush()
+        gepi = {EPI_STORE: F.GEPI_STORE, EPI_SWIGLU: F.GEPI_SWIGLU, EPI_ROWPAR: F.GEPI_ROWPAR, EPI_F32: F.GEPI_F32}[epi]
+        r = None if resid is None else resid[:M]
+        if W.wt == F.W_INT8:
+            limbs = F.Limbs(M, W.K, self.dev)
+            F.ar_rows(self.peer, pend["parity"], M, W.K, pend["resid"], x, order=pend["order"], mode=F.AR_LIMBS,
+                      norm_w=norm_w, limbs=limbs, eps=self.cfg.rms_eps)
+            F.gemm_w8a16(W, limbs, out=out[:M], epi=gepi, resid=r)
+        else:
+            xn = torch.empty(M, W.K, dtype=BF16, device=self.dev)
+            F.ar_rows(self.peer, pend["parity"], M, W.K, pend["resid"], x, order=pend["order"], mode=F.AR_BF16,
+                      norm_w=norm_w, xn=xn, eps=self.cfg.rms_eps)
+            F.gemm_bf16(W, xn, out=out[:M], epi=gepi, resid=r)
+        self._launches += 2
+
+    def _ar_flush(self):
+        """Completes a pending many-row all-reduce whose consumer is not a normalising GEMM (end of the step)."""
+        pend, self._ar_pending = self._ar_pending, None
+        if pend is not None:
+            F.ar_rows(self.peer, pend["parity"], pend["M"], self.H, pend["resid"], pend["out"], order=pend["order"])
+            self._launches += 1
+
     def _flush(self):
         if self._pending:
             F.gemv_chain_launch(self._pending, self._pending_wt)
@@ -349,6 +387,17 @@ class _StepMixin:
         # Under tensor parallelism, steps of up to m_cap rows (every decode bucket, so everything a CUDA graph
         # captures) keep the fused peer-memory all-reduce of the GEMV; only larger (eager prefill) steps take the
         # tcgen05 GEMM followed by an NCCL all-reduce.
+        if self.tp > 1 and self.peer is not None and M > max(self.ar_min_rows, self.gemm_min_rows):
+            # many rows under tensor parallelism: the tcgen05 GEMM stores this rank's partial sums (bf16) straight
+            # into its symmetric buffer; the all-reduce, the residual add and the consumer's prologue are one kernel
+            # launched by whoever consumes `out` (see _gemm_after_ar)
+            self._ar_flush()
+            order = self._order
+            self._order += 1
+            part = self.peer.part_view(order & 1, M)
+            self._gemm(W, x, part, M, epi=EPI_STORE)
+            self._ar_pending = {"parity": order & 1, "resid": resid[:M], "out": out, "M": M, "order": order}
+            return
         fused_cap = self.peer.m_cap if self.peer is not None else self.gemm_min_rows
         if self.tp > 1 and M > max(fused_cap, self.gemm_min_rows):
             # prefill under tensor parallelism: tcgen05 GEMM to a bf16 partial, NCCL all-reduce, residual add
@@ -445,6 +494,7 @@ class _StepMixin:
             self._rowpar(L.down, x.act, cur, nxt, T)
             cur, nxt = nxt, cur
         self._flush()
+        self._ar_flush()
         return cur
 
 

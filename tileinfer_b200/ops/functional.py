@@ -75,6 +75,14 @@ class TopkParams(ctypes.Structure):
                 ("vocab_start", _I), ("tp", _I), ("rank", _I), ("order", _I), ("m_cap", _I)]
 
 
+class ArRowsParams(ctypes.Structure):
+    _fields_ = [("part_peer", ctypes.c_uint64 * MAX_RANKS), ("part_mc", ctypes.c_uint64),
+                ("flag_peer", ctypes.c_uint64 * MAX_RANKS), ("resid", _P), ("h_out", _P), ("norm_w", _P), ("xh", _P),
+                ("xl", _P), ("xscale", _P), ("xn", _P), ("step_ptr", _P), ("status", _P),
+                ("timeout_ns", ctypes.c_ulonglong), ("M", _I), ("N", _I), ("tp", _I), ("rank", _I), ("order", _I),
+                ("mode", _I), ("eps", _F)]
+
+
 class EditParams(ctypes.Structure):
     _fields_ = [("logits", _P), ("row_slot", _P), ("add_rows", _P), ("add_valid", _P), ("pen_ids", _P), ("pen_cnt", _P),
                 ("pen_rp", _P), ("M", _I), ("V", _I), ("ld", _I), ("pen_cap", _I), ("chunk", _I)]
@@ -85,6 +93,8 @@ class SampleParams(ctypes.Structure):
                 ("out_tok", _P), ("status_src", _P), ("M", _I), ("n_cand", _I)]
 
 
+_l.register("ti_ar_rows_params_size", _I, [])
+_l.register("ti_ar_rows", _I, [ctypes.POINTER(ArRowsParams), _P])
 _l.register("ti_edit_params_size", _I, [])
 _l.register("ti_sample_params_size", _I, [])
 _l.register("ti_logits_edit", _I, [ctypes.POINTER(EditParams), _P])
@@ -127,7 +137,8 @@ def L():
     if not _checked:
         for fn, st in (("ti_gdn_params_size", GdnParams), ("ti_gdn_chunk_params_size", GdnChunkParams), ("ti_qkv_prep_params_size", QkvPrepParams),
                        ("ti_attn_params_size", AttnParams), ("ti_topk_params_size", TopkParams),
-                       ("ti_edit_params_size", EditParams), ("ti_sample_params_size", SampleParams)):
+                       ("ti_edit_params_size", EditParams), ("ti_sample_params_size", SampleParams),
+                       ("ti_ar_rows_params_size", ArRowsParams)):
             if getattr(lib, fn)() != ctypes.sizeof(st):
                 raise RuntimeError(f"{st.__name__} layout mismatch between Python and CUDA")
         _checked = True
@@ -481,6 +492,28 @@ def attn_prefill(q, kcache, vcache, num_blocks, block_tables, positions, tiles, 
     check(L().ti_attn_prefill(ptr(q), q.shape[0], ptr(kcache), ptr(vcache), num_blocks, ptr(block_tables), ptr(positions),
                               ptr(tiles[0]), ptr(tiles[1]), ptr(tiles[2]), n, ptr(gate_src), ptr(out), hq, hkv,
                               max_blocks, ld, scale, D, status_ptr(), stream()), "ti_attn_prefill")
+
+
+AR_NONE, AR_LIMBS, AR_BF16 = 0, 1, 2
+
+
+def ar_rows(comm, parity: int, M: int, N: int, resid, h_out, *, order: int, mode: int = AR_NONE, norm_w=None,
+            limbs: "Limbs" = None, xn=None, eps: float = 1e-6):
+    """All-reduce of the row-parallel partials in `comm`'s symmetric buffer `parity` + residual -> h_out, fused with
+    the RMSNorm / activation-quantisation prologue of the consuming product (ops/csrc/fused_ar.cu)."""
+    p = ArRowsParams()
+    for r in range(comm.tp):
+        p.part_peer[r] = comm.part_ptrs[parity][r]
+        p.flag_peer[r] = comm.flag_ptrs[r]
+    p.part_mc = comm.part_mc[parity]
+    p.resid, p.h_out, p.norm_w = ptr(resid), ptr(h_out), ptr(norm_w)
+    if mode == AR_LIMBS:
+        p.xh, p.xl, p.xscale = ptr(limbs.hi), ptr(limbs.lo), ptr(limbs.scale)
+    elif mode == AR_BF16:
+        p.xn = ptr(xn)
+    p.step_ptr, p.status, p.timeout_ns = comm.step_ptr, comm.status_ptr, comm.timeout_ns
+    p.M, p.N, p.tp, p.rank, p.order, p.mode, p.eps = M, N, comm.tp, comm.rank, order, mode, eps
+    check(L().ti_ar_rows(ctypes.byref(p), stream()), "ti_ar_rows")
 
 
 def logits_edit(p: EditParams):

@@ -1,5 +1,15 @@
 """Symmetric peer buffers for the fused tensor-parallel kernels.
 
+Two allocators sit behind `PeerComm`:
+
+* `torch.distributed._symmetric_memory` (driver VMM allocations exchanged between the ranks and, where the
+  GPUs and the driver support it, bound to an NVLS multicast object): gives a pointer table of every rank's
+  buffer plus ONE multicast address through which `multimem.ld_reduce` sums all ranks' copies inside NVSwitch.
+  Used for the large partial-sum buffers of the many-row all-reduce (ops/csrc/fused_ar.cu).
+* plain `cudaMalloc` + CUDA IPC handles (no multicast): the packet buffers of the decode path, and the fallback
+  for everything when NVLS is switched off (`TI_NVLS=0` or `NCCL_NVLS_ENABLE=0`) or unavailable.  Processes that
+  may lose a peer must run in this mode: memory bound to a multicast object must not outlive a rank that dies.
+
 Each rank owns (a) a packet buffer for the row-parallel all-reduce, laid out
 [2 slots][tp sources][m_cap rows][N/2] 16-byte packet pairs, (b) a packet buffer for the top-k
 candidate exchange [2][tp][m_cap][64] and (c) a step counter and a status word.  The buffers are
@@ -13,14 +23,21 @@ The reference has no counterpart; its communicator is NCCL only (engine/parallel
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
 from ..ops import functional as F
 
 
+def nvls_wanted() -> bool:
+    """Multicast (NVLS) data plane for this package's own kernels: on unless TI_NVLS=0 or NCCL's own switch is off
+    (the tests in which a rank leaves run everything, NCCL included, without NVLS)."""
+    return os.environ.get("TI_NVLS", "1") != "0" and os.environ.get("NCCL_NVLS_ENABLE", "1") != "0"
+
+
 class PeerComm:
-    def __init__(self, comm, hidden: int, m_cap: int = 64, timeout_s: float = 2.0, device=None):
+    def __init__(self, comm, hidden: int, m_cap: int = 64, timeout_s: float = 2.0, device=None, ar_rows: int = 0):
         self.comm = comm
         self.tp, self.rank = comm.world_size, comm.rank
         self.m_cap = m_cap
@@ -37,6 +54,59 @@ class PeerComm:
         self._mapped = []
         self.ll_ptrs = self._exchange(self.ll_bytes)
         self.cand_ptrs = self._exchange(self.cand_bytes)
+        # many-row all-reduce: two alternating partial-sum buffers [ar_rows, hidden] bf16 and one flag per source rank
+        self.ar_rows = ar_rows
+        self.part_ptrs, self.part_mc, self._symm_keep = [None, None], [0, 0], []
+        self.flag_ptrs = self._exchange(256)
+        self.nvls = False
+        if ar_rows > 0 and self.tp > 1:
+            nbytes = ar_rows * hidden * 2
+            for i in range(2):
+                got = self._symm_alloc(nbytes) if nvls_wanted() else None
+                if got is None:
+                    self.part_ptrs[i], self.part_mc[i] = self._exchange(nbytes), 0
+                else:
+                    self.part_ptrs[i], self.part_mc[i] = got
+            self.nvls = all(mc != 0 for mc in self.part_mc)
+
+    def _symm_alloc(self, nbytes: int):
+        """(pointer table, multicast address) of a torch symmetric-memory allocation, or None when that allocator or
+        multicast is not available here (all ranks then take the same fallback: the decision is agreed on)."""
+        import torch.distributed as dist
+        ok, out = 1, None
+        try:
+            import torch.distributed._symmetric_memory as symm
+            t = symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+            hdl = symm.rendezvous(t, dist.group.WORLD.group_name)
+            mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+            ptrs = [int(x) for x in hdl.buffer_ptrs]
+            if mc == 0 or len(ptrs) != self.tp:
+                ok = 0
+            else:
+                t.zero_()
+                out = (t, hdl, ptrs, mc)
+        except Exception:
+            ok = 0
+        flag = torch.tensor([ok], device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0 or out is None:
+            return None
+        self._symm_keep.append(out[:2])
+        torch.cuda.synchronize()
+        self.comm.barrier()
+        return out[2], out[3]
+
+    def part_view(self, parity: int, rows: int) -> torch.Tensor:
+        """This rank's partial-sum buffer `parity` as a [rows, hidden] bf16 tensor (the GEMM epilogue stores into it)."""
+        assert rows <= self.ar_rows, f"{rows} rows exceed the all-reduce buffers ({self.ar_rows}); raise max_num_batched_tokens"
+        key = ("part", parity)
+        base = getattr(self, "_views", None)
+        if base is None:
+            base = self._views = {}
+        if key not in base:
+            base[key] = _tensor_from_ptr(self.part_ptrs[parity][self.rank], self.ar_rows * self.hidden, torch.bfloat16,
+                                         self.device).view(self.ar_rows, self.hidden)
+        return base[key][:rows]
 
     def _exchange(self, nbytes: int) -> list:
         lib = F.L()
@@ -107,6 +177,18 @@ class PeerComm:
         for p in self._local:
             lib.ti_symm_free(ctypes.c_void_p(p))
         self._local = []
+
+
+class _PtrOwner:
+    """Exposes raw device memory through __cuda_array_interface__ so that torch can wrap it without copying."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def _tensor_from_ptr(ptr: int, numel: int, dtype, device) -> torch.Tensor:
+    nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+    return torch.as_tensor(_PtrOwner(ptr, nbytes), device=device).view(dtype)
 
 
 class LocalRanks:
