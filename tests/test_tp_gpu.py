@@ -13,8 +13,10 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(tp, fused, port):
-    env = dict(os.environ, TI_TEST_FUSED="1" if fused else "0", NCCL_NVLS_ENABLE="0")
+def _run(tp, fused, port, nvls=False):
+    # NVLS (NCCL's and this package's own multimem loads) stays off except in the one test that is about it
+    env = dict(os.environ, TI_TEST_FUSED="1" if fused else "0", NCCL_NVLS_ENABLE="1" if nvls else "0",
+               TI_NVLS="1" if nvls else "0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(tp),
                         "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_gpu_worker.py")],
                        capture_output=True, text=True, env=env, timeout=240)
@@ -23,16 +25,17 @@ def _run(tp, fused, port):
     return json.loads(line[len("TP_RESULT "):])
 
 
-def _near_greedy(tokens, prompt, slack=0.08):
-    from tileinfer_b200.models.config import TINY_HYBRID_TP
+def _near_greedy(tokens, prompt, slack=0.08, tp=2):
+    from tileinfer_b200.models.config import TINY_HYBRID_TP, TINY_HYBRID_TP8
     from tileinfer_b200.models.reference_cpu import naive_logits
     from tileinfer_b200.models.weights import RandomWeights
-    lg = naive_logits(TINY_HYBRID_TP, RandomWeights(TINY_HYBRID_TP, 0), list(prompt) + list(tokens), quant="w8a16")
+    cfg = TINY_HYBRID_TP8 if tp == 8 else TINY_HYBRID_TP
+    lg = naive_logits(cfg, RandomWeights(cfg, 0), list(prompt) + list(tokens), quant="w8a16")
     worst = max(float(lg[len(prompt) - 1 + i].max() - lg[len(prompt) - 1 + i][t]) for i, t in enumerate(tokens))
     assert worst <= slack, f"token off the oracle arg-max by {worst}"
 
 
-@pytest.mark.parametrize("tp", [2, 4])
+@pytest.mark.parametrize("tp", [2, 4, 8])
 def test_fused_tp_matches_oracle_and_all_ranks_agree(tp):
     if torch.cuda.device_count() < tp:
         pytest.skip(f"needs {tp} GPUs")
@@ -43,6 +46,21 @@ def test_fused_tp_matches_oracle_and_all_ranks_agree(tp):
     assert ranks[0]["graph_launches"] > 0 and all(r["scrubs"] >= 2 for r in ranks)
     for p, o in zip(res["prompts"], ranks[0]["greedy"]):
         assert len(o) == 12
+        _near_greedy(o, p, tp=tp)
+
+
+def test_fused_tp_with_nvls_multimem_reduction():
+    """The many-row all-reduce reading the partial sums through the NVLS multicast window (multimem.ld_reduce):
+    same tokens as the oracle, all ranks agree.  Nobody leaves in this test."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    res = _run(2, True, 29551, nvls=True)
+    ranks = res["ranks"]
+    if not all(r.get("nvls") for r in ranks):
+        pytest.skip("no NVLS multicast binding on this machine (torch symmetric memory reported none)")
+    assert all(r["status"] == 0 for r in ranks)
+    assert all(r["greedy"] == ranks[0]["greedy"] and r["sampled"] == ranks[0]["sampled"] for r in ranks)
+    for p, o in zip(res["prompts"], ranks[0]["greedy"]):
         _near_greedy(o, p)
 
 

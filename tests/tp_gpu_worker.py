@@ -55,7 +55,8 @@ def main():
     faulthandler.dump_traceback_later(int(os.environ.get("TI_TEST_WATCHDOG_S", "150")), exit=True)   # a stuck rank says where
     fused = os.environ.get("TI_TEST_FUSED", "1") == "1"
     tp = int(os.environ["WORLD_SIZE"])
-    llm = LLM("preset:tiny-hybrid-tp", quantization="w8a16", tp_size=tp, num_kvcache_blocks=128, max_num_seqs=8,
+    preset = "preset:tiny-hybrid-tp8" if tp == 8 else "preset:tiny-hybrid-tp"
+    llm = LLM(preset, quantization="w8a16", tp_size=tp, num_kvcache_blocks=128, max_num_seqs=8,
               max_model_len=512, max_prefill_chunk_tokens=32, fused_collectives=fused, nccl_timeout=120)
     peer = llm.model_runner.model.peer
     if peer is not None:
@@ -65,6 +66,7 @@ def main():
     sampled = llm.generate_token_ids(prompts[:2], SamplingParams(temperature=0.8, top_k=20, max_tokens=8, ignore_eos=True))
     status = llm.model_runner.model.peer_status()
     mine = {"greedy": greedy, "sampled": sampled, "status": status, "scrubs": getattr(peer, "scrubs", 0),
+            "nvls": bool(getattr(peer, "nvls", False)),
             "graph_launches": llm.model_runner.model.launches_per_decode_step}
     box = [None] * tp
     dist.all_gather_object(box, mine)

@@ -131,6 +131,14 @@ TINY_HYBRID_TP = replace(
     hidden_size=512,
 )
 
+# every head count divisible by 8 (except the 2 KV heads, which are then replicated): the 8-rank tests
+TINY_HYBRID_TP8 = replace(
+    TINY_HYBRID_TP,
+    name="tiny-hybrid-tp8",
+    gdn_num_k_heads=8,
+    gdn_num_v_heads=16,
+)
+
 QWEN36_27B = ModelConfig(
     name="qwen3.6-27b",
     vocab_size=248320,
@@ -155,7 +163,7 @@ QWEN36_27B = ModelConfig(
 # The 27B layer shapes with only 8 layers: used to test full-size kernels quickly.
 QWEN36_27B_8L = replace(QWEN36_27B, name="qwen3.6-27b-8l", num_layers=8, layer_types=_pattern(8))
 
-PRESETS = {c.name: c for c in (TINY_HYBRID, TINY_HYBRID_TP, QWEN36_27B, QWEN36_27B_8L)}
+PRESETS = {c.name: c for c in (TINY_HYBRID, TINY_HYBRID_TP, TINY_HYBRID_TP8, QWEN36_27B, QWEN36_27B_8L)}
 
 
 def get_preset(name: str) -> ModelConfig:
