@@ -32,50 +32,131 @@ struct TopkParams {
   int tp, rank, order, m_cap;
 };
 
-struct Best { float v; int i; };
-TI_DEVICE bool better(const Best& a, const Best& b) { return a.v > b.v || (a.v == b.v && a.i < b.i); }
-
-TI_DEVICE Best block_argmax(Best b, Best* sm) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    Best other{__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
-    if (better(other, b)) b = other;
-  }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  if (lane == 0) sm[warp] = b;
-  __syncthreads();
-  Best r = sm[0];
-  for (int w = 1; w < nw; ++w)
-    if (better(sm[w], r)) r = sm[w];
-  __syncthreads();
-  return r;
-}
-
 constexpr int kNoIdx = 0x7fffffff;
 
+// Order-preserving key of a float (larger value -> larger key); 0 is reserved for "no element".
+TI_DEVICE uint32_t float_key(float v) {
+  const uint32_t u = __float_as_uint(v);
+  const uint32_t k = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  return k == 0u ? 1u : k;
+}
+
+// Block-wide top-k (k <= 64) of the EPT elements each of the 256 threads holds, by radix selection: four passes of
+// 8 bits narrow down the key of the k-th largest element (a 256-bin histogram in shared memory per pass), then the
+// elements above it are compacted, ties at the threshold are taken in position order (the smallest token ids), and
+// the k winners are ranked (value descending, token id ascending) and written out.  A dozen block barriers in all,
+// where extracting the maxima one by one cost two barriers per extracted element.
+// Element e of thread t sits at position t + 256 e; positions are in ascending token-id order among equal values.
+struct TopkSmem {
+  int hist[256];
+  int sel_bin, need, cnt, base;
+  int warp_cnt[8];
+  float cv[64];
+  int ci[64];
+};
+
 template <int EPT>
-TI_DEVICE void select_topk(float (&val)[EPT], int (&idx)[EPT], int k, float* out_v, int* out_i, Best* sm) {
-  for (int j = 0; j < k; ++j) {
-    Best b{-INFINITY, kNoIdx};
+TI_DEVICE void select_topk(float (&val)[EPT], int (&idx)[EPT], int k, float* out_v, int* out_i, TopkSmem& sm) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint32_t key[EPT];
 #pragma unroll
-    for (int e = 0; e < EPT; ++e) {
-      Best c{val[e], idx[e]};
-      if (idx[e] != kNoIdx && better(c, b)) b = c;
-    }
-    const Best w = block_argmax(b, sm);
+  for (int e = 0; e < EPT; ++e) key[e] = idx[e] == kNoIdx ? 0u : float_key(val[e]);
+  uint32_t prefix = 0u, mask = 0u;
+  int need = k;
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    sm.hist[tid] = 0;
+    __syncthreads();
 #pragma unroll
     for (int e = 0; e < EPT; ++e)
-      if (idx[e] == w.i) idx[e] = kNoIdx;          // taken
-    if (threadIdx.x == 0) {
-      out_v[j] = w.i == kNoIdx ? -INFINITY : w.v;
-      out_i[j] = w.i == kNoIdx ? -1 : w.i;
+      if ((key[e] & mask) == prefix) atomicAdd(&sm.hist[(key[e] >> shift) & 255u], 1);
+    __syncthreads();
+    if (warp == 0) {
+      // lane l owns bins 255 - 8l .. 248 - 8l; find the bin in which the count from the top reaches `need`
+      int c[8], tot = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        c[j] = sm.hist[255 - 8 * lane - j];
+        tot += c[j];
+      }
+      int incl = tot;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      const int excl = incl - tot;                         // elements in the bins above this lane's
+      if (excl < need && incl >= need) {
+        int run = excl;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (run < need && run + c[j] >= need) {
+            sm.sel_bin = 255 - 8 * lane - j;
+            sm.need = need - run;
+          }
+          run += c[j];
+        }
+      }
     }
+    __syncthreads();
+    prefix |= (uint32_t)sm.sel_bin << shift;
+    mask |= 0xFFu << shift;
+    need = sm.need;
+    __syncthreads();
   }
+  // prefix = key of the k-th largest element; `need` of the elements equal to it are taken, everything above it is
+  const int n_gt = k - need;
+  if (tid == 0) { sm.cnt = 0; sm.base = 0; }
+  __syncthreads();
+#pragma unroll
+  for (int e = 0; e < EPT; ++e)
+    if (key[e] > prefix) {
+      const int pos = atomicAdd(&sm.cnt, 1);
+      sm.cv[pos] = val[e];
+      sm.ci[pos] = idx[e];
+    }
+  // ties in position order: element e of thread t is at position t + 256 e
+  for (int e = 0; e < EPT; ++e) {
+    const bool tie = key[e] == prefix;
+    const unsigned bal = __ballot_sync(0xffffffffu, tie);
+    if (lane == 0) sm.warp_cnt[warp] = __popc(bal);
+    __syncthreads();
+    int before = sm.base, total = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      if (w < warp) before += sm.warp_cnt[w];
+      total += sm.warp_cnt[w];
+    }
+    const int rank = before + __popc(bal & ((1u << lane) - 1u));
+    if (tie && rank < need) {
+      sm.cv[n_gt + rank] = key[e] == 0u ? -INFINITY : val[e];
+      sm.ci[n_gt + rank] = key[e] == 0u ? -1 : idx[e];
+    }
+    __syncthreads();
+    if (tid == 0) sm.base += total;
+    __syncthreads();
+    if (sm.base >= need) break;                            // uniform: every thread reads the same value
+  }
+  __syncthreads();
+  // rank the k winners: value descending, then token id ascending (empty entries, id -1, last)
+  if (tid < k) {
+    const float v = sm.cv[tid];
+    const unsigned id = (unsigned)sm.ci[tid];
+    int rank = 0;
+    for (int j = 0; j < k; ++j) {
+      const float vj = sm.cv[j];
+      const unsigned ij = (unsigned)sm.ci[j];
+      rank += (vj > v || (vj == v && (ij < id || (ij == id && j < tid)))) ? 1 : 0;
+    }
+    out_v[rank] = v;
+    out_i[rank] = (int)id;
+  }
+  __syncthreads();
 }
 
 __global__ void __launch_bounds__(256) topk_stage1_kernel(const __grid_constant__ TopkParams p) {
   constexpr int EPT = 16;
-  __shared__ Best sm[8];
+  __shared__ TopkSmem sm;
   const int m = blockIdx.x, c = blockIdx.y;
   pdl_trigger();
   pdl_wait();
@@ -95,7 +176,7 @@ __global__ void __launch_bounds__(256) topk_stage1_kernel(const __grid_constant_
 
 __global__ void __launch_bounds__(256) topk_stage2_kernel(const __grid_constant__ TopkParams p) {
   constexpr int EPT = 32;
-  __shared__ Best sm[8];
+  __shared__ TopkSmem sm;
   __shared__ float fin_v[64];
   __shared__ int fin_i[64];
   const int m = blockIdx.x;
