@@ -116,6 +116,7 @@ TI_DEVICE void select_topk(float (&val)[EPT], int (&idx)[EPT], int k, float* out
       sm.ci[pos] = idx[e];
     }
   // ties in position order: element e of thread t is at position t + 256 e
+#pragma unroll
   for (int e = 0; e < EPT; ++e) {
     const bool tie = key[e] == prefix;
     const unsigned bal = __ballot_sync(0xffffffffu, tie);
