@@ -35,21 +35,29 @@ def main():
     ap.add_argument("--chunk", type=int, default=2048)
     ap.add_argument("--swap-gb", type=float, default=8.0)
     ap.add_argument("--quantization", default="w8a16")
+    ap.add_argument("--prefix-share", type=float, default=0.5, help="fraction of the requests that start with the shared prefix")
+    ap.add_argument("--kv-blocks", type=int, default=-1, help="size of the KV pool in 16-token pages (default: from free memory); "
+                                                               "a small pool forces preemption by swapping")
     args = ap.parse_args()
 
     llm = LLM(args.model, tp_size=args.tp, quantization=args.quantization, max_num_seqs=min(64, args.requests),
               max_model_len=args.max_prompt + args.max_tokens + 16, max_prefill_chunk_tokens=args.chunk,
               max_num_batched_tokens=args.chunk + 64, num_scheduler_steps=args.scheduler_steps,
-              swap_space_bytes=int(args.swap_gb * (1 << 30)), gpu_memory_utilization=0.85)
+              swap_space_bytes=int(args.swap_gb * (1 << 30)), gpu_memory_utilization=0.85,
+              num_kvcache_blocks=args.kv_blocks)
     vocab = llm.config.model_config.vocab_size
     cuda = torch.cuda.is_available() and llm.config.device != "cpu"
     sync = torch.cuda.synchronize if cuda else (lambda: None)
     g = torch.Generator().manual_seed(7)
     prefix = torch.randint(0, vocab - 1, (args.prefix,), generator=g).tolist()
     prompts = []
-    for _ in range(args.requests):
+    for i in range(args.requests):
         n = int(torch.randint(args.min_prompt, args.max_prompt + 1, (1,), generator=g))
-        prompts.append(prefix + torch.randint(0, vocab - 1, (max(1, n - args.prefix),), generator=g).tolist())
+        shared = (i % 100) < int(100 * args.prefix_share)       # e.g. every other request for 0.5
+        if args.prefix_share == 0.5:
+            shared = i % 2 == 0
+        head = prefix if shared else torch.randint(0, vocab - 1, (args.prefix,), generator=g).tolist()
+        prompts.append(head + torch.randint(0, vocab - 1, (max(1, n - args.prefix),), generator=g).tolist())
     sp = SamplingParams(temperature=0.6, top_k=50, max_tokens=args.max_tokens, ignore_eos=True)
     # warm-up: compiles nothing, but touches every graph bucket's first replay and the allocator
     llm.generate_token_ids([prompts[0][:64]], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
@@ -74,7 +82,7 @@ def main():
                           "prompt_tokens": sum(len(p) for p in prompts),
                           "total_tok_s": round((gen + sum(len(p) for p in prompts)) / dt, 1),
                           "config": {"model": args.model, "requests": args.requests, "prompt": [args.min_prompt, args.max_prompt],
-                                     "shared_prefix": args.prefix, "max_tokens": args.max_tokens, "temperature": 0.6, "top_k": 50,
+                                     "shared_prefix": args.prefix, "prefix_share": args.prefix_share, "kv_blocks": llm.config.num_kvcache_blocks, "max_tokens": args.max_tokens, "temperature": 0.6, "top_k": 50,
                                      "scheduler_steps": args.scheduler_steps, "chunk": args.chunk, "parallelism": f"tp{args.tp}"},
                           "stats": {k: st.get(k) for k in keys}}), flush=True)
     if args.tp > 1:

@@ -1,9 +1,13 @@
 """Decode-step driver for profilers: builds the model, captures the CUDA-graph decode step for one
-batch size and replays it.  Meant to be run as is (prints ms/step) or under
-`ncu --metrics gpu__time_duration.sum --clock-control none` for a per-kernel launch list
-(the reference's counterpart is tests/profile_decode.py, a torch.profiler wrapper).
+batch size and replays it.  Meant to be run as is (prints ms/step), under
+`ncu --metrics gpu__time_duration.sum --clock-control none` for a per-kernel launch list, or with
+`--torch-profiler`, which runs eager decode steps under torch.profiler, prints the kernel time per category
+(GEMV / GEMM / attention / DeltaNet / sampling / communication / ...) and the top kernels, and with `--trace FILE`
+writes a Chrome trace.  That mode is the counterpart of the reference's tests/profile_decode.py:71-114,188-191.
+`TI_NVTX=1` adds an NVTX range per layer and block for external timeline tools.
 
     python benchmarks/profile_decode.py --model preset:qwen3.6-27b-8l --batch 1 --ctx 256 --steps 3
+    python benchmarks/profile_decode.py --model preset:qwen3.6-27b-8l --torch-profiler --trace gpurun_out/decode_trace.json
 """
 import argparse
 import os
@@ -46,6 +50,8 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--quant", default="w8a16")
     ap.add_argument("--prefill", type=int, default=0, help="run eager prefill forwards of this many tokens instead")
+    ap.add_argument("--torch-profiler", action="store_true", help="category buckets + top kernels through torch.profiler")
+    ap.add_argument("--trace", default=None, help="with --torch-profiler: write a Chrome trace here")
     args = ap.parse_args()
     cfg = get_preset(args.model)
     torch.cuda.set_device(0)
@@ -62,6 +68,18 @@ def main():
                   tables, torch.tensor([t[pos // 16] * 16 + pos % 16 for t in tables]), list(range(B)))
     m._decode_graph_step(batch, 1)
     torch.cuda.synchronize()
+    if args.torch_profiler:
+        from tileinfer_b200.utils.trace import format_profile, profile_call
+
+        def steps():
+            for _ in range(args.steps):
+                h = m.forward(batch)                # eager: every kernel shows up by name (a graph replay is one node)
+                m.logits(h)
+        steps()
+        res = profile_call(steps, trace_path=args.trace)
+        print(f"model={cfg.name} batch={B} ctx={args.ctx}: {args.steps} eager decode steps")
+        print(format_profile(res))
+        return
     g = m.graphs[(m.buckets[-1], 1)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()

@@ -24,6 +24,7 @@ import torch
 from ..ops import functional as F
 from ..ops.functional import (EPI_F32, EPI_ROWPAR, EPI_STORE, EPI_SWIGLU, XGLOBAL, XNORM, AttnParams, EditParams,
                               GdnChunkParams, GdnParams, GemvWorkspace, LinearW, QkvPrepParams, SampleParams, TopkParams, ptr)
+from ..utils.trace import nvtx_end, nvtx_mark
 from .config import ModelConfig
 from .weights import ShardSpec, shard_layer
 
@@ -234,20 +235,53 @@ class _ModelBase:
         self.rec[:, slot].zero_()
         self.conv[:, slot].zero_()
 
+    # ---- swap: pinned host buffers (recycled by shape), asynchronous copies ordered by the compute stream
+    def _pinned(self, shape, dtype):
+        pool = getattr(self, "_pin_pool", None)
+        if pool is None:
+            pool = self._pin_pool = {}
+        free = pool.setdefault((tuple(shape), dtype), [])
+        return free.pop() if free else torch.empty(tuple(shape), dtype=dtype, pin_memory=True)
+
+    def _unpin(self, t):
+        self._pin_pool.setdefault((tuple(t.shape), t.dtype), []).append(t)
+
     def state_out(self, slot: int):
-        return self.rec[:, slot].float().cpu(), self.conv[:, slot].cpu()
+        """Recurrent state + conv history of a slot -> pinned host memory (asynchronous; the copy back is ordered
+        after it on the same stream).  The buffers are recycled when `state_in` consumes them."""
+        rec, conv = self.rec[:, slot], self.conv[:, slot]
+        hr, hc = self._pinned(rec.shape, rec.dtype), self._pinned(conv.shape, conv.dtype)
+        hr.copy_(rec, non_blocking=True)
+        hc.copy_(conv, non_blocking=True)
+        live = getattr(self, "_swap_live", None)
+        if live is None:
+            live = self._swap_live = []
+        live.extend((hr, hc))
+        return hr, hc
 
     def state_in(self, slot: int, st):
-        self.rec[:, slot].copy_(st[0].to(self.dev, non_blocking=True))
-        self.conv[:, slot].copy_(st[1].to(self.dev, non_blocking=True))
+        """Restores a slot from a swapped-out state (pinned host tensors from `state_out`) or from a prefix
+        snapshot (device tensors, which stay owned by the snapshot cache)."""
+        self.rec[:, slot].copy_(st[0], non_blocking=True)
+        self.conv[:, slot].copy_(st[1], non_blocking=True)
+        live = getattr(self, "_swap_live", [])
+        for t in st:
+            if any(t is x for x in live):
+                self._swap_live = live = [x for x in live if x is not t]
+                self._unpin(t)               # later writers of this buffer are ordered after the copy above
 
     def blocks_out(self, block_ids: list):
         idx = torch.tensor(block_ids, dtype=torch.long, device=self.dev)
-        return self.kv[:, :, idx].cpu()
+        dev = self.kv[:, :, idx]
+        host = self._pinned(dev.shape, dev.dtype)
+        host.copy_(dev, non_blocking=True)
+        return host
 
     def blocks_in(self, block_ids: list, data):
         idx = torch.tensor(block_ids, dtype=torch.long, device=self.dev)
-        self.kv[:, :, idx] = data.to(self.dev)
+        self.kv[:, :, idx] = data.to(self.dev, non_blocking=True)
+        if data.device.type == "cpu" and data.is_pinned():
+            self._unpin(data)
 
     def take_snapshots(self):
         out, self.snapshots = self.snapshots, {}
@@ -428,7 +462,8 @@ class _StepMixin:
         self._order = 0
         cur, nxt = x.h[0], x.h[1]
         ig = ia = 0
-        for L in self.layers:
+        for li, L in enumerate(self.layers):
+            nvtx_mark(f"layer {li} {'deltanet' if L.is_gdn else 'attention'} mixer")     # ranges only with TI_NVTX=1
             if L.is_gdn:
                 self._gemv(L.in_proj, cur, x.proj, T, xmode=XNORM, epi=EPI_STORE, norm_w=L.input_norm)
                 p = GdnParams()
@@ -466,7 +501,7 @@ class _StepMixin:
                 q.positions, q.slot_mapping, q.q_out = ptr(x.positions), ptr(x.slot_mapping), ptr(x.qbuf)
                 q.kcache, q.vcache = ptr(self.kv[ia, 0]), ptr(self.kv[ia, 1])
                 q.ld, q.hq, q.hkv, q.rotary_dim = x.proj.stride(0), self.hq, self.hkv, c.rotary_dim
-                q.eps, q.log2_theta = eps, math.log2(c.rope_theta)
+                q.eps, q.log2_theta, q.num_blocks = eps, math.log2(c.rope_theta), self.num_blocks
                 self._flush()
                 F.qkv_prep(q, T, self.D)
                 a = AttnParams()
@@ -478,7 +513,7 @@ class _StepMixin:
                 a.out = ptr(mix)
                 a.hq, a.hkv, a.max_blocks, a.nsplit = self.hq, self.hkv, x.max_blocks, x.nsplit
                 a.ld, a.num_qg = x.proj.stride(0), x.num_qg
-                a.scale_log2e = self.D ** -0.5 * 1.4426950408889634
+                a.scale_log2e, a.num_blocks = self.D ** -0.5 * 1.4426950408889634, self.num_blocks
                 F.attn_paged(a, self.D)
                 self._launches += 3 if x.num_qg else 1
                 if x.tiles is not None:
@@ -490,11 +525,13 @@ class _StepMixin:
                 self._rowpar(L.o, mix, cur, nxt, T)
                 ia += 1
             cur, nxt = nxt, cur
+            nvtx_mark(f"layer {li} mlp")
             self._gemv(L.gate_up, cur, x.act, T, xmode=XNORM, epi=EPI_SWIGLU, norm_w=L.post_norm)
             self._rowpar(L.down, x.act, cur, nxt, T)
             cur, nxt = nxt, cur
         self._flush()
         self._ar_flush()
+        nvtx_end()
         return cur
 
 

@@ -54,6 +54,27 @@ def is_current() -> bool:
         return f.read().strip() == _hash()
 
 
+# The checked variant: every peer-buffer / KV-page / workspace index that comes from run-time data goes through
+# TI_CHECK (common.cuh), which records kStatusBounds in the status word and SKIPS the access instead of faulting;
+# TI_JITTER adds random __nanosleep delays before packet sends and collects (stress of the flag protocols).
+# Selected at run time with TI_DEBUG_LIB=1 (see lib.py).
+DEBUG_FLAGS = ["-DTI_BOUNDS_CHECK", "-DTI_JITTER"]
+LIB_DEBUG = os.path.join(HERE, "libtileinfer_b200_dbg.so")
+BUILD_DEBUG = os.path.join(HERE, "build_dbg")
+
+
+def build_debug(force: bool = False) -> str:
+    """Compile the bounds-checked, jittered variant of the library (same sources, DEBUG_FLAGS)."""
+    global LIB, BUILD, STAMP, NVCC_FLAGS
+    keep = (LIB, BUILD, STAMP, NVCC_FLAGS)
+    LIB, BUILD, STAMP = LIB_DEBUG, BUILD_DEBUG, os.path.join(BUILD_DEBUG, "stamp.txt")
+    NVCC_FLAGS = keep[3] + DEBUG_FLAGS
+    try:
+        return build(force)
+    finally:
+        LIB, BUILD, STAMP, NVCC_FLAGS = keep
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     """Compile (if needed) and return the path of the shared library."""
     if not force and is_current():
@@ -61,9 +82,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(BUILD, exist_ok=True)
     nvcc = _nvcc()
     extra = ["-Xptxas", "-v"] if verbose else []
+    build_dir, lib_path, stamp_path = BUILD, LIB, STAMP
 
     def one(src):
-        obj = os.path.join(BUILD, src[:-3] + ".o")
+        obj = os.path.join(build_dir, src[:-3] + ".o")
         cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
@@ -74,14 +96,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
         objs = list(ex.map(one, sources()))
-    cmd = [nvcc, "-shared", "-o", LIB, *objs, "-lcudart"]
+    cmd = [nvcc, "-shared", "-o", lib_path, *objs, "-lcudart"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    with open(STAMP, "w") as f:
+    with open(stamp_path, "w") as f:
         f.write(_hash())
-    return LIB
+    return lib_path
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--debug" in sys.argv:
+        print(build_debug(force="--force" in sys.argv))
+    else:
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -32,6 +32,8 @@ struct QkvPrepParams {
   __nv_bfloat16* vcache;         // [blocks, hkv, D, 16]
   int ld, hq, hkv, rotary_dim;
   float eps, log2_theta;
+  int num_blocks;                // pages in the cache (checked builds verify the slot mapping against it; 0: unknown)
+  unsigned* status;              // error bits of the checked build, may be nullptr
 };
 
 template <int D>
@@ -54,6 +56,7 @@ __global__ void __launch_bounds__(32) qkv_prep_kernel(const __grid_constant__ Qk
     if (slot < 0) return;
     const long long blk = slot >> 4;
     const int off = (int)(slot & 15);
+    if (p.num_blocks > 0 && !TI_CHECK(blk, p.num_blocks, p.status)) return;
     __nv_bfloat16* dst = p.vcache + ((size_t)blk * p.hkv + kvh) * D * 16 + off;
 #pragma unroll
     for (int i = 0; i < E; ++i) dst[(size_t)(lane * E + i) * 16] = __float2bfloat16_rn(v[i]);
@@ -89,6 +92,7 @@ __global__ void __launch_bounds__(32) qkv_prep_kernel(const __grid_constant__ Qk
     if (slot < 0) return;
     const long long blk = slot >> 4;
     const int off = (int)(slot & 15);
+    if (p.num_blocks > 0 && !TI_CHECK(blk, p.num_blocks, p.status)) return;
     dst = p.kcache + (((size_t)blk * p.hkv + kvh) * 16 + off) * D;
   }
 #pragma unroll
@@ -111,6 +115,8 @@ struct AttnParams {
   __nv_bfloat16* out;            // merge: [T, hq*D]
   int hq, hkv, max_blocks, nsplit, ld, num_qg;
   float scale_log2e;
+  int num_blocks;                // pages in the cache (checked builds verify block-table entries; 0: unknown)
+  unsigned* status;
 };
 
 constexpr float kNegBig = -1e30f;
@@ -175,6 +181,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const __grid_constant__ AttnP
 
   for (int pg = p0 + stream; pg < p1; pg += NSTREAM) {
     const int blk = p.block_tables[(size_t)pr.seq * p.max_blocks + pg];
+    if (p.num_blocks > 0 && !TI_CHECK(blk, p.num_blocks, p.status)) continue;      // checked build: skip a bad page
     const __nv_bfloat16* kbase = p.kcache + ((size_t)blk * p.hkv + kh) * 16 * D;
     float sA[4] = {0.f, 0.f, 0.f, 0.f}, sB[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll

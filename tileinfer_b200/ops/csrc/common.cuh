@@ -21,6 +21,31 @@ enum StatusBits : unsigned {
   kStatusBounds = 4u,        // a checked index was out of range (debug builds)
 };
 
+// ---------------------------------------------------------------- checked build
+// -DTI_BOUNDS_CHECK: indices derived from run-time data (peer-buffer offsets, KV page numbers, workspace rows) are
+// verified before use; a violation sets kStatusBounds in the status word and the access is SKIPPED, so a wrong index
+// shows up as an error bit and a wrong result, never as a device fault.  Without the flag the macro is `true` and
+// compiles away.  -DTI_JITTER: random delays in front of the packet / flag protocol steps (arrival-order stress).
+#ifdef TI_BOUNDS_CHECK
+TI_DEVICE bool check_index(long long idx, long long limit, unsigned* status) {
+  if (idx >= 0 && idx < limit) return true;
+  if (status != nullptr) atomicOr(status, kStatusBounds);
+  return false;
+}
+#define TI_CHECK(idx, limit, status) ti::check_index((long long)(idx), (long long)(limit), (status))
+#else
+#define TI_CHECK(idx, limit, status) true
+#endif
+#ifdef TI_JITTER
+TI_DEVICE void jitter() {
+  unsigned h = (blockIdx.x + 1u) * 2654435761u ^ ((threadIdx.x >> 5) + 1u) * 40503u ^ (unsigned)clock();
+  h ^= h >> 13;
+  __nanosleep(h % 4000u);
+}
+#else
+TI_DEVICE void jitter() {}
+#endif
+
 // ---------------------------------------------------------------- small math
 TI_DEVICE float warp_sum(float v) {
 #pragma unroll

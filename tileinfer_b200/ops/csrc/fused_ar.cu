@@ -40,6 +40,7 @@ struct ArRowsParams {
   unsigned long long timeout_ns;
   int M, N, tp, rank, order, mode;
   float eps;
+  int rows_cap;                    // rows the partial buffers hold (checked builds; 0: unknown)
 };
 
 TI_DEVICE uint4 ld_volatile16(const void* p) {
@@ -66,6 +67,7 @@ __global__ void __launch_bounds__(512) ar_rows_kernel(const __grid_constant__ Ar
   pdl_trigger();
   pdl_wait();                                  // the producing GEMM has completed: this rank's partials are in memory
   if (m == 0 && tid == 0) {
+    jitter();
     __threadfence_system();
     for (int q = 0; q < p.tp; ++q)
       store_flag_release(reinterpret_cast<uint32_t*>(p.flag_peer[q]) + p.rank, tag);
@@ -78,6 +80,7 @@ __global__ void __launch_bounds__(512) ar_rows_kernel(const __grid_constant__ Ar
 
   const int nchunk = p.N >> 3;
   const size_t row_off = (size_t)m * p.N * 2;
+  if (p.rows_cap > 0 && !TI_CHECK(m, p.rows_cap, p.status)) return;
   float v[5][8];
   float ss = 0.f;
 #pragma unroll

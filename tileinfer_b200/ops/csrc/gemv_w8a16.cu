@@ -154,7 +154,9 @@ TI_DEVICE void epilogue(const GemvParams& p, int nt, int g, int t, const float (
         const unsigned tag = (*p.step_ptr) * 65536u + (unsigned)p.order + 1u;
         const int slot = p.order & 1;
         const size_t mine = ((((size_t)slot * p.tp + p.rank) * p.m_cap + m) * (size_t)(p.N >> 1) + (n >> 1)) * 16;
-        for (int q = 0; q < p.tp; ++q) ll_store2(reinterpret_cast<uint8_t*>(p.peer_ll[q]) + mine, v0, v1, tag);
+        jitter();
+        if (TI_CHECK(mine + 15, (size_t)2 * p.tp * p.m_cap * (size_t)(p.N >> 1) * 16, p.status))
+          for (int q = 0; q < p.tp; ++q) ll_store2(reinterpret_cast<uint8_t*>(p.peer_ll[q]) + mine, v0, v1, tag);
       } else {
         const uint32_t rw = half ? pre.r1 : pre.r0;
         uint32_t* o = reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.N + n);
@@ -174,13 +176,15 @@ TI_DEVICE void rowpar_reduce(const GemvParams& p, int cta, int ncta) {
   const int slot = p.order & 1;
   const int pairs = p.N >> 1;
   const uint8_t* local = reinterpret_cast<const uint8_t*>(p.peer_ll[p.rank]);
+  jitter();
   for (int i = cta * blockDim.x + threadIdx.x; i < p.M * pairs; i += ncta * blockDim.x) {
     const int m = i / pairs, pr = i - m * pairs;
     float s0 = 0.f, s1 = 0.f;
     for (int r = 0; r < p.tp; ++r) {
-      float a, b;
-      ll_wait2(local + ((((size_t)slot * p.tp + r) * p.m_cap + m) * (size_t)pairs + pr) * 16, tag, a, b, p.timeout_ns,
-               p.status);
+      float a = 0.f, b = 0.f;
+      const size_t off = ((((size_t)slot * p.tp + r) * p.m_cap + m) * (size_t)pairs + pr) * 16;
+      if (TI_CHECK(off + 15, (size_t)2 * p.tp * p.m_cap * (size_t)pairs * 16, p.status))
+        ll_wait2(local + off, tag, a, b, p.timeout_ns, p.status);
       s0 += a;
       s1 += b;
     }

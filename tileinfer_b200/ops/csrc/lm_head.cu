@@ -210,14 +210,17 @@ __global__ void __launch_bounds__(256) topk_stage2_kernel(const __grid_constant_
     const float v = fin_v[j];
     const int gi = fin_i[j] < 0 ? -1 : fin_i[j] + p.vocab_start;
     const size_t mine = ((((size_t)slot * p.tp + p.rank) * p.m_cap + m) * 64 + j) * 16;
-    for (int q = 0; q < p.tp; ++q)
-      if (q != p.rank) ll_store2(reinterpret_cast<uint8_t*>(p.peer_buf[q]) + mine, v, __int_as_float(gi), tag);
+    const size_t cand_bytes = (size_t)2 * p.tp * p.m_cap * 64 * 16;
+    jitter();
+    if (TI_CHECK(mine + 15, cand_bytes, p.status))
+      for (int q = 0; q < p.tp; ++q)
+        if (q != p.rank) ll_store2(reinterpret_cast<uint8_t*>(p.peer_buf[q]) + mine, v, __int_as_float(gi), tag);
     const uint8_t* local = reinterpret_cast<const uint8_t*>(p.peer_buf[p.rank]);
     for (int r = 0; r < p.tp; ++r) {
       float a = v, b = __int_as_float(gi);
       if (r != p.rank) {
         const size_t off = ((((size_t)slot * p.tp + r) * p.m_cap + m) * 64 + j) * 16;
-        ll_wait2(local + off, tag, a, b, p.timeout_ns, p.status);
+        if (TI_CHECK(off + 15, cand_bytes, p.status)) ll_wait2(local + off, tag, a, b, p.timeout_ns, p.status);
       }
       p.out_val[((size_t)m * p.tp + r) * kk + j] = a;
       p.out_idx[((size_t)m * p.tp + r) * kk + j] = __float_as_int(b);

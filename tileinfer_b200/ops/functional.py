@@ -57,14 +57,14 @@ class GdnChunkParams(ctypes.Structure):
 class QkvPrepParams(ctypes.Structure):
     _fields_ = [("proj", _P), ("q_norm", _P), ("k_norm", _P), ("positions", _P), ("slot_mapping", _P),
                 ("q_out", _P), ("kcache", _P), ("vcache", _P), ("ld", _I), ("hq", _I), ("hkv", _I),
-                ("rotary_dim", _I), ("eps", _F), ("log2_theta", _F)]
+                ("rotary_dim", _I), ("eps", _F), ("log2_theta", _F), ("num_blocks", _I), ("status", _P)]
 
 
 class AttnParams(ctypes.Structure):
     _fields_ = [("q", _P), ("kcache", _P), ("vcache", _P), ("block_tables", _P), ("positions", _P),
                 ("qg_seq", _P), ("qg_tok0", _P), ("qg_ntok", _P), ("o_part", _P), ("ml_part", _P),
                 ("gate_src", _P), ("out", _P), ("hq", _I), ("hkv", _I), ("max_blocks", _I), ("nsplit", _I),
-                ("ld", _I), ("num_qg", _I), ("scale_log2e", _F)]
+                ("ld", _I), ("num_qg", _I), ("scale_log2e", _F), ("num_blocks", _I), ("status", _P)]
 
 
 class TopkParams(ctypes.Structure):
@@ -80,7 +80,7 @@ class ArRowsParams(ctypes.Structure):
                 ("flag_peer", ctypes.c_uint64 * MAX_RANKS), ("resid", _P), ("h_out", _P), ("norm_w", _P), ("xh", _P),
                 ("xl", _P), ("xscale", _P), ("xn", _P), ("step_ptr", _P), ("status", _P),
                 ("timeout_ns", ctypes.c_ulonglong), ("M", _I), ("N", _I), ("tp", _I), ("rank", _I), ("order", _I),
-                ("mode", _I), ("eps", _F)]
+                ("mode", _I), ("eps", _F), ("rows_cap", _I)]
 
 
 class EditParams(ctypes.Structure):
@@ -476,10 +476,14 @@ def gdn_chunked(p: GdnChunkParams, num_seqs: int, T: int, dk: int, dv: int, stat
 
 
 def qkv_prep(p: QkvPrepParams, T: int, D: int):
+    if not p.status:
+        p.status = status_ptr()
     check(L().ti_qkv_prep(ctypes.byref(p), T, D, stream()), "ti_qkv_prep")
 
 
 def attn_paged(p: AttnParams, D: int):
+    if not p.status:
+        p.status = status_ptr()
     check(L().ti_attn_paged(ctypes.byref(p), D, stream()), "ti_attn_paged")
 
 
@@ -513,6 +517,7 @@ def ar_rows(comm, parity: int, M: int, N: int, resid, h_out, *, order: int, mode
         p.xn = ptr(xn)
     p.step_ptr, p.status, p.timeout_ns = comm.step_ptr, comm.status_ptr, comm.timeout_ns
     p.M, p.N, p.tp, p.rank, p.order, p.mode, p.eps = M, N, comm.tp, comm.rank, order, mode, eps
+    p.rows_cap = int(getattr(comm, "ar_rows", 0) or 0)
     check(L().ti_ar_rows(ctypes.byref(p), stream()), "ti_ar_rows")
 
 

@@ -40,9 +40,12 @@ class ChainParams(ctypes.Structure):
 def lib() -> ctypes.CDLL:
     global _LIB
     if _LIB is None:
-        path = _build.LIB
-        if not _build.is_current():
-            path = _build.build()
+        if os.environ.get("TI_DEBUG_LIB", "0") == "1":
+            path = _build.build_debug()          # bounds-checked + jittered variant (tests, debugging)
+        else:
+            path = _build.LIB
+            if not _build.is_current():
+                path = _build.build()
         _LIB = ctypes.CDLL(path)
         for name in dir(_Sigs):
             if name.startswith("ti_"):
