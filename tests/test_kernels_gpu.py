@@ -905,3 +905,46 @@ def test_ar_rows_fused_allreduce_residual_norm_quant(M, N, tp):
     torch.cuda.synchronize()
     assert int(ctrl[1]) & 1 == 1
     assert float(torch.ones(4, device="cuda").sum()) == 4.0
+
+
+@pytest.mark.parametrize("shift", [10, 13])
+def test_two_limb_activation_format_on_outlier_rows(shift):
+    """Activation rows with one channel 2^10 / 2^13 above the rest, through the W8A16 GEMV and the tcgen05 GEMM.
+
+    The kernels turn a bf16 row into 16-bit fixed point with ONE power-of-two exponent per row, so an element 2^s
+    below the row maximum keeps 15 - s bits.  The error of an output n is then a sum of K independent rounding errors
+    of at most half a fixed-point unit u = 2^(e-14): standard deviation u / sqrt(12) * |w_n|_2.  The test pins that
+    bound (6 sigma, plus the bf16 rounding of the stored output), and reports the same rows through the bf16-weight
+    kernels (bf16 activations, exact products), whose only error is the output rounding."""
+    F = _F()
+    torch.manual_seed(shift)
+    N, K = 1024, 5120
+    w = _rand_w(N, K, seed=shift)
+    W = F.LinearW(w, True)
+    wd = W.dense().double()                                     # the dequantised weights the kernel multiplies with
+    Wb = F.LinearW(W.dense().float(), False)                    # the same values as bf16 weights
+    for M in (1, 4, 64):
+        x = torch.randn(M, K, device="cuda")
+        x[:, 77] = 2.0 ** shift * (1 + 0.25 * torch.rand(M, device="cuda"))
+        x = x.to(BF16)
+        ref = x.double() @ wd.t()
+        if M <= 8:
+            y = F.gemv(W, x).double()
+            yb = F.gemv(Wb, x).double()
+        else:
+            y = F.gemm_w8a16(W, F.quant_rows(x)).double()
+            yb = F.gemm_bf16(Wb, x.contiguous()).double()
+        torch.cuda.synchronize()
+        e = torch.floor(torch.log2(x.float().abs().amax(dim=1))).double()            # exponent of the row maximum
+        unit = torch.exp2(e - 14)[:, None]
+        sigma = unit / math.sqrt(12.0) * wd.norm(dim=1)[None, :]
+        bound = 6.0 * sigma + 2.0 ** -8 * ref.abs() + 1e-3
+        err, errb = (y - ref).abs(), (yb - ref).abs()
+        assert bool((err <= bound).all()), f"M={M}: worst excess {float((err - bound).max())}"
+        # the bf16-activation path is limited by the output rounding alone
+        assert bool((errb <= 2.0 ** -8 * ref.abs() + 1e-3).all())
+        # how much is lost: error of the fixed-point form in units of the part of the output that does NOT come from
+        # the outlier channel (what later layers can still distinguish)
+        rest = (x.double() @ wd.t() - x[:, 77:78].double() * wd[:, 77][None, :]).abs().mean()
+        rel = float(err.mean() / rest)
+        assert rel < (0.05 if shift == 10 else 0.4), rel
