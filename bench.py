@@ -109,7 +109,7 @@ def run_ours(args) -> dict:
     b = Batch(torch.tensor([first]), torch.tensor([PROMPT_LEN]), [0, 1], [PROMPT_LEN + 1], [table],
               torch.tensor([PROMPT_LEN]), [0])
     model.forward_and_sample(b, [0], 1)
-    gr = model.graphs[(1, 1)]
+    gr = model.decode_graph(1, 1)
     x = gr.x
 
     def advance():

@@ -60,7 +60,7 @@ def main():
         if args.sample:
             spec.update(temperature=[0.6] * B, top_k=[50] * B, u=torch.rand(B).tolist())
         model.forward_and_sample(batch, list(range(B)), k, spec)
-        gr = model.graphs[(next(b for b in model.buckets if b >= B), 1 if k == 1 else 64)]
+        gr = model.decode_graph(B, k)
         x = gr.x
 
         def advance():

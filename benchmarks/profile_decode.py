@@ -80,7 +80,7 @@ def main():
         print(f"model={cfg.name} batch={B} ctx={args.ctx}: {args.steps} eager decode steps")
         print(format_profile(res))
         return
-    g = m.graphs[(m.buckets[-1], 1)]
+    g = m.decode_graph(m.buckets[-1], 1)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):

@@ -452,7 +452,8 @@ def test_topk(k):
 
 # token tiles of 32 / 64 / 128; (24, 1024, 4096), (48, 1552, 2048) and (64, 5120, 4096) also split k over gridDim.z
 @pytest.mark.parametrize("M,N,K", [(128, 256, 128), (200, 1552, 384), (64, 5120, 768), (300, 2048, 5120),
-                                   (24, 1024, 4096), (48, 1552, 2048), (64, 5120, 4096), (17, 640, 1024)])
+                                   (24, 1024, 4096), (48, 1552, 2048), (64, 5120, 4096), (17, 640, 1024),
+                                   (1024, 9480, 512), (1100, 9600, 1024)])     # the last two: 256-row tiles
 def test_tcgen05_gemm_w8a16(M, N, K):
     """TMA-fed tcgen05 kind::i8 GEMM with two-limb activations against fp32 matmul, all three epilogues."""
     F = _F()
@@ -484,7 +485,8 @@ def test_tcgen05_gemm_w8a16(M, N, K):
     assert int(torch.zeros(1, device="cuda").item()) == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(24, 1024, 2048), (64, 5128, 768), (200, 1552, 384), (130, 2048, 5120)])
+@pytest.mark.parametrize("M,N,K", [(24, 1024, 2048), (64, 5128, 768), (200, 1552, 384), (130, 2048, 5120),
+                                   (1024, 9480, 512)])                          # 256-row tiles
 def test_tcgen05_gemm_bf16(M, N, K):
     """kind::f16 variant (bf16 weights in the GEMV tile layout, bf16 activations, fp32 accumulation in TMEM)."""
     F = _F()

@@ -22,7 +22,7 @@ import os
 import torch
 
 from ..ops import functional as F
-from ..ops.functional import (EPI_F32, EPI_ROWPAR, EPI_STORE, EPI_SWIGLU, XGLOBAL, XNORM, AttnParams, EditParams,
+from ..ops.functional import (EPI_ARGMAX, EPI_F32, EPI_ROWPAR, EPI_STORE, EPI_SWIGLU, XGLOBAL, XNORM, AttnParams, EditParams,
                               GdnChunkParams, GdnParams, GemvWorkspace, LinearW, QkvPrepParams, SampleParams, TopkParams, ptr)
 from ..utils.trace import nvtx_end, nvtx_mark
 from .config import ModelConfig
@@ -345,7 +345,7 @@ class _StepMixin:
         F.gemm_bf16(W, xs, out=out[:M], epi=gepi, resid=r)
         self._launches += 1
 
-    def _gemv(self, W: LinearW, x, out, M, *, xmode, epi, norm_w=None, resid=None, ldo=None):
+    def _gemv(self, W: LinearW, x, out, M, *, xmode, epi, norm_w=None, resid=None, ldo=None, out_idx=None):
         """y = x W^T in row chunks of 16; counts launches; assigns collective order numbers."""
         pend = self._ar_pending
         if pend is not None:
@@ -372,7 +372,8 @@ class _StepMixin:
                 W, x[m0:m0 + m], out[m0:m0 + m], m, xmode=xmode, epi=epi, norm_w=norm_w,
                 resid=None if resid is None else resid[m0:m0 + m], ws=self.ws, eps=self.cfg.rms_eps,
                 ldx=x.stride(0), ldo=out.stride(0) if ldo is None else ldo,
-                comm=self.peer if epi == EPI_ROWPAR else None, order=order, xll=xll)
+                comm=self.peer if epi == EPI_ROWPAR else None, order=order, xll=xll,
+                out_idx=None if out_idx is None else out_idx[m0:m0 + m])
             if M <= step and self.chain:
                 # dependent products are collected and launched together (up to four per launch)
                 if self._pending and (self._pending_wt != W.wt or len(self._pending) >= F.MAX_CHAIN):
@@ -548,8 +549,10 @@ class _RunMixin:
         assert cs <= 4096, "vocabulary shard too large for the top-k kernel"
         return -(-V // cs), cs
 
-    def _make_topk(self, logits, n, k, order=65000):
+    def _make_topk(self, logits, n, k, order=65000, per_cta=False):
         chunks, cs = self._topk_geometry(k)
+        if per_cta:                      # candidates come from the arg-max epilogue of the GEMV: one per row and CTA
+            chunks, cs = F.NUM_SMS, 0
         dev = self.dev
         t = _Ctx()
         t.ws_val = torch.empty(n * chunks * k, dtype=torch.float32, device=dev)
@@ -558,7 +561,7 @@ class _RunMixin:
         t.out_idx = torch.empty_like(t.out_val, dtype=torch.int32)
         p = TopkParams()
         p.logits, p.ws_val, p.ws_idx, p.out_val, p.out_idx = ptr(logits), ptr(t.ws_val), ptr(t.ws_idx), ptr(t.out_val), ptr(t.out_idx)
-        p.M, p.V, p.ld, p.k, p.chunks, p.chunk_size = n, self.v_local, logits.stride(0), k, chunks, cs
+        p.M, p.V, p.ld, p.k, p.chunks, p.chunk_size = n, self.v_local, 0 if logits is None else logits.stride(0), k, chunks, cs
         p.vocab_start = self.vocab_start
         p.tp, p.rank, p.order, p.m_cap = 1, 0, order, 0
         if self.peer is not None:
@@ -572,6 +575,19 @@ class _RunMixin:
     def _lm_head(self, hidden, logits, n):
         self._gemv(self.lm_head, hidden, logits, n, xmode=XNORM, epi=EPI_F32, norm_w=self.final_norm)
         self._flush()
+
+    def _lm_head_argmax(self, hidden, t, n):
+        """Greedy rows, no logit edits: the lm_head GEMV keeps the best column of every row per CTA in its epilogue
+        (no [n, V] logits in memory, no first selection pass); the merge kernel picks the winner and exchanges it."""
+        self._gemv(self.lm_head, hidden, t.ws_val.view(n, -1), n, xmode=XNORM, epi=EPI_ARGMAX, norm_w=self.final_norm,
+                   out_idx=t.ws_idx.view(n, -1))
+        self._flush()
+        F.topk_merge(t.params)
+        self._launches += 1
+
+    def fused_argmax_ok(self, n: int, k: int) -> bool:
+        return k == 1 and n <= min(self.gemm_min_rows, F.max_rows(self.lm_head.wt, XNORM, self.lm_head.K)) \
+            and os.environ.get("TI_FUSED_ARGMAX", "1") != "0"
 
     def _topk_rows(self, logits, n, k):
         """Per-rank top-k (+ fused candidate exchange); rows in chunks of the peer buffer capacity."""
@@ -687,16 +703,23 @@ class _RunMixin:
         self.buckets.append(top)
         self.graph_pool = None
         for b in self.buckets:
-            self._get_graph(b, 1)
+            self._get_graph(b, 1, self.fused_argmax_ok(b, 1))
 
-    def _get_graph(self, B: int, k: int):
-        key = (B, k)
+    def decode_graph(self, n: int, k: int = 1, edits: bool = False):
+        """The captured decode step that serves `n` sequences with `k` candidates (captured on first use)."""
+        B = next(b for b in self.buckets if b >= n)
+        k = 1 if k <= 1 else 64
+        return self._get_graph(B, k, not edits and self.fused_argmax_ok(B, k))
+
+    def _get_graph(self, B: int, k: int, fa: bool = False):
+        """fa: the lm_head product keeps only each CTA's arg-max (greedy rows without logit edits)."""
+        key = (B, k, fa)
         g = self.graphs.get(key)
         if g is not None:
             return g
         dev = self.dev
         nsplit = max(1, min(32, -(-8 * F.NUM_SMS // (B * self.hkv))))
-        base = self.graphs.get((B, 1))
+        base = next((v for kk, v in self.graphs.items() if kk[0] == B), None)
         g = _Ctx()
         if base is not None:      # same bucket, other k: share the input tensors
             g.x = base.x
@@ -714,18 +737,21 @@ class _RunMixin:
             }
             x.slots.fill_(self.padding_slot)
         x = g.x
-        g.logits = torch.zeros(B, self.v_local, dtype=torch.float32, device=dev)
-        g.topk = self._make_topk(g.logits, B, k)
+        g.logits = None if fa else torch.zeros(B, self.v_local, dtype=torch.float32, device=dev)
+        g.topk = self._make_topk(g.logits, B, k, per_cta=fa)
         g.k = k
-        g.samp = self._make_sampler_state(g.logits, B, g.topk)
+        g.samp = self._make_sampler_state(g.logits if not fa else g.topk.out_val, B, g.topk)
         fused_sample = self.tp == 1 or self.peer is not None
 
         def body():
             cur = self._run_layers(x)
-            self._lm_head(cur, g.logits, B)
-            F.logits_edit(g.samp.edit)                 # rows without an edit slot leave at once
-            F.topk(g.topk.params)
-            self._launches += 3
+            if fa:
+                self._lm_head_argmax(cur, g.topk, B)
+            else:
+                self._lm_head(cur, g.logits, B)
+                F.logits_edit(g.samp.edit)             # rows without an edit slot leave at once
+                F.topk(g.topk.params)
+                self._launches += 3
             if fused_sample:
                 F.sample(g.samp.sample)
                 self._launches += 1
@@ -843,8 +869,8 @@ class _RunMixin:
 
     def _decode_graph_step(self, batch, k: int, spec=None):
         n = batch.num_seqs
-        B = next(b for b in self.buckets if b >= n)
-        g = self._get_graph(B, k)
+        g = self.decode_graph(n, k, edits=bool(spec and spec.get("edits")))
+        self._last_graph = g
         h, x = g.host, g.x
         h["ids"][:n] = batch.input_ids
         h["positions"][:n] = batch.positions
@@ -894,8 +920,7 @@ class _RunMixin:
                 and max(len(b) for b in batch.block_tables) <= self.graph_max_blocks:
             vals, idx = self._decode_graph_step(batch, k, spec)
             if fused:
-                g = self.graphs[(next(b for b in self.buckets if b >= n), k)]
-                return self._read_tokens(g.samp, n)
+                return self._read_tokens(self._last_graph.samp, n)
         else:
             hidden = self.forward(batch)
             rows = torch.tensor(sample_rows, dtype=torch.long, device=self.dev)

@@ -41,9 +41,11 @@ constexpr int kGemmThreads = 192;
 // one overlaps the main loop of the other.
 constexpr int kGemmRingBytes = TI_GEMM_RING_KB * 1024;
 // BN = tokens per CTA (TMEM columns per accumulator); BF16: bf16 weights and activations (one plane, one accumulator)
-template <int BN, bool BF16> struct GemmGeom {
+// BMH = weight-row halves per CTA: 1 -> a 128-row tile; 2 -> a 256-row tile as two 128-row MMAs that share ONE
+// activation tile in shared memory (the bytes a CTA pulls through L2 per multiply-add drop by a third).
+template <int BN, bool BF16, int BMH = 1> struct GemmGeom {
   static constexpr int kStageB = BN * kBK;                         // one limb plane / the bf16 activation tile
-  static constexpr int kStageBytes = kStageA + (BF16 ? 1 : 2) * kStageB;
+  static constexpr int kStageBytes = BMH * kStageA + (BF16 ? 1 : 2) * kStageB;
   static constexpr int kStages = kGemmRingBytes / kStageBytes < 24 ? kGemmRingBytes / kStageBytes : 24;
   static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 16 * kStages + 64 + 1024;
 };
@@ -119,9 +121,10 @@ TI_DEVICE void gemm_epilogue4(const GemmParams& p, int m, int n, float4 v) {
       make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
 }
 
-template <int BN, bool BF16>
+template <int BN, bool BF16, int BMH>
 __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) gemm_w8a16_kernel(const __grid_constant__ GemmParams p) {
-  using G = GemmGeom<BN, BF16>;
+  using G = GemmGeom<BN, BF16, BMH>;
+  constexpr int kAcc = BF16 ? 1 : 2;                               // accumulators (limbs) per row half
   constexpr int kStages = G::kStages, kStageBytes = G::kStageBytes, kStageB = G::kStageB;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte aligned stage buffers (the swizzle pattern repeats every 512 bytes)
@@ -138,7 +141,7 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
   const int tile_m = blockIdx.x, tile_n = blockIdx.y, split = blockIdx.z, S = gridDim.z;
   const int KB = p.K / kBK;
   const int kb0 = split * p.kb_per_split, kb1 = min(KB, kb0 + p.kb_per_split);
-  constexpr uint32_t kCols = (BF16 ? 1 : 2) * BN < 32 ? 32 : (BF16 ? 1 : 2) * BN;   // TMEM allocation: a power of two >= 32
+  constexpr uint32_t kCols = BMH * kAcc * BN < 32 ? 32 : BMH * kAcc * BN;   // TMEM allocation: a power of two >= 32
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -168,9 +171,9 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
         if (!ok) break;
         const uint32_t dst = stage0 + s * kStageBytes;
         mbar_expect_tx(full0 + 8 * s, kStageBytes);
-        tma_load_4d(dst, &p.map_w, 0, 0, kb, tile_n * (kBM / 8), full0 + 8 * s);
-        tma_load_2d(dst + kStageA, &p.map_xh, kb * kBK, tile_m * BN, full0 + 8 * s);
-        if (!BF16) tma_load_2d(dst + kStageA + kStageB, &p.map_xl, kb * kBK, tile_m * BN, full0 + 8 * s);
+        tma_load_4d(dst, &p.map_w, 0, 0, kb, tile_n * (BMH * kBM / 8), full0 + 8 * s);     // box: BMH * 16 row tiles
+        tma_load_2d(dst + BMH * kStageA, &p.map_xh, kb * kBK, tile_m * BN, full0 + 8 * s);
+        if (!BF16) tma_load_2d(dst + BMH * kStageA + kStageB, &p.map_xl, kb * kBK, tile_m * BN, full0 + 8 * s);
       }
     }
   } else if (warp == 1) {
@@ -182,16 +185,21 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
         ok = mbar_wait(full0 + 8 * s, (it / kStages) & 1, kGemmWaitNs, p.status);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a = stage0 + s * kStageBytes, bh = a + kStageA, bl = bh + kStageB;
+        const uint32_t a = stage0 + s * kStageBytes, bh = a + BMH * kStageA, bl = bh + kStageB;
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks) {                          // two 32-byte k steps inside the 64-byte slab
-          const uint64_t da = smem_desc_sw64(a + ks * 32);
           const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
-          if (BF16) {
-            umma_bf16(tmem_base, da, smem_desc_sw64(bh + ks * 32), idesc_bf16<BN>(), acc);
-          } else {
-            umma_i8(tmem_base, da, smem_desc_sw64(bh + ks * 32), idesc_i8<BN>(true), acc);
-            umma_i8(tmem_base + BN, da, smem_desc_sw64(bl + ks * 32), idesc_i8<BN>(false), acc);
+          const uint64_t dbh = smem_desc_sw64(bh + ks * 32), dbl = smem_desc_sw64(bl + ks * 32);
+#pragma unroll
+          for (int h = 0; h < BMH; ++h) {                         // the row halves share the activation operand
+            const uint64_t da = smem_desc_sw64(a + h * kStageA + ks * 32);
+            const uint32_t d0 = tmem_base + (uint32_t)(h * kAcc * BN);
+            if (BF16) {
+              umma_bf16(d0, da, dbh, idesc_bf16<BN>(), acc);
+            } else {
+              umma_i8(d0, da, dbh, idesc_i8<BN>(true), acc);
+              umma_i8(d0 + BN, da, dbl, idesc_i8<BN>(false), acc);
+            }
           }
         }
         umma_commit(empty0 + 8 * s);                              // stage may be refilled once these MMAs are done
@@ -203,22 +211,25 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
     const int quarter = warp & 3;
     const bool ok = mbar_wait(acc_bar, 0, 2 * kGemmWaitNs, p.status);
     tc_fence_after();
-    const int n = tile_n * kBM + quarter * 32 + lane;             // weight row == output feature of this lane
-    const float ws = (ok && n < p.N) ? (BF16 ? 1.f : __bfloat162float(p.wscale[n])) : 0.f;
-    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    for (int c0 = 0; c0 < BN; c0 += 32) {
-      uint32_t hi[32], lo[32];
-      tmem_ld32(taddr + c0, hi);
-      if (!BF16) tmem_ld32(taddr + BN + c0, lo);
-      tmem_ld_wait();
+#pragma unroll 1
+    for (int h = 0; h < BMH; ++h) {
+      const int n = tile_n * (BMH * kBM) + h * kBM + quarter * 32 + lane;   // weight row == output feature of this lane
+      const float ws = (ok && n < p.N) ? (BF16 ? 1.f : __bfloat162float(p.wscale[n])) : 0.f;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * kAcc * BN);
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t hi[32], lo[32];
+        tmem_ld32(taddr + c0, hi);
+        if (!BF16) tmem_ld32(taddr + BN + c0, lo);
+        tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int m = tile_m * BN + c0 + j;                       // token (uniform over the warp)
-        if (m >= p.M) break;
-        const float v = BF16 ? __uint_as_float(hi[j]) * ws
-                             : ((float)(int)hi[j] * 256.f + (float)(int)lo[j]) * p.xscale[m] * ws;
-        if (S == 1) gemm_epilogue(p, m, n, lane, v);
-        else if (n < p.N) p.part[((size_t)split * p.M + m) * p.N + n] = v;
+        for (int j = 0; j < 32; ++j) {
+          const int m = tile_m * BN + c0 + j;                     // token (uniform over the warp)
+          if (m >= p.M) break;
+          const float v = BF16 ? __uint_as_float(hi[j]) * ws
+                               : ((float)(int)hi[j] * 256.f + (float)(int)lo[j]) * p.xscale[m] * ws;
+          if (S == 1) gemm_epilogue(p, m, n, lane, v);
+          else if (n < p.N) p.part[((size_t)split * p.M + m) * p.N + n] = v;
+        }
       }
     }
     tc_fence_before();
@@ -237,8 +248,9 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
     if (s_last && warp >= 2) {
       // lane -> four adjacent output features, warp -> every fourth token; the loads of four tokens and all
       // slices are issued before the first is used
-      const int n4 = tile_n * kBM + lane * 4;
       const int m_end = min(p.M, (tile_m + 1) * BN);
+      for (int hh = 0; hh < BMH; ++hh) {
+      const int n4 = tile_n * (BMH * kBM) + hh * kBM + lane * 4;
       for (int m0 = tile_m * BN + (warp - 2); m0 < m_end; m0 += 16) {
         float4 acc[4];
 #pragma unroll
@@ -259,6 +271,7 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
           const int m = m0 + 4 * u;
           if (m < m_end && n4 < p.N) gemm_epilogue4(p, m, n4, acc[u]);
         }
+      }
       }
     }
   }
@@ -425,7 +438,8 @@ struct MapKey {
   int d0, d1, box;
   bool operator<(const MapKey& o) const { return std::tie(base, d0, d1, box) < std::tie(o.base, o.d0, o.d1, o.box); }
 };
-// box == 0: weight map over [n_tiles = d1][KB = d0][8][64]; box > 0: limb plane [M = d1][K = d0], box {64, box}
+// box <= 0: weight map over [n_tiles = d1][KB = d0][8][64] with a box of 16 (box == 0) or -box row tiles;
+// box > 0: limb plane [M = d1][K = d0], box {64, box}
 static int cached_map(CUtensorMap* dst, const void* base, int d0, int d1, int box) {
   static std::map<MapKey, CUtensorMap> cache;
   static std::mutex mu;
@@ -435,10 +449,10 @@ static int cached_map(CUtensorMap* dst, const void* base, int d0, int d1, int bo
   if (it == cache.end()) {
     CUtensorMap m;
     int rc;
-    if (box == 0) {
+    if (box <= 0) {
       const cuuint64_t dims[4] = {64, 8, (cuuint64_t)d0, (cuuint64_t)d1};
       const cuuint64_t strides[3] = {64, 512, (cuuint64_t)d0 * 512};
-      const cuuint32_t bx[4] = {64, 8, 1, 16};
+      const cuuint32_t bx[4] = {64, 8, 1, (cuuint32_t)(box == 0 ? 16 : -box)};
       rc = encode_map(&m, base, 4, dims, strides, bx);
     } else {
       const cuuint64_t dims[2] = {(cuuint64_t)d0, (cuuint64_t)d1};
@@ -454,16 +468,28 @@ static int cached_map(CUtensorMap* dst, const void* base, int d0, int d1, int bo
   return 0;
 }
 
-template <int BN, bool BF16>
+template <int BN, bool BF16, int BMH = 1>
 static int launch_gemm(const GemmParams& p, dim3 grid, cudaStream_t st) {
   static bool configured = false;
-  auto k = gemm_w8a16_kernel<BN, BF16>;
+  auto k = gemm_w8a16_kernel<BN, BF16, BMH>;
   if (!configured) {
-    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmGeom<BN, BF16>::kSmem);
+    cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmGeom<BN, BF16, BMH>::kSmem);
     configured = true;
   }
-  k<<<grid, kGemmThreads, GemmGeom<BN, BF16>::kSmem, st>>>(p);
+  k<<<grid, kGemmThreads, GemmGeom<BN, BF16, BMH>::kSmem, st>>>(p);
   return (int)cudaGetLastError();
+}
+
+// 256-row tiles when the token tile is full-size and there are enough tiles to fill the GPU several times over
+// (TI_GEMM_BMH=1 / 2 forces a choice)
+static int pick_bmh(int M, int n_tiles) {
+  static const int forced = [] {
+    const char* e = getenv("TI_GEMM_BMH");
+    return e == nullptr ? 0 : atoi(e);
+  }();
+  if (forced == 1 || forced == 2) return n_tiles >= 32 ? forced : 1;
+  const long long tiles256 = (long long)((n_tiles * 8 + 255) / 256) * ((M + 127) / 128);
+  return (M > 64 && n_tiles >= 32 && tiles256 >= 2 * 148) ? 2 : 1;
 }
 
 // k split that fills the 148 SMs when there are few output tiles (at least 16 slabs per slice); sets kb_per_split
@@ -511,7 +537,8 @@ int ti_gemm_w8a16(const void* w, const void* wscale, int n_tiles, int N, int K, 
   ti::GemmParams p = {};
   const int KB = K / 64;
   const int BN = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
-  int rc = ti::cached_map(&p.map_w, w, KB, n_tiles, 0);
+  const int BMH = ti::pick_bmh(M, n_tiles);
+  int rc = ti::cached_map(&p.map_w, w, KB, n_tiles, BMH == 2 ? -32 : 0);
   if (rc) return rc;
   rc = ti::cached_map(&p.map_xh, xh, K, M, BN);
   if (rc) return rc;
@@ -527,10 +554,12 @@ int ti_gemm_w8a16(const void* w, const void* wscale, int n_tiles, int N, int K, 
   p.K = K;
   p.ldo = ldo;
   p.epi = epi;
-  const int tiles_n = (n_tiles * 8 + ti::kBM - 1) / ti::kBM, tiles_m = (M + BN - 1) / BN;
+  const int rows = ti::kBM * BMH;
+  const int tiles_n = (n_tiles * 8 + rows - 1) / rows, tiles_m = (M + BN - 1) / BN;
   const int S = ti::plan_split(p, KB, tiles_n * tiles_m, M, N, ldo, part, part_bytes, tile_count, n_count);
   dim3 grid(tiles_m, tiles_n, S);
   cudaStream_t st = (cudaStream_t)stream;
+  if (BMH == 2) return ti::launch_gemm<128, false, 2>(p, grid, st);
   if (BN == 32) return ti::launch_gemm<32, false>(p, grid, st);
   if (BN == 64) return ti::launch_gemm<64, false>(p, grid, st);
   return ti::launch_gemm<128, false>(p, grid, st);
@@ -545,7 +574,8 @@ int ti_gemm_bf16(const void* w, int n_tiles, int N, int K, const void* x, int M,
   ti::GemmParams p = {};
   const int KB = K / 32;                                       // 64-byte slabs
   const int BN = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
-  int rc = ti::cached_map(&p.map_w, w, KB, n_tiles, 0);
+  const int BMH = ti::pick_bmh(M, n_tiles);
+  int rc = ti::cached_map(&p.map_w, w, KB, n_tiles, BMH == 2 ? -32 : 0);
   if (rc) return rc;
   rc = ti::cached_map(&p.map_xh, x, 2 * K, M, BN);
   if (rc) return rc;
@@ -557,10 +587,12 @@ int ti_gemm_bf16(const void* w, int n_tiles, int N, int K, const void* x, int M,
   p.K = 2 * K;                                                 // bytes of k: the kernel counts 64-byte slabs
   p.ldo = ldo;
   p.epi = epi;
-  const int tiles_n = (n_tiles * 8 + ti::kBM - 1) / ti::kBM, tiles_m = (M + BN - 1) / BN;
+  const int rows = ti::kBM * BMH;
+  const int tiles_n = (n_tiles * 8 + rows - 1) / rows, tiles_m = (M + BN - 1) / BN;
   const int S = ti::plan_split(p, KB, tiles_n * tiles_m, M, N, ldo, part, part_bytes, tile_count, n_count);
   dim3 grid(tiles_m, tiles_n, S);
   cudaStream_t st = (cudaStream_t)stream;
+  if (BMH == 2) return ti::launch_gemm<128, true, 2>(p, grid, st);
   if (BN == 32) return ti::launch_gemm<32, true>(p, grid, st);
   if (BN == 64) return ti::launch_gemm<64, true>(p, grid, st);
   return ti::launch_gemm<128, true>(p, grid, st);

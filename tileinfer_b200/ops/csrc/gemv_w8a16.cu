@@ -62,6 +62,7 @@ struct GemvParams {
   int xll;                       // 1: x is the all-reduced output of the PREVIOUS product of the chain (row-parallel, tp > 1);
                                  // every CTA collects that product's packets itself instead of waiting for a collect pass
                                  // and a grid barrier
+  int* out_idx;                  // EPI_ARGMAX: [M][ncta] column of each CTA's candidate (`out`: float [M][ncta] values)
 };
 
 // Up to four dependent products run back to back in one launch (e.g. out_proj -> gate_up -> down -> the
@@ -85,7 +86,10 @@ TI_HOST_DEVICE size_t x_smem_bytes_impl(int wt, int xmode, int M, int K, int ksl
 }
 
 enum { XGLOBAL = 0, XNORM = 1 };
-enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ROWPAR = 2, EPI_F32 = 3 };
+// EPI_ARGMAX: nothing is stored per output; every warp keeps the best (value, column) of each activation row over the
+// row tiles it owns, the CTA reduces them, and writes ONE candidate per row and CTA to out / out_idx ([M][gridDim]):
+// the lm_head product fused with the first stage of the arg-max (greedy sampling needs no logits in memory).
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ROWPAR = 2, EPI_F32 = 3, EPI_ARGMAX = 4 };
 enum { W_INT8 = 0, W_BF16 = 1 };
 
 #ifndef TI_GEMV_WARPS
@@ -687,6 +691,9 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
   if (stamp) p0.dbg[cta * 32 + 1] = globaltimer_ns();
   if (lane == 0) ws.can_ticket = true;
 
+  // EPI_ARGMAX: best (value, column) seen by this lane for rows g and g + 8 over all the row tiles of its warp
+  float am_v0 = -INFINITY, am_v1 = -INFINITY;
+  int am_i0 = 0x7fffffff, am_i1 = 0x7fffffff;
   unsigned cidx = 0;                            // chunks consumed by this warp so far
   uint32_t cst = 0, cpar = 0;                   // ring stage / mbarrier phase of the next chunk to consume
   unsigned tcount = 0;                          // team exchanges of this warp in the current product
@@ -856,10 +863,20 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
             acc[2] += v.z;
             acc[3] += v.w;
           }
-          epilogue(p, grp * p.R + r, g, t, acc, pre);
+          if (p.epi != EPI_ARGMAX) epilogue(p, grp * p.R + r, g, t, acc, pre);
         }
-      } else {
+      } else if (p.epi != EPI_ARGMAX) {
         epilogue(p, grp * p.R + r, g, t, acc, pre);
+      }
+      if (p.epi == EPI_ARGMAX && (p.T == 1 || warp % p.T == 0)) {
+        const int n = (grp * p.R + r) * 8 + 2 * t;
+        if (n < p.N) {
+          const float a0 = acc[0] * pre.s0, a1 = acc[1] * pre.s1, b0 = acc[2] * pre.s0, b1 = acc[3] * pre.s1;
+          if (a0 > am_v0 || (a0 == am_v0 && n < am_i0)) { am_v0 = a0; am_i0 = n; }
+          if (n + 1 < p.N && (a1 > am_v0 || (a1 == am_v0 && n + 1 < am_i0))) { am_v0 = a1; am_i0 = n + 1; }
+          if (b0 > am_v1 || (b0 == am_v1 && n < am_i1)) { am_v1 = b0; am_i1 = n; }
+          if (n + 1 < p.N && (b1 > am_v1 || (b1 == am_v1 && n + 1 < am_i1))) { am_v1 = b1; am_i1 = n + 1; }
+        }
       }
     }
     if (stamp) p0.dbg[cta * 32 + 11 + 4 * op] = globaltimer_ns();
@@ -867,6 +884,40 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
   if (stamp) p0.dbg[cta * 32 + 5] = globaltimer_ns();
   // the last CTA of the launch resets the tickets and the barrier counter for the next launch
   __syncthreads();
+  const GemvParams& pl = c.op[c.n_ops - 1];
+  if (pl.epi == EPI_ARGMAX) {
+    // (an arg-max product is the last of its launch) warp -> shared memory -> one candidate per row of this CTA
+    float* sv = scratch;                                    // [kWarps][16] values, then [kWarps][16] columns
+    int* si = reinterpret_cast<int*>(scratch + kWarps * 16);
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+      const float ov0 = __shfl_xor_sync(0xffffffffu, am_v0, o), ov1 = __shfl_xor_sync(0xffffffffu, am_v1, o);
+      const int oi0 = __shfl_xor_sync(0xffffffffu, am_i0, o), oi1 = __shfl_xor_sync(0xffffffffu, am_i1, o);
+      if (ov0 > am_v0 || (ov0 == am_v0 && oi0 < am_i0)) { am_v0 = ov0; am_i0 = oi0; }
+      if (ov1 > am_v1 || (ov1 == am_v1 && oi1 < am_i1)) { am_v1 = ov1; am_i1 = oi1; }
+    }
+    if (t == 0) {
+      sv[warp * 16 + g] = am_v0;
+      si[warp * 16 + g] = am_i0;
+      sv[warp * 16 + g + 8] = am_v1;
+      si[warp * 16 + g + 8] = am_i1;
+    }
+    __syncthreads();
+    if (tid < pl.M) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int w = 0; w < kWarps; ++w) {
+        const float v = sv[w * 16 + tid];
+        const int i = si[w * 16 + tid];
+        if (v > bv || (v == bv && i < bi)) {
+          bv = v;
+          bi = i;
+        }
+      }
+      static_cast<float*>(pl.out)[(size_t)tid * pl.ldo + cta] = bv;
+      pl.out_idx[(size_t)tid * pl.ldo + cta] = bi == 0x7fffffff ? -1 : bi;
+    }
+  }
   if (tid == 0) {
     __threadfence();
     const int fin = atomicAdd(p0.sched + 1, 1);
@@ -912,7 +963,8 @@ static int check(const GemvParams& p, int wt) {
   if ((p.n_tiles + p.R - 1) / p.R >= kUnitMask) return -3;
   if (p.tps != kTPS) return -7;
   if (p.sched == nullptr || p.stages < 1 || p.stages > kMaxStages) return -7;
-  if (p.xmode < 0 || p.xmode > 1 || p.epi < 0 || p.epi > 3) return -8;
+  if (p.xmode < 0 || p.xmode > 1 || p.epi < 0 || p.epi > 4) return -8;
+  if (p.epi == EPI_ARGMAX && p.out_idx == nullptr) return -8;
   if (p.K % 8 || p.ldx % 8) return -4;
   if (p.tp > kMaxRanks || (p.tp > 1 && p.M > p.m_cap)) return -5;
   return 0;
@@ -930,6 +982,7 @@ static int prepare(ChainParams& c, int wt) {
       const GemvParams &q = c.op[i - 1], &p = c.op[i];
       if (q.epi != EPI_ROWPAR || q.tp < 2 || q.M != p.M || q.N != p.K || q.out != (void*)p.x || p.ldx != q.N) return -10;
     }
+    if (c.op[i].epi == EPI_ARGMAX && i != c.n_ops - 1) return -11;     // an arg-max product closes its launch
     xb = std::max(xb, op_x_bytes(c.op[i], wt));
   }
   c.x_bytes = xb;

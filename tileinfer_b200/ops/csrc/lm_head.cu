@@ -245,6 +245,15 @@ int ti_topk(const ti::TopkParams* p, void* stream) {
   return (int)cudaGetLastError();
 }
 
+// Merge + exchange only: ws_val / ws_idx [M][chunks][k] already hold per-chunk candidates (LOCAL column numbers).
+int ti_topk_merge(const ti::TopkParams* p, void* stream) {
+  if (p->M <= 0) return 0;
+  if (p->k < 1 || p->k > 64 || p->chunks < 1 || p->chunks * p->k > 8192) return -2;
+  if (p->tp > ti::kMaxRanks || (p->tp > 1 && p->M > p->m_cap)) return -5;
+  cudaError_t e = ti::launch_kernel(ti::topk_stage2_kernel, dim3(p->M), dim3(256), 0, (cudaStream_t)stream, true, *p);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
 }  // extern "C"
 
 // ------------------------------------------------------------------ allocation-free entry point

@@ -17,7 +17,7 @@ from .lib import ChainParams, GemvParams, MAX_CHAIN, MAX_RANKS, check, ptr, stre
 _I, _P, _F = ctypes.c_int, ctypes.c_void_p, ctypes.c_float
 
 XGLOBAL, XNORM = 0, 1
-EPI_STORE, EPI_SWIGLU, EPI_ROWPAR, EPI_F32 = 0, 1, 2, 3
+EPI_STORE, EPI_SWIGLU, EPI_ROWPAR, EPI_F32, EPI_ARGMAX = 0, 1, 2, 3, 4
 W_INT8, W_BF16 = 0, 1
 
 
@@ -115,6 +115,7 @@ _l.register("ti_attn_paged", _I, [ctypes.POINTER(AttnParams), _I, _P])
 _l.register("ti_attn_prefill", _I, [_P, _I, _P, _P, _I, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P])
 _l.register("ti_topk_params_size", _I, [])
 _l.register("ti_topk", _I, [ctypes.POINTER(TopkParams), _P])
+_l.register("ti_topk_merge", _I, [ctypes.POINTER(TopkParams), _P])
 _l.register("ti_symm_alloc", _I, [ctypes.POINTER(_P), ctypes.c_size_t])
 _l.register("ti_symm_free", _I, [_P])
 _l.register("ti_ipc_handle_size", _I, [])
@@ -302,10 +303,11 @@ def default_workspace():
 
 
 def make_gemv_params(W: LinearW, x, out, M, *, xmode=XGLOBAL, epi=EPI_STORE, norm_w=None, resid=None, ws=None,
-                     eps=1e-6, ldx=None, ldo=None, comm=None, order=0, ncta=NUM_SMS, team=None, xll=False) -> GemvParams:
+                     eps=1e-6, ldx=None, ldo=None, comm=None, order=0, ncta=NUM_SMS, team=None, xll=False,
+                     out_idx=None) -> GemvParams:
     p = GemvParams()
     p.w, p.scale, p.x, p.norm_w = ptr(W.tiles), ptr(W.scale), ptr(x), ptr(norm_w)
-    p.out, p.resid = ptr(out), ptr(resid)
+    p.out, p.resid, p.out_idx = ptr(out), ptr(resid), ptr(out_idx)
     plan = plan_gemv(W.wt, xmode, M, W.n_tiles, W.KB, ncta)
     if plan is None:
         raise ValueError(f"{M} rows of K={W.K} do not fit in shared memory; split the rows (max_rows)")
@@ -531,6 +533,12 @@ def sample(p: SampleParams):
 
 def topk(p: TopkParams):
     check(L().ti_topk(ctypes.byref(p), stream()), "ti_topk")
+
+
+def topk_merge(p: TopkParams):
+    """Second stage only: merges the per-chunk candidates already in ws_val / ws_idx (written, for instance, by the
+    arg-max epilogue of the lm_head GEMV: one candidate per row and CTA) and exchanges the winners between ranks."""
+    check(L().ti_topk_merge(ctypes.byref(p), stream()), "ti_topk_merge")
 
 
 # ------------------------------------------------------------------------------------ prefill GEMM (tcgen05)

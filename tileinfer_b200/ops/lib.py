@@ -26,7 +26,7 @@ class GemvParams(ctypes.Structure):
         ("KB", ctypes.c_int), ("S", ctypes.c_int), ("kb_per_split", ctypes.c_int),
         ("ldx", ctypes.c_int), ("ldo", ctypes.c_int),
         ("tp", ctypes.c_int), ("rank", ctypes.c_int), ("order", ctypes.c_int), ("m_cap", ctypes.c_int),
-        ("eps", ctypes.c_float), ("stages", ctypes.c_int), ("T", ctypes.c_int), ("dbg", ctypes.c_void_p), ("sched", ctypes.c_void_p), ("tps", ctypes.c_int), ("xmode", ctypes.c_int), ("epi", ctypes.c_int), ("R", ctypes.c_int), ("xll", ctypes.c_int),
+        ("eps", ctypes.c_float), ("stages", ctypes.c_int), ("T", ctypes.c_int), ("dbg", ctypes.c_void_p), ("sched", ctypes.c_void_p), ("tps", ctypes.c_int), ("xmode", ctypes.c_int), ("epi", ctypes.c_int), ("R", ctypes.c_int), ("xll", ctypes.c_int), ("out_idx", ctypes.c_void_p),
     ]
 
 
