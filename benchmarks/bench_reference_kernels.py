@@ -24,24 +24,44 @@ BF16 = torch.bfloat16
 
 
 def timed(fn, iters=30, warm=5):
+    """us per call and how it was launched: inside a CUDA graph of `iters` calls where the kernel can be captured
+    (device time without host launch overhead: how a decode step runs it), else eagerly back to back."""
     for i in range(warm):
         fn(i)
     torch.cuda.synchronize()
+    how, g = "graph", torch.cuda.CUDAGraph()
+    try:
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(g, stream=s):
+                for i in range(iters):
+                    fn(i)
+        torch.cuda.current_stream().wait_stream(s)
+        g.replay()
+        torch.cuda.synchronize()
+        run = g.replay
+    except Exception:                              # noqa: BLE001  (not capturable: time it eagerly)
+        how = "eager"
+        torch.cuda.synchronize()
+
+        def run():
+            for i in range(iters):
+                fn(i)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(iters):
-        fn(warm + i)
+    run()
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) * 1e3 / iters
+    return e0.elapsed_time(e1) * 1e3 / iters, how
 
 
 def guarded(name, rows, build):
     """Runs build() -> (callable, note); records its time or the one-line error."""
     try:
         fn, note = build()
-        us = timed(fn)
-        rows.append({"kernel": name, "impl": "reference", "us": round(us, 2), "note": note})
+        us, how = timed(fn)
+        rows.append({"kernel": name, "impl": "reference", "us": round(us, 2), "launch": how, "note": note})
     except Exception as e:                       # noqa: BLE001  (the record IS the result)
         rows.append({"kernel": name, "impl": "reference", "error": f"{type(e).__name__}: {str(e)[:160]}".replace("\n", " ")})
     print(json.dumps(rows[-1]), flush=True)
@@ -67,8 +87,9 @@ def main():
         x = torch.randn(1, K, device="cuda").to(BF16)
         ours = [F.LinearW(w, True) for w in ws]
         out = torch.zeros(1, N, dtype=BF16, device="cuda")
-        us = timed(lambda i: F.gemv(ours[i % ncopy], x, out=out))
-        rows.append({"kernel": f"gemv_w8a16 {name} N={N} K={K}", "impl": "tileinfer_b200", "us": round(us, 2),
+        ps = [F.make_gemv_params(W, x, out, 1) for W in ours]
+        us, how = timed(lambda i: F.gemv_launch(ps[i % ncopy], F.W_INT8))
+        rows.append({"kernel": f"gemv_w8a16 {name} N={N} K={K}", "impl": "tileinfer_b200", "us": round(us, 2), "launch": how,
                      "weight_gbs": round(N * K / us / 1e3, 1)})
         print(json.dumps(rows[-1]), flush=True)
         if have_ref:
@@ -87,11 +108,12 @@ def main():
     w = torch.zeros(5120, dtype=BF16, device="cuda")
     o = torch.zeros_like(h)
     r = torch.zeros_like(h)
-    rows.append({"kernel": "rmsnorm 1x5120", "impl": "tileinfer_b200", "us": round(timed(lambda i: F.rmsnorm(h, w, 1e-6, out=o)), 2),
+    us, how = timed(lambda i: F.rmsnorm(h, w, 1e-6, out=o))
+    rows.append({"kernel": "rmsnorm 1x5120", "impl": "tileinfer_b200", "us": round(us, 2), "launch": how,
                  "note": "stand-alone form; in the decode step the norm is the prologue of the consuming GEMV (no launch)"})
     print(json.dumps(rows[-1]), flush=True)
-    rows.append({"kernel": "residual+rmsnorm 1x5120", "impl": "tileinfer_b200",
-                 "us": round(timed(lambda i: F.rmsnorm(h, w, 1e-6, add=h, out=o, r_out=r)), 2)})
+    us, how = timed(lambda i: F.rmsnorm(h, w, 1e-6, add=h, out=o, r_out=r))
+    rows.append({"kernel": "residual+rmsnorm 1x5120", "impl": "tileinfer_b200", "us": round(us, 2), "launch": how})
     print(json.dumps(rows[-1]), flush=True)
     if have_ref:
         def build_norm():
@@ -127,8 +149,9 @@ def main():
         a.o_part, a.ml_part, a.gate_src, a.out = o_part.data_ptr(), ml.data_ptr(), proj.data_ptr(), out.data_ptr()
         a.hq, a.hkv, a.max_blocks, a.nsplit, a.ld, a.num_qg = hq, hkv, nb_seq, nsplit, proj.shape[1], B
         a.scale_log2e = D ** -0.5 * 1.4426950408889634
-        rows.append({"kernel": f"paged decode attention B={B} ctx={ctx}", "impl": "tileinfer_b200",
-                     "us": round(timed(lambda i: F.attn_paged(a, D)), 2), "note": "split-KV + merge + sigmoid gate (2 launches)"})
+        us, how = timed(lambda i: F.attn_paged(a, D))
+        rows.append({"kernel": f"paged decode attention B={B} ctx={ctx}", "impl": "tileinfer_b200", "us": round(us, 2),
+                     "launch": how, "note": "split-KV + merge + sigmoid gate (2 launches)"})
         print(json.dumps(rows[-1]), flush=True)
         if have_ref:
             def build_attn(B=B, q=q, ctx=ctx, hq=hq, hkv=hkv, D=D, nb_seq=nb_seq, nblocks=nblocks, bt=bt):
@@ -155,8 +178,9 @@ def main():
     p.proj, p.conv_w, p.neg_a_exp, p.dt_bias, p.norm_w = proj.data_ptr(), conv_w.data_ptr(), neg.data_ptr(), dtb.data_ptr(), nw.data_ptr()
     p.state, p.conv_state, p.slots, p.cu, p.out = state.data_ptr(), cs.data_ptr(), slots.data_ptr(), cu.data_ptr(), outg.data_ptr()
     p.ld, p.hk, p.hv, p.eps = ld, hk, hv, 1e-6
+    us, how = timed(lambda i: F.gdn_step(p, 1, dk, dv, False, single=True))
     rows.append({"kernel": "DeltaNet decode step B=1 (conv + delta rule + gated norm, in place, fp32 state)", "impl": "tileinfer_b200",
-                 "us": round(timed(lambda i: F.gdn_step(p, 1, dk, dv, False, single=True)), 2)})
+                 "us": round(us, 2), "launch": how})
     print(json.dumps(rows[-1]), flush=True)
     if have_ref:
         def build_gdn():

@@ -922,14 +922,18 @@ def test_two_limb_activation_format_on_outlier_rows(shift):
     torch.manual_seed(shift)
     N, K = 1024, 5120
     w = _rand_w(N, K, seed=shift)
+    from tileinfer_b200.models.weights import untile_int8
     W = F.LinearW(w, True)
-    wd = W.dense().double()                                     # the dequantised weights the kernel multiplies with
-    Wb = F.LinearW(W.dense().float(), False)                    # the same values as bf16 weights
+    # exactly what the kernel multiplies with: int8 values times the bf16 row scales, no intermediate rounding
+    wd = untile_int8(W.tiles)[:N].double() * W.scale.double()[:N, None]
+    Wb = F.LinearW(W.dense().float(), False)                    # (nearly) the same values as bf16 weights
+    wbd = Wb.dense().double()
     for M in (1, 4, 64):
         x = torch.randn(M, K, device="cuda")
         x[:, 77] = 2.0 ** shift * (1 + 0.25 * torch.rand(M, device="cuda"))
         x = x.to(BF16)
         ref = x.double() @ wd.t()
+        refb = x.double() @ wbd.t()
         if M <= 8:
             y = F.gemv(W, x).double()
             yb = F.gemv(Wb, x).double()
@@ -941,10 +945,10 @@ def test_two_limb_activation_format_on_outlier_rows(shift):
         unit = torch.exp2(e - 14)[:, None]
         sigma = unit / math.sqrt(12.0) * wd.norm(dim=1)[None, :]
         bound = 6.0 * sigma + 2.0 ** -8 * ref.abs() + 1e-3
-        err, errb = (y - ref).abs(), (yb - ref).abs()
+        err, errb = (y - ref).abs(), (yb - refb).abs()
         assert bool((err <= bound).all()), f"M={M}: worst excess {float((err - bound).max())}"
         # the bf16-activation path is limited by the output rounding alone
-        assert bool((errb <= 2.0 ** -8 * ref.abs() + 1e-3).all())
+        assert bool((errb <= 2.0 ** -8 * refb.abs() + 1e-3).all())
         # how much is lost: error of the fixed-point form in units of the part of the output that does NOT come from
         # the outlier channel (what later layers can still distinguish)
         rest = (x.double() @ wd.t() - x[:, 77:78].double() * wd[:, 77][None, :]).abs().mean()

@@ -23,7 +23,8 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
               "-DTI_GEMV_WARPS=" + os.environ.get("TI_GEMV_WARPS", "16"),
               "-DTI_GEMV_TPS=" + os.environ.get("TI_GEMV_TPS", "8"),
-              "-DTI_GEMM_RING_KB=" + os.environ.get("TI_GEMM_RING_KB", "192")]
+              "-DTI_GEMM_RING_KB=" + os.environ.get("TI_GEMM_RING_KB", "192"),
+              "-DTI_GEMV_PREFETCH_KB=" + os.environ.get("TI_GEMV_PREFETCH_KB", "24")]
 
 
 def _nvcc() -> str:

@@ -69,7 +69,7 @@ TI_DEVICE void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.r
 TI_DEVICE void bulk_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
 
 template <int DK, int DV, typename ST, bool STAGED>
-__global__ void __launch_bounds__(DV * 4) gdn_token_kernel(const __grid_constant__ GdnParams p, int num_seqs) {
+__global__ void __launch_bounds__(DV * 4, STAGED ? 1 : 2) gdn_token_kernel(const __grid_constant__ GdnParams p, int num_seqs) {
   constexpr int DPT = DK / 4;           // state elements per thread
   constexpr int NCH = 2 * DK + DV;      // conv channels this block needs
   constexpr int NW = DV * 4 / 32;
@@ -580,7 +580,11 @@ int ti_gdn_step(const ti::GdnParams* p, int num_seqs, int dk, int dv, int state_
   cudaError_t e;
   if (split == 2) {                     // one token per sequence: the single-pass decode kernel
     // more (head, sequence) pairs than two waves of SMs: blocks walk several sequences with staged state
-    const bool staged = (long long)p->hv * num_seqs > 2 * 148;
+    static const int staged_mode = [] {
+      const char* e = getenv("TI_GDN_STAGED");              // 0: never, 1: always, unset: by batch size
+      return e == nullptr ? -1 : atoi(e);
+    }();
+    const bool staged = staged_mode >= 0 ? staged_mode == 1 : (long long)p->hv * num_seqs > 2 * 148;
     const int gy = staged ? std::max(1, 148 / p->hv) : num_seqs;
     dim3 grid(p->hv, gy);
     if (dk == 128 && dv == 128) {

@@ -620,6 +620,42 @@ struct WarpStream {           // registers of lane 0 of each warp; queue storage
   }
 };
 
+// While the previous kernel of the stream is still running (before griddepcontrol.wait) the rings hold only a few
+// stages per warp; what follows them in this warp's first unit of the first two products is asked into L2, so that
+// HBM keeps working through the token-mixer kernel that precedes a chain and the rings then refill from L2.
+#ifndef TI_GEMV_PREFETCH_KB
+#define TI_GEMV_PREFETCH_KB 24
+#endif
+TI_DEVICE void l2_prefetch(const void* ptr, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(ptr), "r"(bytes) : "memory");
+}
+TI_DEVICE void prefetch_ahead(const ChainParams& c, const int* tb, int stages) {
+  int budget = TI_GEMV_PREFETCH_KB * 1024;
+  int skip = stages * kTPS * 512;                      // already requested through the ring
+  for (int op = 0; op < c.n_ops && op < 2 && budget > 0; ++op) {
+    const int* t = tb + op * TB_N;
+    const GemvParams& p = c.op[op];
+    const int u = t[TB_WIDX];
+    if (t[TB_NS] >= 1 && u < t[TB_U]) {
+      int kt0, run;
+      my_slice(tb, op, kt0, run);
+      const int rn = min(p.R, p.n_tiles - u * p.R);
+      for (int r = 0; r < rn && budget > 0; ++r) {
+        const uint8_t* base = p.w + ((size_t)(u * p.R + r) * p.KB + kt0) * 512;
+        const int bytes = run * 512;
+        const int off = min(skip, bytes);
+        skip -= off;
+        const int n = min(bytes - off, budget);
+        if (n > 0) {
+          l2_prefetch(base + off, (uint32_t)n);
+          budget -= n;
+        }
+      }
+    }
+    skip = 0;
+  }
+}
+
 // Grid-wide barrier between chained products.  All CTAs of the launch are resident (one per SM), the
 // counter is reset by the last CTA of the launch.  The wait is bounded like every other wait here.
 TI_DEVICE void grid_barrier(int* counter, int target, unsigned* status, unsigned long long* arrived = nullptr) {
@@ -681,6 +717,7 @@ TI_DEVICE void gemv_body(const ChainParams& c, int cta, int ncta, uint8_t* smem)
     for (int s = 0; s < stages; ++s) mbar_init(bar0 + s * 8, 1);
     fence_mbar_init();
     for (int s = 0; s < stages; ++s) ws.next(c, widx, W, q, ring_u32, bar0, stages);   // static units only
+    if (TI_GEMV_PREFETCH_KB > 0) prefetch_ahead(c, tb, stages);
   }
   __syncwarp();
   // Everything above touched only weights and this CTA's shared memory.  Let the next kernel of the
