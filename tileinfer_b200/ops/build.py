@@ -24,7 +24,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-DTI_GEMV_WARPS=" + os.environ.get("TI_GEMV_WARPS", "16"),
               "-DTI_GEMV_TPS=" + os.environ.get("TI_GEMV_TPS", "8"),
               "-DTI_GEMM_RING_KB=" + os.environ.get("TI_GEMM_RING_KB", "192"),
-              "-DTI_GEMV_PREFETCH_KB=" + os.environ.get("TI_GEMV_PREFETCH_KB", "24")]
+              "-DTI_GEMV_PREFETCH_KB=" + os.environ.get("TI_GEMV_PREFETCH_KB", "0")]
 
 
 def _nvcc() -> str:

@@ -69,7 +69,7 @@ TI_DEVICE void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.r
 TI_DEVICE void bulk_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
 
 template <int DK, int DV, typename ST, bool STAGED>
-__global__ void __launch_bounds__(DV * 4, STAGED ? 1 : 2) gdn_token_kernel(const __grid_constant__ GdnParams p, int num_seqs) {
+__global__ void __launch_bounds__(DV * 4) gdn_token_kernel(const __grid_constant__ GdnParams p, int num_seqs) {
   constexpr int DPT = DK / 4;           // state elements per thread
   constexpr int NCH = 2 * DK + DV;      // conv channels this block needs
   constexpr int NW = DV * 4 / 32;

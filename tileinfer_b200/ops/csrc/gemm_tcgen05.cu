@@ -489,7 +489,16 @@ static int pick_bmh(int M, int n_tiles) {
   }();
   if (forced == 1 || forced == 2) return n_tiles >= 32 ? forced : 1;
   const long long tiles256 = (long long)((n_tiles * 8 + 255) / 256) * ((M + 127) / 128);
-  return (M > 64 && n_tiles >= 32 && tiles256 >= 2 * 148) ? 2 : 1;
+  if (M <= 64) {
+    // few tokens: the limb planes are as many bytes per stage as the weights of a 128-row tile; with 256 rows they
+    // are a third (the k split of plan_split fills the SMs when there are few row tiles).  TI_GEMM_BMH_SMALL=0: off
+    static const int small = [] {
+      const char* e = getenv("TI_GEMM_BMH_SMALL");
+      return e == nullptr ? 1 : atoi(e);
+    }();
+    return (small && n_tiles >= 64) ? 2 : 1;
+  }
+  return (n_tiles >= 32 && tiles256 >= 2 * 148) ? 2 : 1;
 }
 
 // k split that fills the 148 SMs when there are few output tiles (at least 16 slabs per slice); sets kb_per_split
@@ -559,6 +568,8 @@ int ti_gemm_w8a16(const void* w, const void* wscale, int n_tiles, int N, int K, 
   const int S = ti::plan_split(p, KB, tiles_n * tiles_m, M, N, ldo, part, part_bytes, tile_count, n_count);
   dim3 grid(tiles_m, tiles_n, S);
   cudaStream_t st = (cudaStream_t)stream;
+  if (BMH == 2 && BN == 32) return ti::launch_gemm<32, false, 2>(p, grid, st);
+  if (BMH == 2 && BN == 64) return ti::launch_gemm<64, false, 2>(p, grid, st);
   if (BMH == 2) return ti::launch_gemm<128, false, 2>(p, grid, st);
   if (BN == 32) return ti::launch_gemm<32, false>(p, grid, st);
   if (BN == 64) return ti::launch_gemm<64, false>(p, grid, st);
@@ -592,6 +603,8 @@ int ti_gemm_bf16(const void* w, int n_tiles, int N, int K, const void* x, int M,
   const int S = ti::plan_split(p, KB, tiles_n * tiles_m, M, N, ldo, part, part_bytes, tile_count, n_count);
   dim3 grid(tiles_m, tiles_n, S);
   cudaStream_t st = (cudaStream_t)stream;
+  if (BMH == 2 && BN == 32) return ti::launch_gemm<32, true, 2>(p, grid, st);
+  if (BMH == 2 && BN == 64) return ti::launch_gemm<64, true, 2>(p, grid, st);
   if (BMH == 2) return ti::launch_gemm<128, true, 2>(p, grid, st);
   if (BN == 32) return ti::launch_gemm<32, true>(p, grid, st);
   if (BN == 64) return ti::launch_gemm<64, true>(p, grid, st);

@@ -620,11 +620,13 @@ struct WarpStream {           // registers of lane 0 of each warp; queue storage
   }
 };
 
-// While the previous kernel of the stream is still running (before griddepcontrol.wait) the rings hold only a few
-// stages per warp; what follows them in this warp's first unit of the first two products is asked into L2, so that
-// HBM keeps working through the token-mixer kernel that precedes a chain and the rings then refill from L2.
+// Optional (-DTI_GEMV_PREFETCH_KB=n, off by default): while the previous kernel of the stream is still running
+// (before griddepcontrol.wait) the rings hold only a few stages per warp; what follows them in this warp's first unit
+// of the first two products can be asked into L2.  Measured with 24 KB per warp on the 27B layer: the chain alone
+// 87.5 -> 90.5 us and the decode step 6.70 -> 7.0 ms: the prefetches compete with the ring fills of all warps for the
+// same HBM queue at the moment the chain starts, so it stays off.
 #ifndef TI_GEMV_PREFETCH_KB
-#define TI_GEMV_PREFETCH_KB 24
+#define TI_GEMV_PREFETCH_KB 0
 #endif
 TI_DEVICE void l2_prefetch(const void* ptr, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(ptr), "r"(bytes) : "memory");
