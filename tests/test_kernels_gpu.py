@@ -954,3 +954,16 @@ def test_two_limb_activation_format_on_outlier_rows(shift):
         rest = (x.double() @ wd.t() - x[:, 77:78].double() * wd[:, 77][None, :]).abs().mean()
         rel = float(err.mean() / rest)
         assert rel < (0.05 if shift == 10 else 0.4), rel
+
+
+def test_paged_attention_pipelined_kernel():
+    """The cp.async-pipelined decode attention kernel (chosen by itself for large decode batches) on the cases of
+    test_paged_attention_prefill_and_decode: forced with TI_ATTN_PIPE=1 in a child process."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_kernels_gpu.py"), "-q", "-x", "-k",
+                        "test_paged_attention_prefill_and_decode"], capture_output=True, text=True,
+                       env=dict(os.environ, TI_ATTN_PIPE="1"), timeout=600, cwd=root)
+    assert r.returncode == 0 and "4 passed" in r.stdout, (r.stdout[-2500:], r.stderr[-1000:])

@@ -580,11 +580,7 @@ int ti_gdn_step(const ti::GdnParams* p, int num_seqs, int dk, int dv, int state_
   cudaError_t e;
   if (split == 2) {                     // one token per sequence: the single-pass decode kernel
     // more (head, sequence) pairs than two waves of SMs: blocks walk several sequences with staged state
-    static const int staged_mode = [] {
-      const char* e = getenv("TI_GDN_STAGED");              // 0: never, 1: always, unset: by batch size
-      return e == nullptr ? -1 : atoi(e);
-    }();
-    const bool staged = staged_mode >= 0 ? staged_mode == 1 : (long long)p->hv * num_seqs > 2 * 148;
+    const bool staged = (long long)p->hv * num_seqs > 2 * 148;
     const int gy = staged ? std::max(1, 148 / p->hv) : num_seqs;
     dim3 grid(p->hv, gy);
     if (dk == 128 && dv == 128) {

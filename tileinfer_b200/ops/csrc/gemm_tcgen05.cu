@@ -491,10 +491,12 @@ static int pick_bmh(int M, int n_tiles) {
   const long long tiles256 = (long long)((n_tiles * 8 + 255) / 256) * ((M + 127) / 128);
   if (M <= 64) {
     // few tokens: the limb planes are as many bytes per stage as the weights of a 128-row tile; with 256 rows they
-    // are a third (the k split of plan_split fills the SMs when there are few row tiles).  TI_GEMM_BMH_SMALL=0: off
+    // would be a third.  Measured at 64 tokens on the 27B shapes: in_proj 32.7 -> 62.8 us, down 51 -> 91 us, out_proj
+    // 38 -> 72 us, gate_up 65 -> 62 us: halving the number of CTAs (and the deeper k split it forces) costs more
+    // than the bytes saved, so this stays off (TI_GEMM_BMH_SMALL=1 turns it on).
     static const int small = [] {
       const char* e = getenv("TI_GEMM_BMH_SMALL");
-      return e == nullptr ? 1 : atoi(e);
+      return e == nullptr ? 0 : atoi(e);
     }();
     return (small && n_tiles >= 64) ? 2 : 1;
   }
