@@ -141,7 +141,7 @@ def main():
         rows.append({"op": "prefill_tcgen05", "tokens": 8192, "heads": f"{hq_}q/{hkv_}kv", "D": D, "ms": round(ms, 3),
                      "tflops": round(tf, 1), f"fraction_of_{how}_bf16_sustained": round(tf / tflops_peak, 3)})
         print(json.dumps(rows[-1]), flush=True)
-    for B, ctx in ((1, 4096), (1, 32768), (64, 2048), (64, 8192)):
+    for B, ctx in ((1, 256), (1, 1024), (1, 4096), (1, 32768), (16, 2048), (64, 2048), (64, 8192)):
         ms, gbs = decode_case(F, B, ctx, hq, hkv, D, flush)
         rows.append({"op": "decode_paged_splitkv", "batch": B, "context": ctx, "ms": round(ms, 4), "kv_gbs": round(gbs, 1),
                      f"fraction_of_{how}_hbm": round(gbs / hbm, 3)})

@@ -553,10 +553,12 @@ def test_gemv_rowpar_handoff_to_next_product_emulated_ranks(tp, M):
         assert torch.equal(hs[r], hs[0]) and torch.equal(projs[r], projs[0])
 
 
+@pytest.mark.parametrize("staged", [False, True])
 @pytest.mark.parametrize("state_bf16", [False, True])
-def test_gdn_decode_many_sequences_staged(state_bf16):
-    """64 single-token sequences x 6 heads: the decode kernel walks several sequences per block with the state
-    staged through shared memory (bulk copies, inputs fetched one sequence ahead).  Must equal the tiled kernel."""
+def test_gdn_decode_many_sequences_staged(state_bf16, staged):
+    """64 single-token sequences x 6 heads, the two decode kernels for large batches: column-split blocks (a cluster
+    of four blocks per head and sequence, 32 state columns each), and blocks that walk several sequences with the state
+    staged through shared memory (bulk copies, inputs fetched one sequence ahead).  Both must equal the tiled kernel."""
     F = _F()
     torch.manual_seed(1)
     dk = dv = 128
@@ -581,7 +583,7 @@ def test_gdn_decode_many_sequences_staged(state_bf16):
         p.dt_bias, p.norm_w = dt_bias.data_ptr(), norm_w.data_ptr()
         p.state, p.conv_state, p.slots, p.out = state.data_ptr(), cs.data_ptr(), slots.data_ptr(), out.data_ptr()
         p.ld, p.hk, p.hv, p.eps = ld, hk, hv, 1e-6
-        F.gdn_step(p, S, dk, dv, state_bf16, single=single)
+        F.gdn_step(p, S, dk, dv, state_bf16, single=single, staged=staged and single)
         torch.cuda.synchronize()
         outs.append((out, state, cs))
     (o1, s1, c1), (o2, s2, c2) = outs
@@ -956,14 +958,15 @@ def test_two_limb_activation_format_on_outlier_rows(shift):
         assert rel < (0.05 if shift == 10 else 0.4), rel
 
 
-def test_paged_attention_pipelined_kernel():
-    """The cp.async-pipelined decode attention kernel (chosen by itself for large decode batches) on the cases of
-    test_paged_attention_prefill_and_decode: forced with TI_ATTN_PIPE=1 in a child process."""
+def test_paged_attention_direct_load_kernel():
+    """The paged attention kernel has two forms: the cp.async-pipelined one (the default, exercised by
+    test_paged_attention_prefill_and_decode) and the direct-load one; this runs the same cases on the second,
+    forced with TI_ATTN_PIPE=0 in a child process."""
     import os
     import subprocess
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_kernels_gpu.py"), "-q", "-x", "-k",
                         "test_paged_attention_prefill_and_decode"], capture_output=True, text=True,
-                       env=dict(os.environ, TI_ATTN_PIPE="1"), timeout=600, cwd=root)
+                       env=dict(os.environ, TI_ATTN_PIPE="0"), timeout=600, cwd=root)
     assert r.returncode == 0 and "4 passed" in r.stdout, (r.stdout[-2500:], r.stderr[-1000:])

@@ -291,6 +291,138 @@ TI_DEVICE float ld_cluster_f32(const float* local, int rank) {
   return v;
 }
 
+// Large decode batches: the state columns of a head are dealt to NSPL small blocks (32 columns x DK rows = 16 KB of
+// fp32 state each), one block per (sequence, v-head, column part): thousands of independent blocks keep two dozen warps
+// per SM in flight, 4 KB of loads each, which streams the recurrent state at HBM speed without any staging (the staged kernel above
+// walks ~20 sequences per block one after the other and reaches a third of it).  A warp owns a quarter of the key
+// rows and 32 consecutive columns, so every state access is one full 128-byte line; the two matrix-vector
+// products meet across the four warps in shared memory.  The gated RMSNorm spans the whole head: this kernel writes
+// the un-normalised output and gdn_finish_kernel applies norm * silu(z) in place.  The NSPL blocks of a head form a
+// thread-block cluster (they share the q / k conv history).
+template <int DK, int DV, typename ST>
+__global__ void __launch_bounds__(128) gdn_token_split_kernel(const __grid_constant__ GdnParams p) {
+  constexpr int CB = 32, NSPL = DV / CB, DPT = DK / 4;
+  constexpr int NCH = 2 * DK + DV, NCHL = 2 * DK + CB;
+  constexpr int NCPT = (NCHL + 127) / 128;
+  __shared__ float qs[DK], ks[DK], vs[CB], red[2][4], part_s[2][4][CB];
+  const int tid = threadIdx.x, lane = tid & 31, dg = tid >> 5;      // warp = quarter of the key rows
+  const int c = lane;
+  const int part = blockIdx.x % NSPL, vh = blockIdx.x / NSPL, s = blockIdx.y;
+  const int kh = vh / (p.hv / p.hk);
+  const int slot = p.slots[s];
+  const int tok = p.cu ? p.cu[s] : s;
+  ST* Sp = static_cast<ST*>(p.state) + ((size_t)slot * p.hv + vh) * DK * DV + part * CB + c;
+  float S[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) S[i] = ld_state<ST>(Sp + (size_t)(dg * DPT + i) * DV);     // last written a step ago
+  __nv_bfloat16* cs = p.conv_state + ((size_t)slot * p.hv + vh) * 3 * NCH;
+  float x0[NCPT], x1[NCPT], x2[NCPT], cw[NCPT][4];
+  int col[NCPT], hch[NCPT];
+#pragma unroll
+  for (int u = 0; u < NCPT; ++u) {
+    const int ch = tid + u * 128;
+    x0[u] = x1[u] = x2[u] = 0.f;
+    col[u] = hch[u] = 0;
+    cw[u][0] = cw[u][1] = cw[u][2] = cw[u][3] = 0.f;
+    if (ch < NCHL) {
+      if (ch < DK) { col[u] = kh * DK + ch; hch[u] = ch; }
+      else if (ch < 2 * DK) { col[u] = p.hk * DK + kh * DK + (ch - DK); hch[u] = ch; }
+      else { col[u] = 2 * p.hk * DK + vh * DV + part * CB + (ch - 2 * DK); hch[u] = 2 * DK + part * CB + (ch - 2 * DK); }
+      const float4 w = *reinterpret_cast<const float4*>(p.conv_w + (size_t)col[u] * 4);
+      cw[u][0] = w.x; cw[u][1] = w.y; cw[u][2] = w.z; cw[u][3] = w.w;
+      x0[u] = __bfloat162float(cs[hch[u]]);
+      x1[u] = __bfloat162float(cs[NCH + hch[u]]);
+      x2[u] = __bfloat162float(cs[2 * NCH + hch[u]]);
+    }
+  }
+  const float neg_a = p.neg_a_exp[vh], dtb = p.dt_bias[vh];
+  const int bcol = 2 * p.hk * DK + 2 * p.hv * DV + vh, acol = bcol + p.hv;
+  pdl_trigger();
+  pdl_wait();                                              // `proj` comes from the preceding projection kernel
+  const __nv_bfloat16* row = p.proj + (size_t)tok * p.ld;
+#pragma unroll
+  for (int u = 0; u < NCPT; ++u) {
+    const int ch = tid + u * 128;
+    if (ch < NCHL) {
+      const float x3 = __bfloat162float(row[col[u]]);
+      const float y = silu_f(cw[u][0] * x0[u] + cw[u][1] * x1[u] + cw[u][2] * x2[u] + cw[u][3] * x3);
+      if (ch < DK) qs[ch] = y;
+      else if (ch < 2 * DK) ks[ch - DK] = y;
+      else vs[ch - 2 * DK] = y;
+      x0[u] = x3;                                          // kept for the history update below
+    }
+  }
+  // The q / k history of a head is read by all NSPL blocks of the cluster and written by part 0: nobody writes
+  // before every block of the cluster has read (the blocks of a cluster are co-scheduled).
+  cluster_sync_all();
+#pragma unroll
+  for (int u = 0; u < NCPT; ++u) {
+    const int ch = tid + u * 128;
+    if (ch < NCHL && (part == 0 || ch >= 2 * DK)) {
+      cs[hch[u]] = __float2bfloat16_rn(x1[u]);
+      cs[NCH + hch[u]] = __float2bfloat16_rn(x2[u]);
+      cs[2 * NCH + hch[u]] = __float2bfloat16_rn(x0[u]);
+    }
+  }
+  __syncthreads();
+  float sq = 0.f, sk = 0.f;
+  for (int i = tid; i < DK; i += 128) { sq += qs[i] * qs[i]; sk += ks[i] * ks[i]; }
+  sq = warp_sum(sq);
+  sk = warp_sum(sk);
+  if (lane == 0) { red[0][dg] = sq; red[1][dg] = sk; }
+  const float a = __bfloat162float(row[acol]) + dtb;
+  const float sp = a > 20.f ? a : log1pf(__expf(a));
+  const float decay = __expf(neg_a * sp);
+  const float beta = sigmoid_f(__bfloat162float(row[bcol]));
+  __syncthreads();
+  const float qn = rsqrtf(red[0][0] + red[0][1] + red[0][2] + red[0][3] + 1e-6f) * rsqrtf((float)DK);
+  const float kn = rsqrtf(red[1][0] + red[1][1] + red[1][2] + red[1][3] + 1e-6f);
+  float kv = 0.f;
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) { S[i] *= decay; kv += S[i] * ks[dg * DPT + i]; }
+  part_s[0][dg][c] = kv;
+  __syncthreads();
+  kv = part_s[0][0][c] + part_s[0][1][c] + part_s[0][2][c] + part_s[0][3][c];
+  const float kd = kn * (vs[c] - kv * kn) * beta;
+  float o = 0.f;
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) { S[i] += ks[dg * DPT + i] * kd; o += S[i] * qs[dg * DPT + i]; }
+  part_s[1][dg][c] = o;
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) st_state<ST>(Sp + (size_t)(dg * DPT + i) * DV, S[i]);
+  __syncthreads();
+  if (dg == 0) {
+    o = (part_s[1][0][c] + part_s[1][1][c] + part_s[1][2][c] + part_s[1][3][c]) * qn;
+    p.out[(size_t)tok * p.hv * DV + vh * DV + part * CB + c] = __float2bfloat16_rn(o);
+  }
+}
+
+// gated RMSNorm over the head * silu(z), in place on the un-normalised output of the split kernel: a warp per
+// (sequence, v-head)
+template <int DK, int DV>
+__global__ void __launch_bounds__(256) gdn_finish_kernel(const __grid_constant__ GdnParams p, int num_seqs) {
+  constexpr int E = DV / 32;
+  const int item = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  pdl_trigger();
+  pdl_wait();
+  if (item >= num_seqs * p.hv) return;
+  const int s = item / p.hv, vh = item - s * p.hv;
+  const int tok = p.cu ? p.cu[s] : s;
+  __nv_bfloat16* o = p.out + (size_t)tok * p.hv * DV + vh * DV + lane * E;
+  const __nv_bfloat16* z = p.proj + (size_t)tok * p.ld + 2 * p.hk * DK + p.hv * DV + vh * DV + lane * E;
+  float v[E], ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    v[e] = __bfloat162float(o[e]);
+    ss += v[e] * v[e];
+  }
+  ss = warp_sum(ss);
+  const float rr = rsqrtf(ss / (float)DV + p.eps);
+#pragma unroll
+  for (int e = 0; e < E; ++e)
+    o[e] = __float2bfloat16_rn(v[e] * rr * p.norm_w[lane * E + e] * silu_f(__bfloat162float(z[e])));
+}
+
 template <int DK, int DV, typename ST, int NS>
 __global__ void __launch_bounds__(DV / NS * 4) gdn_kernel(const __grid_constant__ GdnParams p) {
   constexpr int DPT = DK / 4;           // state elements per thread
@@ -538,6 +670,32 @@ static cudaError_t launch_token(const GdnParams& p, int num_seqs, dim3 grid, cud
   return launch_kernel(k, grid, dim3(DV * 4), smem, st, true, p, num_seqs);
 }
 
+template <int DK, int DV, typename ST>
+static cudaError_t launch_token_split(const GdnParams& p, int num_seqs, cudaStream_t st) {
+  constexpr int NSPL = DV / 32;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.hv * NSPL, num_seqs);
+  cfg.blockDim = dim3(128);
+  cfg.stream = st;
+  cudaLaunchAttribute at[2];
+  int n = 0;
+  if (pdl_enabled()) {
+    at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  at[n].id = cudaLaunchAttributeClusterDimension;
+  at[n].val.clusterDim.x = NSPL;
+  at[n].val.clusterDim.y = 1;
+  at[n].val.clusterDim.z = 1;
+  ++n;
+  cfg.attrs = at;
+  cfg.numAttrs = n;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gdn_token_split_kernel<DK, DV, ST>, p);
+  if (e != cudaSuccess) return e;
+  return launch_kernel(gdn_finish_kernel<DK, DV>, dim3((num_seqs * p.hv + 7) / 8), dim3(256), 0, st, true, p, num_seqs);
+}
+
 // Launch with programmatic stream serialization and, for NS > 1, clusters of NS blocks along x.
 template <int DK, int DV, typename ST, int NS>
 static cudaError_t launch_gdn(const GdnParams& p, int num_seqs, cudaStream_t st) {
@@ -572,15 +730,27 @@ int ti_gdn_params_size() { return (int)sizeof(ti::GdnParams); }
 
 // state_bf16: 0 = fp32 state pool, 1 = bf16.  (dk, dv) must be (128,128) or (64,64).
 // split 1: the columns of a head go to a cluster of 4 (dv 128) or 2 (dv 64) blocks (prefill; measured slower, off
-// by default).  split 2: the single-pass kernel for steps in which every sequence has exactly one token (decode).
+// by default).  split 2: the single-pass kernels for steps in which every sequence has exactly one token (decode):
+// one block per (head, sequence) for small batches, column-split blocks for large ones (staged blocks that walk
+// several sequences when snapshots are wanted, or with split 3).
 int ti_gdn_step(const ti::GdnParams* p, int num_seqs, int dk, int dv, int state_bf16, int split, void* stream) {
   if (num_seqs <= 0) return 0;
   if (p->hv % p->hk) return -2;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
-  if (split == 2) {                     // one token per sequence: the single-pass decode kernel
+  if (split >= 2) {                     // one token per sequence: the single-pass decode kernel
     // more (head, sequence) pairs than two waves of SMs: blocks walk several sequences with staged state
     const bool staged = (long long)p->hv * num_seqs > 2 * 148;
+    // large batches without snapshots: column-split blocks (split 3 keeps the staged kernel: tests, comparisons)
+    if (staged && split == 2 && p->snap_rel == nullptr) {
+      if (dk == 128 && dv == 128)
+        e = state_bf16 ? ti::launch_token_split<128, 128, __nv_bfloat16>(*p, num_seqs, st) : ti::launch_token_split<128, 128, float>(*p, num_seqs, st);
+      else if (dk == 64 && dv == 64)
+        e = state_bf16 ? ti::launch_token_split<64, 64, __nv_bfloat16>(*p, num_seqs, st) : ti::launch_token_split<64, 64, float>(*p, num_seqs, st);
+      else
+        return -3;
+      return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+    }
     const int gy = staged ? std::max(1, 148 / p->hv) : num_seqs;
     dim3 grid(p->hv, gy);
     if (dk == 128 && dv == 128) {

@@ -160,11 +160,28 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
+  pdl_trigger();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
+    // The weights of the first ring fill do not depend on the preceding kernel: they are requested before the
+    // programmatic-dependency wait, the activations (written by that kernel) after it.
+    const int n_pre = min(kStages, kb1 - kb0);
     if (elect_one()) {
+      for (int it = 0; it < n_pre; ++it) {
+        mbar_expect_tx(full0 + 8 * it, kStageBytes);
+        tma_load_4d(stage0 + it * kStageBytes, &p.map_w, 0, 0, kb0 + it, tile_n * (BMH * kBM / 8), full0 + 8 * it);
+      }
+    }
+    __syncwarp();
+    pdl_wait();
+    if (elect_one()) {
+      for (int it = 0; it < n_pre; ++it) {
+        const uint32_t dst = stage0 + it * kStageBytes;
+        tma_load_2d(dst + BMH * kStageA, &p.map_xh, (kb0 + it) * kBK, tile_m * BN, full0 + 8 * it);
+        if (!BF16) tma_load_2d(dst + BMH * kStageA + kStageB, &p.map_xl, (kb0 + it) * kBK, tile_m * BN, full0 + 8 * it);
+      }
       bool ok = true;
-      for (int kb = kb0; kb < kb1 && ok; ++kb) {
+      for (int kb = kb0 + n_pre; kb < kb1 && ok; ++kb) {
         const int it = kb - kb0, s = it % kStages;
         const uint32_t par = ((it / kStages) & 1) ^ 1;            // a fresh barrier passes a wait on parity 1
         ok = mbar_wait(empty0 + 8 * s, par, kGemmWaitNs, p.status);
@@ -178,6 +195,7 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
+    pdl_wait();
     if (elect_one()) {
       bool ok = true;
       for (int kb = kb0; kb < kb1 && ok; ++kb) {
@@ -209,6 +227,7 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5 -> TMEM lane quarters)
     const int quarter = warp & 3;
+    pdl_wait();
     const bool ok = mbar_wait(acc_bar, 0, 2 * kGemmWaitNs, p.status);
     tc_fence_after();
 #pragma unroll 1
@@ -349,6 +368,8 @@ __global__ void __launch_bounds__(512) quant_rows_fast_kernel(const __nv_bfloat1
   const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const __nv_bfloat16* row = x + (size_t)m * ldx;
   const int nchunk = K >> 3;
+  pdl_trigger();
+  pdl_wait();
   float v[5][8];
   float ss = 0.f;
 #pragma unroll
@@ -476,8 +497,8 @@ static int launch_gemm(const GemmParams& p, dim3 grid, cudaStream_t st) {
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmGeom<BN, BF16, BMH>::kSmem);
     configured = true;
   }
-  k<<<grid, kGemmThreads, GemmGeom<BN, BF16, BMH>::kSmem, st>>>(p);
-  return (int)cudaGetLastError();
+  const cudaError_t e = launch_kernel(k, grid, dim3(kGemmThreads), GemmGeom<BN, BF16, BMH>::kSmem, st, true, p);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 // 256-row tiles when the token tile is full-size and there are enough tiles to fill the GPU several times over
@@ -529,8 +550,8 @@ int ti_quant_rows(const void* x, int ldx, const void* norm_w, float eps, int M, 
   const bool aligned = (K % 8 == 0) && (ldx % 8 == 0) && (((uintptr_t)x | (uintptr_t)xh | (uintptr_t)xl) % 16 == 0) &&
                        (norm_w == nullptr || (uintptr_t)norm_w % 16 == 0);
   if (aligned && K <= 512 * 5 * 8)
-    ti::quant_rows_fast_kernel<<<M, 512, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)norm_w,
-                                                                    eps, K, (int8_t*)xh, (uint8_t*)xl, (float*)xscale);
+    ti::launch_kernel(ti::quant_rows_fast_kernel, dim3(M), dim3(512), 0, (cudaStream_t)stream, true, (const __nv_bfloat16*)x, ldx,
+                      (const __nv_bfloat16*)norm_w, eps, K, (int8_t*)xh, (uint8_t*)xl, (float*)xscale);
   else
     ti::quant_rows_kernel<<<M, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)norm_w,
                                                                eps, K, (int8_t*)xh, (uint8_t*)xl, (float*)xscale);

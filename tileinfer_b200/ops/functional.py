@@ -419,10 +419,13 @@ def swiglu_interleaved(gu, out=None):
 
 
 # ------------------------------------------------------------------------------------ launches by params
-def gdn_step(p: GdnParams, num_seqs: int, dk: int, dv: int, state_bf16: bool, split: bool = False, single: bool = False):
-    """single: every sequence has exactly one token (decode): the single-pass kernel.  split: the state columns
-    of a head go to a cluster of blocks (prefill; optional)."""
-    mode = 2 if single else int(split)
+def gdn_step(p: GdnParams, num_seqs: int, dk: int, dv: int, state_bf16: bool, split: bool = False, single: bool = False,
+             staged: bool = False):
+    """single: every sequence has exactly one token (decode): the single-pass kernels (one block per head and sequence;
+    for large batches column-split blocks, or, with `staged` or when snapshots are wanted, blocks that walk several
+    sequences with the state staged through shared memory).  split: the state columns of a head go to a cluster of
+    blocks (prefill; optional)."""
+    mode = (3 if staged else 2) if single else int(split)
     if not p.status:
         p.status = status_ptr()
     check(L().ti_gdn_step(ctypes.byref(p), num_seqs, dk, dv, int(state_bf16), mode, stream()), "ti_gdn_step")
