@@ -453,7 +453,8 @@ def test_topk(k):
 # token tiles of 32 / 64 / 128; (24, 1024, 4096), (48, 1552, 2048) and (64, 5120, 4096) also split k over gridDim.z
 @pytest.mark.parametrize("M,N,K", [(128, 256, 128), (200, 1552, 384), (64, 5120, 768), (300, 2048, 5120),
                                    (24, 1024, 4096), (48, 1552, 2048), (64, 5120, 4096), (17, 640, 1024),
-                                   (1024, 9480, 512), (1100, 9600, 1024)])     # the last two: 256-row tiles
+                                   (1024, 9480, 512), (1100, 9600, 1024),      # these two: 256-row tiles
+                                   (40, 512, 320), (300, 640, 832)])           # an odd number of 64-byte k slabs
 def test_tcgen05_gemm_w8a16(M, N, K):
     """TMA-fed tcgen05 kind::i8 GEMM with two-limb activations against fp32 matmul, all three epilogues."""
     F = _F()

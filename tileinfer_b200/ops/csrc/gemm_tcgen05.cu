@@ -10,11 +10,16 @@
 // 128 (weight rows) x 128 (tokens) output tile and keeps TWO int32 accumulators in TMEM (columns 0..127 for
 // W*hi, 128..255 for W*lo); the epilogue combines them as (256*acc_hi + acc_lo) * 2^(e-14) * scale[row].
 //
-// Pipeline (192 threads): warp 0 = TMA producer (one elected lane): per 64-byte k slab one 4-D tensor copy
-// of the weight tiles ([N/8][K/64][8][64] layout -> 128 rows x 64 B, 64-byte swizzle) and two 2-D copies of
-// the limb planes; warp 1 = MMA issuer (one lane): four tcgen05.mma (2 k-steps x 2 limbs) per slab, then
+// Pipeline (224 threads): warps 0 and 6 = TMA producers (one elected lane each, alternate stages): per stage of
+// 128 bytes of k one 4-D tensor copy of the weight tiles ([N/8][K/64][8][64] layout -> per row tile the 8 x 64-byte
+// rows of two k slabs, 64-byte swizzle) and two 2-D copies of the limb planes (rows of 128 bytes, 128-byte swizzle);
+// warp 1 = MMA issuer (one lane): eight tcgen05.mma (4 k-steps x 2 limbs) per stage and 128-row half, then
 // tcgen05.commit to release the stage; warps 2..5 = epilogue: tcgen05.ld of their 32 TMEM lanes, scale,
 // fused epilogue (bf16 store / SwiGLU / residual add), coalesced stores.
+// Stage size and the second producer come from measurement: one thread's wait / expect_tx / copy sequence takes
+// ~0.4 us whatever the bytes, so 16 KB stages from one thread cap a CTA at ~40 GB/s (5.9 TB/s over the GPU, operands
+// included), below what the tensor pipe (many tokens) or HBM (few tokens) would take; 32-64 KB stages from two
+// threads lift the cap to ~12 TB/s.
 // The token tile is a template parameter (32, 64 or 128 tokens): a decode batch of 17..64 rows then moves 4-8 KB of
 // limbs per 8 KB of weights instead of 16 KB, and the ring holds 12-16 stages, so the kernel streams weights at
 // HBM speed.  Products with few weight-row tiles (N = 5120: 40 tiles for 148 SMs) are split along k over
@@ -31,9 +36,11 @@
 namespace ti {
 
 constexpr int kBM = 128;          // weight rows per CTA (TMEM lanes)
-constexpr int kBK = 64;           // bytes of k per stage (one 64-byte swizzle row)
-constexpr int kStageA = kBM * kBK;                 // 8 KB of weights per stage
-constexpr int kGemmThreads = 192;
+constexpr int kBK = 64;           // bytes of k per weight slab (one 64-byte swizzle row)
+constexpr int kKS = 2;            // weight slabs per stage: one stage = 128 bytes of k
+constexpr int kStageA = kBM * kBK * kKS;           // 16 KB of weights per stage and 128-row half
+constexpr int kGemmThreads = 224;      // warp 0 and warp 6: TMA producers; warp 1: MMA issuer; warps 2..5: epilogue
+constexpr int kGemmProducerB = 6;
 #ifndef TI_GEMM_RING_KB
 #define TI_GEMM_RING_KB 192
 #endif
@@ -44,7 +51,7 @@ constexpr int kGemmRingBytes = TI_GEMM_RING_KB * 1024;
 // BMH = weight-row halves per CTA: 1 -> a 128-row tile; 2 -> a 256-row tile as two 128-row MMAs that share ONE
 // activation tile in shared memory (the bytes a CTA pulls through L2 per multiply-add drop by a third).
 template <int BN, bool BF16, int BMH = 1> struct GemmGeom {
-  static constexpr int kStageB = BN * kBK;                         // one limb plane / the bf16 activation tile
+  static constexpr int kStageB = BN * kBK * kKS;                   // one limb plane / the bf16 activation tile (128-byte rows)
   static constexpr int kStageBytes = BMH * kStageA + (BF16 ? 1 : 2) * kStageB;
   static constexpr int kStages = kGemmRingBytes / kStageBytes < 24 ? kGemmRingBytes / kStageBytes : 24;
   static constexpr size_t kSmem = (size_t)kStages * kStageBytes + 16 * kStages + 64 + 1024;
@@ -52,8 +59,8 @@ template <int BN, bool BF16, int BMH = 1> struct GemmGeom {
 constexpr unsigned long long kGemmWaitNs = 2000000000ull;
 
 struct GemmParams {
-  alignas(64) CUtensorMap map_w;   // uint8 [n_tiles][KB][8][64], box {64, 8, 1, 16}, 64B swizzle
-  alignas(64) CUtensorMap map_xh;  // uint8 [M][K], box {64, BN}, 64B swizzle (bf16 mode: the activations, [M][2K] bytes)
+  alignas(64) CUtensorMap map_w;   // uint8 [n_tiles][KB][8][64], box {64, 8, 2, 16 or 32}, 64B swizzle
+  alignas(64) CUtensorMap map_xh;  // uint8 [M][K], box {128, BN}, 128B swizzle (bf16 mode: the activations, [M][2K] bytes)
   alignas(64) CUtensorMap map_xl;
   const float* xscale;             // [M] value of one fixed-point unit (2^(e-14))
   const __nv_bfloat16* wscale;     // [N_pad]
@@ -63,7 +70,8 @@ struct GemmParams {
   float* part;                     // split-k partials [S][M][N] fp32
   unsigned* tile_count;            // [tiles_n * tiles_m] arrival counters, zero between launches
   int M, N, K, ldo, epi;
-  int kb_per_split;                // 64-byte k slabs per gridDim.z slice
+  int kb_per_split;                // 128-byte k stages per gridDim.z slice
+  int ablate;                      // timing experiments only (TI_GEMM_ABLATE): 1 no MMA, 2 no activation copies, 4 no weight copies
 };
 
 // kind::i8 instruction descriptor: D = s32, A = int8 (K-major), B = int8 / uint8 (K-major), M = 128, N = BN
@@ -78,27 +86,7 @@ template <int BN> TI_DEVICE constexpr uint32_t idesc_bf16() {
 
 enum { GEPI_STORE = 0, GEPI_SWIGLU = 1, GEPI_ROWPAR = 2, GEPI_F32 = 3 };
 
-// value of output (token m, weight row n) -> fused epilogue
-TI_DEVICE void gemm_epilogue(const GemmParams& p, int m, int n, int lane, float v) {
-  if (p.epi == GEPI_SWIGLU) {
-    // rows come interleaved (gate, up): lanes 2i / 2i+1
-    const float other = __shfl_xor_sync(0xffffffffu, v, 1);
-    if ((lane & 1) == 0 && n < p.N) {
-      const float gate = round_bf16(v), up = round_bf16(other);
-      static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] = __float2bfloat16_rn(silu_f(gate) * up);
-    }
-  } else if (n < p.N) {
-    if (p.epi == GEPI_F32) {
-      static_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
-      return;
-    }
-    float r = v;
-    if (p.epi == GEPI_ROWPAR) r += __bfloat162float(p.resid[(size_t)m * p.N + n]);
-    static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(r);
-  }
-}
-
-// the same for four adjacent weight rows n..n+3 of one token (N is a multiple of 4 here)
+// fused epilogue for four adjacent weight rows n..n+3 of one token (N is a multiple of 4 here): split-k reduction
 TI_DEVICE void gemm_epilogue4(const GemmParams& p, int m, int n, float4 v) {
   if (p.epi == GEPI_SWIGLU) {
     const float g0 = round_bf16(v.x), u0 = round_bf16(v.y), g1 = round_bf16(v.z), u1 = round_bf16(v.w);
@@ -121,6 +109,67 @@ TI_DEVICE void gemm_epilogue4(const GemmParams& p, int m, int n, float4 v) {
       make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
 }
 
+// Eight adjacent weight rows n..n+7 (n a multiple of 8) of one token, straight from the accumulators: split-k
+// partial (fp32), or the fused epilogue.  Rows past N and rows that cannot be stored as one vector go one by one.
+TI_DEVICE void gemm_store8(const GemmParams& p, int m, int n, const float4 a, const float4 b, int S, int split) {
+  const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  if (S > 1) {
+    float* dst = p.part + ((size_t)split * p.M + m) * p.N + n;
+    if (n + 8 <= p.N) {
+      *reinterpret_cast<float4*>(dst) = a;
+      *reinterpret_cast<float4*>(dst + 4) = b;
+    } else {
+      for (int i = 0; i < 8 && n + i < p.N; ++i) dst[i] = v[i];
+    }
+    return;
+  }
+  const bool full = n + 8 <= p.N;
+  if (p.epi == GEPI_SWIGLU) {
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + (n >> 1);
+    float o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = silu_f(round_bf16(v[2 * i])) * round_bf16(v[2 * i + 1]);
+    if (full && (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 7) == 0) {
+      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
+    } else {
+      for (int i = 0; i < 4 && n + 2 * i < p.N; ++i) dst[i] = __float2bfloat16_rn(o[i]);
+    }
+    return;
+  }
+  if (p.epi == GEPI_F32) {
+    float* dst = static_cast<float*>(p.out) + (size_t)m * p.ldo + n;
+    if (full && (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
+      *reinterpret_cast<float4*>(dst) = a;
+      *reinterpret_cast<float4*>(dst + 4) = b;
+    } else {
+      for (int i = 0; i < 8 && n + i < p.N; ++i) dst[i] = v[i];
+    }
+    return;
+  }
+  float r[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) r[i] = v[i];
+  const bool vec = full && (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 &&
+                   (p.epi != GEPI_ROWPAR || ((p.N & 7) == 0 && (reinterpret_cast<uintptr_t>(p.resid) & 15) == 0));
+  if (p.epi == GEPI_ROWPAR) {
+    const __nv_bfloat16* rs = p.resid + (size_t)m * p.N + n;
+    if (vec) {
+      const uint4 q = *reinterpret_cast<const uint4*>(rs);
+      const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { r[2 * i] += bf16lo(w4[i]); r[2 * i + 1] += bf16hi(w4[i]); }
+    } else {
+      for (int i = 0; i < 8 && n + i < p.N; ++i) r[i] += __bfloat162float(rs[i]);
+    }
+  }
+  __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + n;
+  if (vec) {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(r[0], r[1]), pack_bf16(r[2], r[3]), pack_bf16(r[4], r[5]), pack_bf16(r[6], r[7]));
+  } else {
+    for (int i = 0; i < 8 && n + i < p.N; ++i) dst[i] = __float2bfloat16_rn(r[i]);
+  }
+}
+
 template <int BN, bool BF16, int BMH>
 __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) gemm_w8a16_kernel(const __grid_constant__ GemmParams p) {
   using G = GemmGeom<BN, BF16, BMH>;
@@ -139,8 +188,8 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
   // token tiles vary fastest: the CTAs that run at the same time share weight tiles (read from HBM once, then L2
   // hits) and the limb planes of all tokens stay in L2
   const int tile_m = blockIdx.x, tile_n = blockIdx.y, split = blockIdx.z, S = gridDim.z;
-  const int KB = p.K / kBK;
-  const int kb0 = split * p.kb_per_split, kb1 = min(KB, kb0 + p.kb_per_split);
+  const int KB = (p.K + kBK * kKS - 1) / (kBK * kKS);               // stages of 128 bytes of k (a last half stage reads zeros)
+  const int kb0 = split * p.kb_per_split, kb1 = (p.ablate & 16) ? kb0 : min(KB, kb0 + p.kb_per_split);
   constexpr uint32_t kCols = BMH * kAcc * BN < 32 ? 32 : BMH * kAcc * BN;   // TMEM allocation: a power of two >= 32
 
   if (threadIdx.x == 0) {
@@ -161,36 +210,41 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
   const uint32_t tmem_base = *tmem_slot_ptr;
 
   pdl_trigger();
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
-    // The weights of the first ring fill do not depend on the preceding kernel: they are requested before the
-    // programmatic-dependency wait, the activations (written by that kernel) after it.
-    const int n_pre = min(kStages, kb1 - kb0);
+  if (warp == 0 || warp == kGemmProducerB) {
+    // ------------------------------------------------------------ TMA producers
+    // Two producer threads (in two warps) take the stages alternately: one thread's wait / expect / copy sequence
+    // takes ~0.4 us per stage, which is less than the ring can absorb.  The weights of the first ring fill do not
+    // depend on the preceding kernel: they are requested before the programmatic-dependency wait, the activations
+    // (written by that kernel) after it.
+    const int first = warp == 0 ? 0 : 1;
+    const int n_it = kb1 - kb0, n_pre = min(kStages, n_it);
+    const uint32_t stage_tx = ((p.ablate & 4) ? 0 : BMH * kStageA) + ((p.ablate & 2) ? 0 : (BF16 ? 1 : 2) * kStageB) + ((p.ablate & 6) == 6 ? 0 : 0);
     if (elect_one()) {
-      for (int it = 0; it < n_pre; ++it) {
-        mbar_expect_tx(full0 + 8 * it, kStageBytes);
-        tma_load_4d(stage0 + it * kStageBytes, &p.map_w, 0, 0, kb0 + it, tile_n * (BMH * kBM / 8), full0 + 8 * it);
+      for (int it = first; it < n_pre; it += 2) {
+        mbar_expect_tx(full0 + 8 * it, stage_tx);
+        if (!(p.ablate & 4)) tma_load_4d(stage0 + it * kStageBytes, &p.map_w, 0, 0, (kb0 + it) * kKS, tile_n * (BMH * kBM / 8), full0 + 8 * it);
       }
     }
     __syncwarp();
     pdl_wait();
     if (elect_one()) {
-      for (int it = 0; it < n_pre; ++it) {
+      for (int it = first; it < n_pre; it += 2) {
         const uint32_t dst = stage0 + it * kStageBytes;
-        tma_load_2d(dst + BMH * kStageA, &p.map_xh, (kb0 + it) * kBK, tile_m * BN, full0 + 8 * it);
-        if (!BF16) tma_load_2d(dst + BMH * kStageA + kStageB, &p.map_xl, (kb0 + it) * kBK, tile_m * BN, full0 + 8 * it);
+        if (p.ablate & 2) continue;
+        tma_load_2d(dst + BMH * kStageA, &p.map_xh, (kb0 + it) * kBK * kKS, tile_m * BN, full0 + 8 * it);
+        if (!BF16) tma_load_2d(dst + BMH * kStageA + kStageB, &p.map_xl, (kb0 + it) * kBK * kKS, tile_m * BN, full0 + 8 * it);
       }
-      bool ok = true;
-      for (int kb = kb0 + n_pre; kb < kb1 && ok; ++kb) {
-        const int it = kb - kb0, s = it % kStages;
+      int it = n_pre + ((n_pre & 1) == first ? 0 : 1);            // this producer's first stage after the pre-fill
+      for (; it < n_it; it += 2) {
+        const int s = it % kStages, kb = kb0 + it;
         const uint32_t par = ((it / kStages) & 1) ^ 1;            // a fresh barrier passes a wait on parity 1
-        ok = mbar_wait(empty0 + 8 * s, par, kGemmWaitNs, p.status);
-        if (!ok) break;
+        if (!mbar_wait(empty0 + 8 * s, par, kGemmWaitNs, p.status)) break;
         const uint32_t dst = stage0 + s * kStageBytes;
-        mbar_expect_tx(full0 + 8 * s, kStageBytes);
-        tma_load_4d(dst, &p.map_w, 0, 0, kb, tile_n * (BMH * kBM / 8), full0 + 8 * s);     // box: BMH * 16 row tiles
-        tma_load_2d(dst + BMH * kStageA, &p.map_xh, kb * kBK, tile_m * BN, full0 + 8 * s);
-        if (!BF16) tma_load_2d(dst + BMH * kStageA + kStageB, &p.map_xl, kb * kBK, tile_m * BN, full0 + 8 * s);
+        mbar_expect_tx(full0 + 8 * s, stage_tx);
+        if (!(p.ablate & 4)) tma_load_4d(dst, &p.map_w, 0, 0, kb * kKS, tile_n * (BMH * kBM / 8), full0 + 8 * s);   // box: 2 slabs x BMH * 16 row tiles
+        if (p.ablate & 2) continue;
+        tma_load_2d(dst + BMH * kStageA, &p.map_xh, kb * kBK * kKS, tile_m * BN, full0 + 8 * s);
+        if (!BF16) tma_load_2d(dst + BMH * kStageA + kStageB, &p.map_xl, kb * kBK * kKS, tile_m * BN, full0 + 8 * s);
       }
     }
   } else if (warp == 1) {
@@ -205,12 +259,15 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
         tc_fence_after();
         const uint32_t a = stage0 + s * kStageBytes, bh = a + BMH * kStageA, bl = bh + kStageB;
 #pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {                          // two 32-byte k steps inside the 64-byte slab
-          const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
-          const uint64_t dbh = smem_desc_sw64(bh + ks * 32), dbl = smem_desc_sw64(bl + ks * 32);
+        for (int j = 0; j < 2 * kKS; ++j) {                       // four 32-byte k steps inside the 128 bytes of the stage
+          if (p.ablate & 1) break;
+          const uint32_t acc = (it > 0 || j > 0) ? 1u : 0u;
+          // activations: rows of 128 bytes (128-byte swizzle); weights: per row tile the 8 x 64-byte rows of slab 0,
+          // then those of slab 1 (64-byte swizzle, 8-row groups 1024 bytes apart)
+          const uint64_t dbh = smem_desc_sw128(bh + j * 32), dbl = smem_desc_sw128(bl + j * 32);
 #pragma unroll
           for (int h = 0; h < BMH; ++h) {                         // the row halves share the activation operand
-            const uint64_t da = smem_desc_sw64(a + h * kStageA + ks * 32);
+            const uint64_t da = smem_desc_sw64_sbo(a + h * kStageA + (j >> 1) * 512 + (j & 1) * 32, 1024);
             const uint32_t d0 = tmem_base + (uint32_t)(h * kAcc * BN);
             if (BF16) {
               umma_bf16(d0, da, dbh, idesc_bf16<BN>(), acc);
@@ -230,24 +287,43 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
     pdl_wait();
     const bool ok = mbar_wait(acc_bar, 0, 2 * kGemmWaitNs, p.status);
     tc_fence_after();
+    // The operand ring is idle now (every copy has landed and every MMA has read its operands): each warp stages
+    // a 32-token x 32-row block of results there (fp32, 36-float pitch: conflict-free both ways) and writes it out
+    // with 8 rows = 16 bytes of bf16 per thread, 8 tokens per instruction, instead of 2 bytes per thread.
+    float* stage_t = reinterpret_cast<float*>(smem) + (warp - 2) * (32 * 36);
 #pragma unroll 1
     for (int h = 0; h < BMH; ++h) {
-      const int n = tile_n * (BMH * kBM) + h * kBM + quarter * 32 + lane;   // weight row == output feature of this lane
+      const int n0 = tile_n * (BMH * kBM) + h * kBM + quarter * 32;           // first weight row of this warp's block
+      const int n = n0 + lane;                                                 // weight row == output feature of this lane
       const float ws = (ok && n < p.N) ? (BF16 ? 1.f : __bfloat162float(p.wscale[n])) : 0.f;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * kAcc * BN);
       for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (p.ablate & 8) break;
+        if (tile_m * BN + c0 >= p.M) break;
         uint32_t hi[32], lo[32];
         tmem_ld32(taddr + c0, hi);
         if (!BF16) tmem_ld32(taddr + BN + c0, lo);
+        // the row scales of the 32 tokens of this chunk: one coalesced load, handed round by shuffles
+        const int m_lane = tile_m * BN + c0 + lane;
+        const float xs_lane = (!BF16 && m_lane < p.M) ? p.xscale[m_lane] : 0.f;
         tmem_ld_wait();
+        __syncwarp();                                                          // the previous block has been written out
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          const int m = tile_m * BN + c0 + j;                     // token (uniform over the warp)
-          if (m >= p.M) break;
-          const float v = BF16 ? __uint_as_float(hi[j]) * ws
-                               : ((float)(int)hi[j] * 256.f + (float)(int)lo[j]) * p.xscale[m] * ws;
-          if (S == 1) gemm_epilogue(p, m, n, lane, v);
-          else if (n < p.N) p.part[((size_t)split * p.M + m) * p.N + n] = v;
+          const float xs = __shfl_sync(0xffffffffu, xs_lane, j);
+          stage_t[j * 36 + lane] = BF16 ? __uint_as_float(hi[j]) * ws
+                                        : ((float)(int)hi[j] * 256.f + (float)(int)lo[j]) * xs * ws;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int t = (lane >> 2) + 8 * i, c = lane & 3;
+          const int m = tile_m * BN + c0 + t;
+          if (m < p.M && n0 + c * 8 < p.N) {
+            const float4 a = *reinterpret_cast<const float4*>(stage_t + t * 36 + c * 8);
+            const float4 b = *reinterpret_cast<const float4*>(stage_t + t * 36 + c * 8 + 4);
+            gemm_store8(p, m, n0 + c * 8, a, b, S, split);
+          }
         }
       }
     }
@@ -264,7 +340,7 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
       __threadfence();
     }
     __syncthreads();
-    if (s_last && warp >= 2) {
+    if (s_last && warp >= 2 && warp < 6) {
       // lane -> four adjacent output features, warp -> every fourth token; the loads of four tokens and all
       // slices are issued before the first is used
       const int m_end = min(p.M, (tile_m + 1) * BN);
@@ -442,12 +518,12 @@ __global__ void __launch_bounds__(512) quant_rows_fast_kernel(const __nv_bfloat1
 }
 
 static int encode_map(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
-                      const cuuint32_t* box) {
+                      const cuuint32_t* box, CUtensorMapSwizzle swizzle) {
   cuuint32_t elem[4] = {1, 1, 1, 1};
   EncodeTiledFn enc = encode_tiled_fn();
   if (enc == nullptr) return 999;
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void*>(base), dims,
-                                            strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                                            strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
@@ -459,8 +535,8 @@ struct MapKey {
   int d0, d1, box;
   bool operator<(const MapKey& o) const { return std::tie(base, d0, d1, box) < std::tie(o.base, o.d0, o.d1, o.box); }
 };
-// box <= 0: weight map over [n_tiles = d1][KB = d0][8][64] with a box of 16 (box == 0) or -box row tiles;
-// box > 0: limb plane [M = d1][K = d0], box {64, box}
+// box <= 0: weight map over [n_tiles = d1][KB = d0][8][64] with a box of two k slabs x 16 (box == 0) or -box row tiles,
+// 64-byte swizzle; box > 0: limb plane [M = d1][K = d0], box {128, box}, 128-byte swizzle
 static int cached_map(CUtensorMap* dst, const void* base, int d0, int d1, int box) {
   static std::map<MapKey, CUtensorMap> cache;
   static std::mutex mu;
@@ -473,13 +549,13 @@ static int cached_map(CUtensorMap* dst, const void* base, int d0, int d1, int bo
     if (box <= 0) {
       const cuuint64_t dims[4] = {64, 8, (cuuint64_t)d0, (cuuint64_t)d1};
       const cuuint64_t strides[3] = {64, 512, (cuuint64_t)d0 * 512};
-      const cuuint32_t bx[4] = {64, 8, 1, (cuuint32_t)(box == 0 ? 16 : -box)};
-      rc = encode_map(&m, base, 4, dims, strides, bx);
+      const cuuint32_t bx[4] = {64, 8, (cuuint32_t)kKS, (cuuint32_t)(box == 0 ? 16 : -box)};
+      rc = encode_map(&m, base, 4, dims, strides, bx, CU_TENSOR_MAP_SWIZZLE_64B);
     } else {
       const cuuint64_t dims[2] = {(cuuint64_t)d0, (cuuint64_t)d1};
       const cuuint64_t strides[1] = {(cuuint64_t)d0};
-      const cuuint32_t bx[2] = {64, (cuuint32_t)box};
-      rc = encode_map(&m, base, 2, dims, strides, bx);
+      const cuuint32_t bx[2] = {(cuuint32_t)(kBK * kKS), (cuuint32_t)box};
+      rc = encode_map(&m, base, 2, dims, strides, bx, CU_TENSOR_MAP_SWIZZLE_128B);
     }
     if (rc) return rc;
     if (cache.size() > 8192) cache.clear();
@@ -524,12 +600,13 @@ static int pick_bmh(int M, int n_tiles) {
   return (n_tiles >= 32 && tiles256 >= 2 * 148) ? 2 : 1;
 }
 
-// k split that fills the 148 SMs when there are few output tiles (at least 16 slabs per slice); sets kb_per_split
+// k split that fills the 148 SMs when there are few output tiles (at least 8 stages = 1024 bytes of k per slice);
+// sets kb_per_split.  KB counts stages of 128 bytes of k.
 static int plan_split(GemmParams& p, int KB, int tiles, int M, int N, int ldo, void* part, size_t part_bytes,
                       void* tile_count, int n_count) {
   int S = 1;
   if (part != nullptr && tile_count != nullptr && tiles < 120 && N % 4 == 0 && ldo % 4 == 0) {
-    S = std::min(std::min(148 / tiles, KB / 16), 16);
+    S = std::min(std::min(148 / tiles, KB / 8), 16);
     while (S > 1 && ((size_t)S * M * N * 4 > part_bytes || tiles > n_count)) --S;
     if (S < 1) S = 1;
   }
@@ -567,7 +644,7 @@ int ti_gemm_w8a16(const void* w, const void* wscale, int n_tiles, int N, int K, 
   if (M <= 0) return 0;
   if (K % 64 || N < 1 || epi < 0 || epi > 2) return -2;
   ti::GemmParams p = {};
-  const int KB = K / 64;
+  const int KB = K / 64, KS = (KB + ti::kKS - 1) / ti::kKS;      // 64-byte slabs of the weight layout; 128-byte stages
   const int BN = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
   const int BMH = ti::pick_bmh(M, n_tiles);
   int rc = ti::cached_map(&p.map_w, w, KB, n_tiles, BMH == 2 ? -32 : 0);
@@ -581,6 +658,10 @@ int ti_gemm_w8a16(const void* w, const void* wscale, int n_tiles, int N, int K, 
   p.resid = (const __nv_bfloat16*)resid;
   p.out = out;
   p.status = (unsigned*)status;
+  {
+    static const int ablate = [] { const char* e = getenv("TI_GEMM_ABLATE"); return e == nullptr ? 0 : atoi(e); }();
+    p.ablate = ablate;
+  }
   p.M = M;
   p.N = N;
   p.K = K;
@@ -588,7 +669,7 @@ int ti_gemm_w8a16(const void* w, const void* wscale, int n_tiles, int N, int K, 
   p.epi = epi;
   const int rows = ti::kBM * BMH;
   const int tiles_n = (n_tiles * 8 + rows - 1) / rows, tiles_m = (M + BN - 1) / BN;
-  const int S = ti::plan_split(p, KB, tiles_n * tiles_m, M, N, ldo, part, part_bytes, tile_count, n_count);
+  const int S = ti::plan_split(p, KS, tiles_n * tiles_m, M, N, ldo, part, part_bytes, tile_count, n_count);
   dim3 grid(tiles_m, tiles_n, S);
   cudaStream_t st = (cudaStream_t)stream;
   if (BMH == 2 && BN == 32) return ti::launch_gemm<32, false, 2>(p, grid, st);
@@ -606,7 +687,7 @@ int ti_gemm_bf16(const void* w, int n_tiles, int N, int K, const void* x, int M,
   if (M <= 0) return 0;
   if (K % 32 || N < 1 || epi < 0 || epi > 3) return -2;
   ti::GemmParams p = {};
-  const int KB = K / 32;                                       // 64-byte slabs
+  const int KB = K / 32, KS = (KB + ti::kKS - 1) / ti::kKS;    // 64-byte slabs; 128-byte stages
   const int BN = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
   const int BMH = ti::pick_bmh(M, n_tiles);
   int rc = ti::cached_map(&p.map_w, w, KB, n_tiles, BMH == 2 ? -32 : 0);
@@ -623,7 +704,7 @@ int ti_gemm_bf16(const void* w, int n_tiles, int N, int K, const void* x, int M,
   p.epi = epi;
   const int rows = ti::kBM * BMH;
   const int tiles_n = (n_tiles * 8 + rows - 1) / rows, tiles_m = (M + BN - 1) / BN;
-  const int S = ti::plan_split(p, KB, tiles_n * tiles_m, M, N, ldo, part, part_bytes, tile_count, n_count);
+  const int S = ti::plan_split(p, KS, tiles_n * tiles_m, M, N, ldo, part, part_bytes, tile_count, n_count);
   dim3 grid(tiles_m, tiles_n, S);
   cudaStream_t st = (cudaStream_t)stream;
   if (BMH == 2 && BN == 32) return ti::launch_gemm<32, true, 2>(p, grid, st);

@@ -82,6 +82,17 @@ TI_DEVICE uint64_t smem_desc_sw64(uint32_t saddr) {
   return d;
 }
 
+// The same rows with the 8-row groups `sbo` bytes apart (two k slabs interleaved per row tile: 1024).
+TI_DEVICE uint64_t smem_desc_sw64_sbo(uint32_t saddr, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(sbo >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)4 << 61;
+  return d;
+}
+
 // K-major operand tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
 TI_DEVICE uint64_t smem_desc_sw128(uint32_t saddr) {
   uint64_t d = 0;
