@@ -5,9 +5,10 @@
 // copy before every later chunk (model/qwen_36.py:1031-1042).  Here a CTA owns 128 query tokens of one head and
 // walks the sequence's KV pages in tiles of 128 keys straight out of the paged cache:
 //
-//   warp 0  TMA producer: Q tile once (4 swizzled 64-column slabs), then per KV tile 8 K pages
-//           ([16 tokens][D], 128-byte swizzle) and 8 V pages ([D][16 tokens] as stored: each page is exactly the
-//           B operand of one k = 16 step of P V, 32-byte swizzle), addressed through the block table;
+//   warp 0  TMA producer: Q tile once (4 swizzled 64-column slabs), then per KV tile 8 K pages, each ONE 4-D copy
+//           ([16 tokens][D] in the cache -> [2 groups of 8 keys][D/64 slabs][8][64], 128-byte swizzle);
+//   warp 6  TMA producer of the 8 V pages per tile ([D][16 tokens] as stored: each page is exactly the B operand
+//           of one k = 16 step of P V, 32-byte swizzle); pages are addressed through the block table;
 //   warp 1  MMA issuer: S = Q K^T (tcgen05.mma kind::f16, M = N = 128, accumulator in TMEM, two S buffers so the
 //           next tile's S is computed while the softmax works on this one), then O += P V (N = D);
 //   warps 2-5  softmax: one thread per query row (= TMEM lane): scale, causal mask, running maximum in the exp2
@@ -29,7 +30,7 @@ namespace ti {
 
 struct AttnPrefillParams {
   alignas(64) CUtensorMap map_q;   // bf16 [T][hq*D], box {64, 128}, 128B swizzle
-  alignas(64) CUtensorMap map_k;   // bf16 [blocks*hkv*16][D], box {64, 16}, 128B swizzle
+  alignas(64) CUtensorMap map_k;   // bf16 [blocks*hkv*2 groups][D/64 slabs][8 keys][64], box {64, 8, D/64, 2}, 128B swizzle
   alignas(64) CUtensorMap map_v;   // bf16 [blocks*hkv*D][16], box {16, D}, 32B swizzle
   const int* block_tables;         // [S, max_blocks]
   const int* positions;            // [T]
@@ -44,6 +45,8 @@ struct AttnPrefillParams {
 };
 
 constexpr unsigned long long kAttnWaitNs = 500000000ull;
+constexpr int kAttnThreads = 224;        // warp 0: Q/K producer, 1: MMA issuer, 2..5: softmax, 6: V producer
+constexpr int kAttnProducerV = 6;
 constexpr float kMaskVal = -1e30f;
 constexpr float kRescaleGap = 8.f;       // log2 units the running maximum may lag behind before O is rescaled
 
@@ -61,7 +64,7 @@ template <int D> struct AttnPrefillGeom {
 };
 
 template <int D>
-__global__ void __launch_bounds__(192, 1) attn_prefill_kernel(const __grid_constant__ AttnPrefillParams p) {
+__global__ void __launch_bounds__(kAttnThreads, 1) attn_prefill_kernel(const __grid_constant__ AttnPrefillParams p) {
   using G = AttnPrefillGeom<D>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -105,29 +108,36 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_kernel(const __grid_const
   const uint32_t tmem_base = *tmem_slot_ptr;
   volatile int* abort_flag = &s_abort;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+  if (warp == 0 || warp == kAttnProducerV) {
+    // ------------------------------------------------------------ TMA producers: warp 0 Q and K, warp 6 V
+    // (one thread's wait / expect / copy sequence is slower than the tensor pipe consumes a tile, so K and V are
+    // requested by two threads; a K page is ONE 4-D copy: [2 groups of 8 keys][kSlabs][8][64 columns])
     if (elect_one()) {
-      mbar_expect_tx(q_full, G::kQBytes);
-#pragma unroll
-      for (int s = 0; s < G::kSlabs; ++s) tma_load_2d(q_s + s * (128 * 128), &p.map_q, head * D + s * 64, tok0, q_full);
       const int* bt = p.block_tables + (size_t)seq * p.max_blocks;
-      for (int j = 0; j < ntiles && !*abort_flag; ++j) {
-        int blk[8];
+      if (warp == 0) {
+        mbar_expect_tx(q_full, G::kQBytes);
 #pragma unroll
-        for (int g = 0; g < 8; ++g) blk[g] = bt[min(j * 8 + g, npages - 1)];   // pages past the end repeat the last one (masked)
-        if (j > 0 && !mbar_wait(k_empty, (uint32_t)((j - 1) & 1), kAttnWaitNs, p.status)) { *abort_flag = 1; break; }
-        mbar_expect_tx(k_full, G::kKBytes);
+        for (int s = 0; s < G::kSlabs; ++s) tma_load_2d(q_s + s * (128 * 128), &p.map_q, head * D + s * 64, tok0, q_full);
+        for (int j = 0; j < ntiles && !*abort_flag; ++j) {
+          int blk[8];
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const int row = (blk[g] * p.hkv + kh) * 16;
+          for (int g = 0; g < 8; ++g) blk[g] = bt[min(j * 8 + g, npages - 1)];   // pages past the end repeat the last one (masked)
+          if (j > 0 && !mbar_wait(k_empty, (uint32_t)((j - 1) & 1), kAttnWaitNs, p.status)) { *abort_flag = 1; break; }
+          mbar_expect_tx(k_full, G::kKBytes);
 #pragma unroll
-          for (int s = 0; s < G::kSlabs; ++s) tma_load_2d(k_s + s * (128 * 128) + g * 2048, &p.map_k, s * 64, row, k_full);
+          for (int g = 0; g < 8; ++g)
+            tma_load_4d(k_s + g * (G::kSlabs * 2048), &p.map_k, 0, 0, 0, (blk[g] * p.hkv + kh) * 2, k_full);
         }
-        if (j > 0 && !mbar_wait(v_empty, (uint32_t)((j - 1) & 1), kAttnWaitNs, p.status)) { *abort_flag = 1; break; }
-        mbar_expect_tx(v_full, G::kVBytes);
+      } else {
+        for (int j = 0; j < ntiles && !*abort_flag; ++j) {
+          int blk[8];
 #pragma unroll
-        for (int g = 0; g < 8; ++g) tma_load_2d(v_s + g * G::kVPage, &p.map_v, 0, (blk[g] * p.hkv + kh) * D, v_full);
+          for (int g = 0; g < 8; ++g) blk[g] = bt[min(j * 8 + g, npages - 1)];
+          if (j > 0 && !mbar_wait(v_empty, (uint32_t)((j - 1) & 1), kAttnWaitNs, p.status)) { *abort_flag = 1; break; }
+          mbar_expect_tx(v_full, G::kVBytes);
+#pragma unroll
+          for (int g = 0; g < 8; ++g) tma_load_2d(v_s + g * G::kVPage, &p.map_v, 0, (blk[g] * p.hkv + kh) * D, v_full);
+        }
       }
     }
   } else if (warp == 1) {
@@ -139,9 +149,9 @@ __global__ void __launch_bounds__(192, 1) attn_prefill_kernel(const __grid_const
 #pragma unroll
         for (int s = 0; s < G::kSlabs; ++s)
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_bf16(d, smem_desc_sw128(q_s + s * (128 * 128) + ks * 32), smem_desc_sw128(k_s + s * (128 * 128) + ks * 32),
-                      idesc_s, (s | ks) ? 1u : 0u);
+          for (int ks = 0; ks < 4; ++ks)                     // K: per 8-key group the kSlabs 64-column slabs side by side
+            umma_bf16(d, smem_desc_sw128(q_s + s * (128 * 128) + ks * 32),
+                      smem_desc_sw128_sbo(k_s + s * 1024 + ks * 32, G::kSlabs * 1024), idesc_s, (s | ks) ? 1u : 0u);
         umma_commit(k_empty);
         umma_commit(s_full0 + 8 * (j & 1));
       };
@@ -337,6 +347,33 @@ static int bf16_map_2d(CUtensorMap* dst, const void* base, long long d0, long lo
   return 0;
 }
 
+// K cache [rows = blocks*hkv*16][D] seen as [groups of 8 rows][D/64 slabs][8 rows][64 columns]: one copy brings a
+// 16-key page as two 8-key groups with their column slabs side by side (the layout the QK^T descriptors walk).
+static int bf16_map_kpage(CUtensorMap* dst, const void* base, int D, long long rows) {
+  static std::map<AMapKey, CUtensorMap> cache;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  const AMapKey key{base, D, rows, 64, 8, -1};
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (enc == nullptr) return 999;
+    CUtensorMap m;
+    const cuuint64_t dims[4] = {64, 8, (cuuint64_t)(D / 64), (cuuint64_t)(rows / 8)};
+    const cuuint64_t strides[3] = {(cuuint64_t)D * 2, 128, (cuuint64_t)D * 16};
+    const cuuint32_t box[4] = {64, 8, (cuuint32_t)(D / 64), 2};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 1000 + (int)r;
+    if (cache.size() > 4096) cache.clear();
+    it = cache.emplace(key, m).first;
+  }
+  *dst = it->second;
+  return 0;
+}
+
 template <int D>
 static int launch_attn_prefill(const AttnPrefillParams& p, int num_tiles, cudaStream_t st) {
   static bool configured = false;
@@ -345,7 +382,7 @@ static int launch_attn_prefill(const AttnPrefillParams& p, int num_tiles, cudaSt
     cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AttnPrefillGeom<D>::kSmem);
     configured = true;
   }
-  k<<<dim3(num_tiles, p.hq), 192, AttnPrefillGeom<D>::kSmem, st>>>(p);
+  k<<<dim3(num_tiles, p.hq), kAttnThreads, AttnPrefillGeom<D>::kSmem, st>>>(p);
   return (int)cudaGetLastError();
 }
 
@@ -366,7 +403,7 @@ int ti_attn_prefill(const void* q, int T, const void* kcache, const void* vcache
   ti::AttnPrefillParams p = {};
   int rc = ti::bf16_map_2d(&p.map_q, q, (long long)hq * D, T, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
-  rc = ti::bf16_map_2d(&p.map_k, kcache, D, (long long)num_blocks * hkv * 16, 64, 16, CU_TENSOR_MAP_SWIZZLE_128B);
+  rc = ti::bf16_map_kpage(&p.map_k, kcache, D, (long long)num_blocks * hkv * 16);
   if (rc) return rc;
   rc = ti::bf16_map_2d(&p.map_v, vcache, 16, (long long)num_blocks * hkv * D, 16, D, CU_TENSOR_MAP_SWIZZLE_32B);
   if (rc) return rc;

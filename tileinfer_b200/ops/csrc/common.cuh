@@ -57,7 +57,7 @@ TI_DEVICE float warp_max(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
-TI_DEVICE float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+TI_DEVICE float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }   // 2 ulp: results are rounded to bf16
 TI_DEVICE float sigmoid_f(float x) { return 1.0f / (1.0f + __expf(-x)); }
 
 TI_DEVICE float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }

@@ -103,6 +103,16 @@ TI_DEVICE uint64_t smem_desc_sw128(uint32_t saddr) {
   d |= (uint64_t)2 << 61;                              // layout type: SWIZZLE_128B
   return d;
 }
+// The same rows with the 8-row groups `sbo` bytes apart (several 128-byte column slabs side by side per group).
+TI_DEVICE uint64_t smem_desc_sw128_sbo(uint32_t saddr, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(sbo >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
 // K-major operand tile, rows of 32 bytes (one 16-element bf16 k step), 32-byte swizzle, 8-row groups 256 bytes apart.
 TI_DEVICE uint64_t smem_desc_sw32(uint32_t saddr) {
   uint64_t d = 0;
