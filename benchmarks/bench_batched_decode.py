@@ -99,7 +99,7 @@ def main():
     if args.tp > 1:
         import torch.distributed as dist
         dist.barrier()
-        model.graphs.clear()
+        model.release_graphs()
         torch.cuda.synchronize()
         if model.peer is not None:
             model.peer.close()

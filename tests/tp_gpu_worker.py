@@ -43,7 +43,7 @@ def leave_between_steps():
     ok = float(torch.ones(8, device="cuda").sum()) == 8.0 and llm.model_runner.model.peer_status() == 0
     if llm.comm.rank == 0:
         print(f"LEAVE_RESULT {verdict} context_ok={ok} first_len={len(first[0])}", flush=True)
-    llm.model_runner.model.graphs.clear()
+    llm.model_runner.model.release_graphs()
     peer.close(collective=False)
     os._exit(0)
 
@@ -74,7 +74,7 @@ def main():
         print("TP_RESULT " + json.dumps({"ranks": box, "prompts": prompts, "fused": fused}), flush=True)
     dist.barrier()
     # graphs that captured collectives go before the communicator does
-    llm.model_runner.model.graphs.clear()
+    llm.model_runner.model.release_graphs()
     torch.cuda.synchronize()
     if llm.model_runner.model.peer is not None:
         llm.model_runner.model.peer.close()

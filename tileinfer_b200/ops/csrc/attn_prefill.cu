@@ -400,6 +400,8 @@ int ti_attn_prefill(const void* q, int T, const void* kcache, const void* vcache
                     void* status, void* stream) {
   if (num_tiles <= 0) return 0;
   if (hq % hkv || (D != 64 && D != 128 && D != 256) || T < 1 || num_blocks < 1) return -2;
+  // the gate and the output are read / written 16 bytes at a time: refuse layouts that would make those accesses misaligned
+  if ((ld & 7) || (reinterpret_cast<uintptr_t>(gate_src) & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return -4;
   ti::AttnPrefillParams p = {};
   int rc = ti::bf16_map_2d(&p.map_q, q, (long long)hq * D, T, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
