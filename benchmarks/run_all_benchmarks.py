@@ -70,6 +70,10 @@ def main():
                                                                   "1,8,64" if args.quick else "1,2,4,8,16,32,64"], port + 1, 1800))
         runs.append(run("benchmarks/bench_prefill.py", n, ["--model", args.model, "--prompts", "1", "--prompt-len", plen,
                                                            "--chunk", "8192"], port + 2, 1800))
+        if n == 1:      # kernel micro-benchmarks (one GPU)
+            for script, extra in (("benchmarks/bench_gemv.py", ["--chain"]), ("benchmarks/bench_gemm.py", ["--M", "64", "2048", "8192"]),
+                                  ("benchmarks/bench_attn.py", ["--max-len", plen]), ("benchmarks/bench_gdn.py", [])):
+                runs.append(run(script, 1, extra, port + 4, 1800))
         if n > 1:
             runs.append(run("benchmarks/bench_fused_collectives.py", n, ["--iters", "30" if args.quick else "100"], port + 3, 1800))
     decode = [r["results"][-1] for r in runs if r["script"] == "bench.py" and r["results"]]

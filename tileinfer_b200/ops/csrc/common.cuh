@@ -58,7 +58,7 @@ TI_DEVICE float warp_max(float v) {
   return v;
 }
 TI_DEVICE float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }   // 2 ulp: results are rounded to bf16
-TI_DEVICE float sigmoid_f(float x) { return 1.0f / (1.0f + __expf(-x)); }
+TI_DEVICE float sigmoid_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
 TI_DEVICE float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 TI_DEVICE float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }

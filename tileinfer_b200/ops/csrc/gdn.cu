@@ -300,7 +300,7 @@ TI_DEVICE float ld_cluster_f32(const float* local, int rank) {
 // the un-normalised output and gdn_finish_kernel applies norm * silu(z) in place.  The NSPL blocks of a head form a
 // thread-block cluster (they share the q / k conv history).
 template <int DK, int DV, typename ST>
-__global__ void __launch_bounds__(128) gdn_token_split_kernel(const __grid_constant__ GdnParams p) {
+__global__ void __launch_bounds__(128, sizeof(ST) == 4 ? 8 : 6) gdn_token_split_kernel(const __grid_constant__ GdnParams p) {
   constexpr int CB = 32, NSPL = DV / CB, DPT = DK / 4;
   constexpr int NCH = 2 * DK + DV, NCHL = 2 * DK + CB;
   constexpr int NCPT = (NCHL + 127) / 128;
