@@ -903,6 +903,26 @@ def test_ar_rows_fused_allreduce_residual_norm_quant(M, N, tp):
     hf = want_h.float()
     want_n = (hf * torch.rsqrt((hf * hf).mean(-1, keepdim=True) + 1e-6) * (1 + nw.float())).to(BF16)
     torch.testing.assert_close(xn.float(), want_n.float(), rtol=1e-2, atol=1e-2)
+    # two-shot form, the ranks emulated one after the other: every rank reduces the rows m = rank (mod tp) and writes
+    # the bf16 sums over those rows in ALL buffers; afterwards one rank's row kernel reads its local buffer only
+    sums = sum(p.float() for p in parts).to(BF16)
+    flags[:8] = 7 * 65536 + 500                     # the one-shot calls above published rank 1's flag with their smaller tags
+    flags[16] = 0                                   # word 16: count of finished blocks of the first shot (reset by the last one)
+    for r in range(tp):
+        comm.rank = r
+        F.ar_rows(comm, 0, M, N, resid, h2, order=7, two_shot=2)
+        assert int(flags[16]) == 0 and int(flags[8 + r]) == 7 * 65536 + 8      # counter back at zero, second flag published
+    torch.cuda.synchronize()
+    assert all(torch.equal(p, sums) for p in parts) and int(ctrl[1]) == 0
+    comm.rank = 1
+    h3 = torch.zeros_like(h)
+    limbs3 = F.Limbs(M, N, "cuda")
+    F.ar_rows(comm, 0, M, N, resid, h3, order=7, mode=F.AR_LIMBS, norm_w=nw, limbs=limbs3, two_shot=3)
+    want_h3 = (sums.float() + resid.float()).to(BF16)
+    ref3 = F.quant_rows(want_h3, norm_w=nw)
+    torch.cuda.synchronize()
+    assert torch.equal(h3, want_h3)
+    assert torch.equal(limbs3.hi, ref3.hi) and torch.equal(limbs3.lo, ref3.lo) and torch.equal(limbs3.scale, ref3.scale)
     # a flag that never arrives: the wait runs out, the status word says so, the context survives
     flags.zero_()
     comm.timeout_ns = 2 * 10 ** 6

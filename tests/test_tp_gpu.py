@@ -13,10 +13,10 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(tp, fused, port, nvls=False):
-    # NVLS (NCCL's and this package's own multimem loads) stays off except in the one test that is about it
+def _run(tp, fused, port, nvls=False, **extra_env):
+    # NVLS (NCCL's and this package's own multimem loads) stays off except in the tests that are about it
     env = dict(os.environ, TI_TEST_FUSED="1" if fused else "0", NCCL_NVLS_ENABLE="1" if nvls else "0",
-               TI_NVLS="1" if nvls else "0")
+               TI_NVLS="1" if nvls else "0", **extra_env)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(tp),
                         "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_gpu_worker.py")],
                        capture_output=True, text=True, env=env, timeout=240)
@@ -62,6 +62,23 @@ def test_fused_tp_with_nvls_multimem_reduction():
     assert all(r["greedy"] == ranks[0]["greedy"] and r["sampled"] == ranks[0]["sampled"] for r in ranks)
     for p, o in zip(res["prompts"], ranks[0]["greedy"]):
         _near_greedy(o, p)
+
+
+@pytest.mark.parametrize("tp,nvls", [(2, True), (4, False), (8, True)])
+def test_fused_tp_two_shot_allreduce(tp, nvls):
+    """The two-shot form of the many-row all-reduce (every rank reduces 1/tp of the rows and writes the sums into all
+    ranks' buffers: multimem.ld_reduce + multimem.st with NVLS, peer loads and stores without), forced for every
+    prefill chunk of 8 rows or more: same tokens as the oracle, all ranks agree, no wait runs out."""
+    if torch.cuda.device_count() < tp:
+        pytest.skip(f"needs {tp} GPUs")
+    res = _run(tp, True, 29560 + tp, nvls=nvls, TI_AR_TWO_SHOT_ROWS="8", TI_AR_TWO_SHOT_TP="2")
+    ranks = res["ranks"]
+    if nvls and not all(r.get("nvls") for r in ranks):
+        pytest.skip("no NVLS multicast binding on this machine (torch symmetric memory reported none)")
+    assert all(r["status"] == 0 for r in ranks)
+    assert all(r["greedy"] == ranks[0]["greedy"] and r["sampled"] == ranks[0]["sampled"] for r in ranks)
+    for p, o in zip(res["prompts"], ranks[0]["greedy"]):
+        _near_greedy(o, p, tp=tp)
 
 
 def test_nccl_baseline_path_tp2():

@@ -82,6 +82,10 @@ class _ModelBase:
         self._ar_pending = None            # a many-row all-reduce whose result nobody has consumed yet
         self.ar_min_rows = int(os.environ.get("TI_AR_MIN_ROWS", "4"))   # more rows than this: GEMM + fused all-reduce
         # (measured at TP = 2: batch 8 964 -> 1167 tok/s, batch 16 1400 -> 2181 tok/s against the packet GEMV in several passes)
+        # two-shot all-reduce (reduce 1/tp of the rows, broadcast the sums, then read locally) from this many rows on this
+        # many ranks: the one-shot form moves tp times more bytes per GPU, which only matters once the rows are many
+        self.ar_two_shot_rows = int(os.environ.get("TI_AR_TWO_SHOT_ROWS", "256"))
+        self.ar_two_shot_tp = int(os.environ.get("TI_AR_TWO_SHOT_TP", "4"))
         self.ctrl = self.peer.ctrl if self.peer is not None else torch.zeros(4, dtype=torch.int32, device=dev)
         self.step_ptr = self.ctrl.data_ptr()
         self.block_size = 16
@@ -402,12 +406,12 @@ class _StepMixin:
         if W.wt == F.W_INT8:
             limbs = F.Limbs(M, W.K, self.dev)
             F.ar_rows(self.peer, pend["parity"], M, W.K, pend["resid"], x, order=pend["order"], mode=F.AR_LIMBS,
-                      norm_w=norm_w, limbs=limbs, eps=self.cfg.rms_eps)
+                      norm_w=norm_w, limbs=limbs, eps=self.cfg.rms_eps, two_shot=self._two_shot(M))
             F.gemm_w8a16(W, limbs, out=out[:M], epi=gepi, resid=r)
         else:
             xn = torch.empty(M, W.K, dtype=BF16, device=self.dev)
             F.ar_rows(self.peer, pend["parity"], M, W.K, pend["resid"], x, order=pend["order"], mode=F.AR_BF16,
-                      norm_w=norm_w, xn=xn, eps=self.cfg.rms_eps)
+                      norm_w=norm_w, xn=xn, eps=self.cfg.rms_eps, two_shot=self._two_shot(M))
             F.gemm_bf16(W, xn, out=out[:M], epi=gepi, resid=r)
         self._launches += 2
 
@@ -415,8 +419,12 @@ class _StepMixin:
         """Completes a pending many-row all-reduce whose consumer is not a normalising GEMM (end of the step)."""
         pend, self._ar_pending = self._ar_pending, None
         if pend is not None:
-            F.ar_rows(self.peer, pend["parity"], pend["M"], self.H, pend["resid"], pend["out"], order=pend["order"])
+            F.ar_rows(self.peer, pend["parity"], pend["M"], self.H, pend["resid"], pend["out"], order=pend["order"],
+                      two_shot=self._two_shot(pend["M"]))
             self._launches += 1
+
+    def _two_shot(self, M: int) -> int:
+        return int(self.tp >= self.ar_two_shot_tp and M >= self.ar_two_shot_rows)
 
     def _flush(self):
         if self._pending:

@@ -15,6 +15,13 @@
 //                         registers, the prologue of the CONSUMING product: RMSNorm(1+w) and either the two int8 limb
 //                         planes + row scale (W8A16 GEMM) or the normalised bf16 row (bf16 GEMM).
 //
+// Two-shot form for many rows on four or more ranks (two_shot = 1): in the one-shot form every GPU serves each of its
+// partial rows to all tp requesters (tp x M x N x 2 bytes of NVLink egress per product); here rank r first reduces only
+// the rows m = r (mod tp) and writes the bf16 sums back over that row in EVERY rank's partial buffer (multimem.st
+// through the switch, or peer stores), the last block to finish publishes a second flag, and the row kernel then
+// reads the sums from LOCAL memory.  A row is read by its owner alone before the owner overwrites it, so the
+// exchange is in place; per GPU M x N x 2 bytes leave and arrive once, whatever tp is.
+//
 // Every rank reduces every row itself (one-shot): nothing is written to a peer but flags, so there is no second
 // barrier and no remote store to order; a row crosses NVLink tp-1 times per rank (10 KB per row at N = 5120), a few
 // percent of the time of the GEMM that produced it.  Tags come from the device step counter and the collective's
@@ -41,7 +48,12 @@ struct ArRowsParams {
   int M, N, tp, rank, order, mode;
   float eps;
   int rows_cap;                    // rows the partial buffers hold (checked builds; 0: unknown)
+  int two_shot;                    // 1: reduce-scatter + broadcast first (ar_reduce_bcast_kernel), the row kernel reads local sums
+                                   // (2 / 3: only the first / second of the two launches)
 };
+
+constexpr int kFlagRound2 = kMaxRanks;          // flag slots of the second round (one per source rank)
+constexpr int kFlagCounter = 2 * kMaxRanks;     // this rank's count of finished blocks of the reduce kernel
 
 TI_DEVICE uint4 ld_volatile16(const void* p) {
   uint4 v;
@@ -58,15 +70,26 @@ TI_DEVICE uint4 multimem_ld_reduce_bf16x8(uint64_t mc_addr) {
   return v;
 }
 
+// The same 16 bytes stored into every rank's copy of the multicast window.
+TI_DEVICE void multimem_st_bf16x8(uint64_t mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1,%2,%3,%4};\n" ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+TI_DEVICE void st_volatile16(void* p, uint4 v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// First shot of the two-shot form: block b owns row m = b * tp + rank.
 template <bool MC>
-__global__ void __launch_bounds__(512) ar_rows_kernel(const __grid_constant__ ArRowsParams p) {
-  __shared__ float red[16], red2[16];
-  __shared__ int s_ok;
-  const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+__global__ void __launch_bounds__(512) ar_reduce_bcast_kernel(const __grid_constant__ ArRowsParams p) {
+  __shared__ int s_last;
+  const int tid = threadIdx.x;
+  const int m = blockIdx.x * p.tp + p.rank;
   const unsigned tag = (*p.step_ptr) * 65536u + (unsigned)p.order + 1u;
   pdl_trigger();
   pdl_wait();                                  // the producing GEMM has completed: this rank's partials are in memory
-  if (m == 0 && tid == 0) {
+  if (blockIdx.x == 0 && tid == 0) {
     jitter();
     __threadfence_system();
     for (int q = 0; q < p.tp; ++q)
@@ -74,6 +97,63 @@ __global__ void __launch_bounds__(512) ar_rows_kernel(const __grid_constant__ Ar
   }
   if (tid < p.tp) {
     const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.flag_peer[p.rank]);
+    wait_flag_ge(mine + tid, tag, p.timeout_ns, p.status);
+  }
+  __syncthreads();
+  if (m < p.M && (p.rows_cap <= 0 || TI_CHECK(m, p.rows_cap, p.status))) {
+    const int nchunk = p.N >> 3;
+    const size_t row_off = (size_t)m * p.N * 2;
+    for (int c = tid; c < nchunk; c += 512) {
+      const size_t off = row_off + (size_t)c * 16;
+      if (MC) {
+        multimem_st_bf16x8(p.part_mc + off, multimem_ld_reduce_bf16x8(p.part_mc + off));
+      } else {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        for (int r = 0; r < p.tp; ++r) {         // rank order: the sum does not depend on who computes it
+          const uint4 q = ld_volatile16(reinterpret_cast<const uint8_t*>(p.part_peer[r]) + off);
+          const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { v[2 * i] += bf16lo(w4[i]); v[2 * i + 1] += bf16hi(w4[i]); }
+        }
+        const uint4 o = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+        for (int r = 0; r < p.tp; ++r) st_volatile16(reinterpret_cast<uint8_t*>(p.part_peer[r]) + off, o);
+      }
+    }
+  }
+  // every thread's stores are visible system-wide before this block is counted; the last block publishes round 2
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    unsigned* counter = reinterpret_cast<unsigned*>(p.flag_peer[p.rank]) + kFlagCounter;
+    const unsigned prev = atomicAdd(counter, 1u);
+    s_last = prev + 1 == gridDim.x;
+    if (s_last) {
+      *counter = 0;                              // ready for the next launch (launches of one rank are stream-ordered)
+      __threadfence_system();
+      jitter();
+      for (int q = 0; q < p.tp; ++q)
+        store_flag_release(reinterpret_cast<uint32_t*>(p.flag_peer[q]) + kFlagRound2 + p.rank, tag);
+    }
+  }
+}
+
+template <bool MC>
+__global__ void __launch_bounds__(512) ar_rows_kernel(const __grid_constant__ ArRowsParams p) {
+  __shared__ float red[16], red2[16];
+  const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const unsigned tag = (*p.step_ptr) * 65536u + (unsigned)p.order + 1u;
+  pdl_trigger();
+  pdl_wait();                                  // the producing GEMM has completed: this rank's partials are in memory
+  if (!p.two_shot && m == 0 && tid == 0) {
+    jitter();
+    __threadfence_system();
+    for (int q = 0; q < p.tp; ++q)
+      store_flag_release(reinterpret_cast<uint32_t*>(p.flag_peer[q]) + p.rank, tag);
+  }
+  if (tid < p.tp) {                            // two-shot: every rank has broadcast the sums of its rows (second flag round)
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(p.flag_peer[p.rank]) + (p.two_shot ? kFlagRound2 : 0);
     wait_flag_ge(mine + tid, tag, p.timeout_ns, p.status);
   }
   __syncthreads();
@@ -96,7 +176,8 @@ __global__ void __launch_bounds__(512) ar_rows_kernel(const __grid_constant__ Ar
 #pragma unroll
         for (int i = 0; i < 4; ++i) { v[j][2 * i] = bf16lo(w4[i]); v[j][2 * i + 1] = bf16hi(w4[i]); }
       } else {
-        for (int r = 0; r < p.tp; ++r) {       // rank order: every rank computes bit-identical sums
+        const int r0 = p.two_shot ? p.rank : 0, r1 = p.two_shot ? p.rank + 1 : p.tp;     // two-shot: the sums are local
+        for (int r = r0; r < r1; ++r) {        // rank order: every rank computes bit-identical sums
           const uint4 q = ld_volatile16(reinterpret_cast<const uint8_t*>(p.part_peer[r]) + off);
           const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
@@ -198,6 +279,18 @@ int ti_ar_rows(const ti::ArRowsParams* p, void* stream) {
   if (p->N % 8 || p->N > 512 * 5 * 8 || p->tp < 1 || p->tp > ti::kMaxRanks || p->mode < 0 || p->mode > 2) return -2;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e;
+  if (p->two_shot && p->tp > 1) {
+    // two_shot 1: both shots; 2 / 3: only the first / the second (ranks emulated one after the other on one GPU)
+    const dim3 g1((p->M + p->tp - 1) / p->tp);
+    e = cudaSuccess;
+    if (p->two_shot != 3) {
+      if (p->part_mc != 0) e = ti::launch_kernel(ti::ar_reduce_bcast_kernel<true>, g1, dim3(512), 0, st, true, *p);
+      else e = ti::launch_kernel(ti::ar_reduce_bcast_kernel<false>, g1, dim3(512), 0, st, true, *p);
+      if (e != cudaSuccess) return (int)e;
+    }
+    if (p->two_shot != 2) e = ti::launch_kernel(ti::ar_rows_kernel<false>, dim3(p->M), dim3(512), 0, st, true, *p);   // sums are local now
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+  }
   if (p->part_mc != 0) e = ti::launch_kernel(ti::ar_rows_kernel<true>, dim3(p->M), dim3(512), 0, st, true, *p);
   else e = ti::launch_kernel(ti::ar_rows_kernel<false>, dim3(p->M), dim3(512), 0, st, true, *p);
   return e != cudaSuccess ? (int)e : (int)cudaGetLastError();

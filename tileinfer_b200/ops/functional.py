@@ -80,7 +80,7 @@ class ArRowsParams(ctypes.Structure):
                 ("flag_peer", ctypes.c_uint64 * MAX_RANKS), ("resid", _P), ("h_out", _P), ("norm_w", _P), ("xh", _P),
                 ("xl", _P), ("xscale", _P), ("xn", _P), ("step_ptr", _P), ("status", _P),
                 ("timeout_ns", ctypes.c_ulonglong), ("M", _I), ("N", _I), ("tp", _I), ("rank", _I), ("order", _I),
-                ("mode", _I), ("eps", _F), ("rows_cap", _I)]
+                ("mode", _I), ("eps", _F), ("rows_cap", _I), ("two_shot", _I)]
 
 
 class EditParams(ctypes.Structure):
@@ -507,9 +507,12 @@ AR_NONE, AR_LIMBS, AR_BF16 = 0, 1, 2
 
 
 def ar_rows(comm, parity: int, M: int, N: int, resid, h_out, *, order: int, mode: int = AR_NONE, norm_w=None,
-            limbs: "Limbs" = None, xn=None, eps: float = 1e-6):
+            limbs: "Limbs" = None, xn=None, eps: float = 1e-6, two_shot: int = 0):
     """All-reduce of the row-parallel partials in `comm`'s symmetric buffer `parity` + residual -> h_out, fused with
-    the RMSNorm / activation-quantisation prologue of the consuming product (ops/csrc/fused_ar.cu)."""
+    the RMSNorm / activation-quantisation prologue of the consuming product (ops/csrc/fused_ar.cu).
+    two_shot = 1: every rank first reduces its 1/tp of the rows and broadcasts the sums into all ranks' buffers, the
+    row kernel then reads local memory (many rows on >= 4 ranks); 2 / 3 run only the first / second launch (tests
+    that emulate the ranks one after the other on one GPU)."""
     p = ArRowsParams()
     for r in range(comm.tp):
         p.part_peer[r] = comm.part_ptrs[parity][r]
@@ -523,6 +526,7 @@ def ar_rows(comm, parity: int, M: int, N: int, resid, h_out, *, order: int, mode
     p.step_ptr, p.status, p.timeout_ns = comm.step_ptr, comm.status_ptr, comm.timeout_ns
     p.M, p.N, p.tp, p.rank, p.order, p.mode, p.eps = M, N, comm.tp, comm.rank, order, mode, eps
     p.rows_cap = int(getattr(comm, "ar_rows", 0) or 0)
+    p.two_shot = int(two_shot)
     check(L().ti_ar_rows(ctypes.byref(p), stream()), "ti_ar_rows")
 
 
