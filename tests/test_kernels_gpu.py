@@ -860,6 +860,16 @@ def test_gdn_chunked_matches_recurrence(dk, hk, hv, state_bf16):
     assert torch.equal(state[1], state0[1]) and torch.equal(cs[1], cs0[1])      # an unused slot stays untouched
 
 
+def _limbs_equal_up_to_one_unit(a, b):
+    """Two quantisations of the same rows by kernels that add the squares of a row in a different order: the same
+    scales, the 16-bit values equal except for isolated roundings one unit apart."""
+    assert torch.equal(a.scale, b.scale)
+    qa = a.hi.int() * 256 + a.lo.int()
+    qb = b.hi.int() * 256 + b.lo.int()
+    d = (qa - qb).abs()
+    assert int(d.max()) <= 1 and float((d > 0).float().mean()) < 1e-3, (int(d.max()), float((d > 0).float().mean()))
+
+
 @pytest.mark.parametrize("M,N,tp", [(40, 384, 2), (300, 5120, 4), (17, 1024, 8)])
 def test_ar_rows_fused_allreduce_residual_norm_quant(M, N, tp):
     """The many-row all-reduce kernel with emulated ranks on one GPU (plain peer loads; the flags of all ranks are set
@@ -894,7 +904,7 @@ def test_ar_rows_fused_allreduce_residual_norm_quant(M, N, tp):
     ref = F.quant_rows(want_h, norm_w=nw)
     torch.cuda.synchronize()
     assert torch.equal(h1, want_h)
-    assert torch.equal(limbs.hi, ref.hi) and torch.equal(limbs.lo, ref.lo) and torch.equal(limbs.scale, ref.scale)
+    _limbs_equal_up_to_one_unit(limbs, ref)
     # mode 2: normalised bf16 rows
     h2 = torch.zeros_like(h)
     xn = torch.zeros(M, N, dtype=BF16, device="cuda")
@@ -922,7 +932,7 @@ def test_ar_rows_fused_allreduce_residual_norm_quant(M, N, tp):
     ref3 = F.quant_rows(want_h3, norm_w=nw)
     torch.cuda.synchronize()
     assert torch.equal(h3, want_h3)
-    assert torch.equal(limbs3.hi, ref3.hi) and torch.equal(limbs3.lo, ref3.lo) and torch.equal(limbs3.scale, ref3.scale)
+    _limbs_equal_up_to_one_unit(limbs3, ref3)
     # a flag that never arrives: the wait runs out, the status word says so, the context survives
     flags.zero_()
     comm.timeout_ns = 2 * 10 ** 6

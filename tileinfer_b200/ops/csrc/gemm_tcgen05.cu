@@ -435,7 +435,10 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* __
 }
 
 // The same for rows of up to 512 * 5 * 8 = 20480 elements in ONE pass: every thread keeps its (up to five) 16-byte
-// chunks of the row in registers between the statistics and the quantisation, so the row is read once.
+// chunks of the row in registers between the statistics and the quantisation, so the row is read once.  The block is
+// as small as the row allows (K / 40 threads, rounded up to warps: 128 threads at K = 5120), so that many rows are in
+// flight per SM: a row is a load -> reduce -> reduce -> store chain of a few microseconds, and 8192 rows of 512 threads
+// each pass through an SM only four at a time.
 __global__ void __launch_bounds__(512) quant_rows_fast_kernel(const __nv_bfloat16* __restrict__ x, int ldx,
                                                               const __nv_bfloat16* __restrict__ norm_w, float eps, int K,
                                                               int8_t* __restrict__ xh, uint8_t* __restrict__ xl,
@@ -444,13 +447,14 @@ __global__ void __launch_bounds__(512) quant_rows_fast_kernel(const __nv_bfloat1
   const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const __nv_bfloat16* row = x + (size_t)m * ldx;
   const int nchunk = K >> 3;
+  const int nthr = blockDim.x, nwarp = nthr >> 5;
   pdl_trigger();
   pdl_wait();
   float v[5][8];
   float ss = 0.f;
 #pragma unroll
   for (int j = 0; j < 5; ++j) {
-    const int c = tid + j * 512;
+    const int c = tid + j * nthr;
     uint4 q = make_uint4(0, 0, 0, 0);
     if (c < nchunk) q = *reinterpret_cast<const uint4*>(row + (size_t)c * 8);
     const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
@@ -465,7 +469,7 @@ __global__ void __launch_bounds__(512) quant_rows_fast_kernel(const __nv_bfloat1
     uint4 nwv[5];
 #pragma unroll
     for (int j = 0; j < 5; ++j) {
-      const int c = tid + j * 512;
+      const int c = tid + j * nthr;
       nwv[j] = c < nchunk ? *reinterpret_cast<const uint4*>(norm_w + (size_t)c * 8) : make_uint4(0, 0, 0, 0);
     }
     ss = warp_sum(ss);
@@ -473,7 +477,7 @@ __global__ void __launch_bounds__(512) quant_rows_fast_kernel(const __nv_bfloat1
     __syncthreads();
     float tot = 0.f;
 #pragma unroll
-    for (int w = 0; w < 16; ++w) tot += red[w];
+    for (int w = 0; w < 16; ++w) tot += w < nwarp ? red[w] : 0.f;
     const float rr = rsqrtf(tot / (float)K + eps);
 #pragma unroll
     for (int j = 0; j < 5; ++j) {
@@ -495,7 +499,7 @@ __global__ void __launch_bounds__(512) quant_rows_fast_kernel(const __nv_bfloat1
   __syncthreads();
   float a = 0.f;
 #pragma unroll
-  for (int w = 0; w < 16; ++w) a = fmaxf(a, red2[w]);
+  for (int w = 0; w < 16; ++w) a = fmaxf(a, w < nwarp ? red2[w] : 0.f);
   int e = (int)((__float_as_uint(a) >> 23) & 0xffu) - 127;
   e = max(e, -100);
   if (!(a < 3.0e38f)) e = 127;
@@ -503,7 +507,7 @@ __global__ void __launch_bounds__(512) quant_rows_fast_kernel(const __nv_bfloat1
   if (tid == 0) xscale[m] = exp2f((float)(e - 14));
 #pragma unroll
   for (int j = 0; j < 5; ++j) {
-    const int c = tid + j * 512;
+    const int c = tid + j * nthr;
     if (c >= nchunk) continue;
     uint32_t hw[2] = {0, 0}, lw[2] = {0, 0};
 #pragma unroll
@@ -627,7 +631,7 @@ int ti_quant_rows(const void* x, int ldx, const void* norm_w, float eps, int M, 
   const bool aligned = (K % 8 == 0) && (ldx % 8 == 0) && (((uintptr_t)x | (uintptr_t)xh | (uintptr_t)xl) % 16 == 0) &&
                        (norm_w == nullptr || (uintptr_t)norm_w % 16 == 0);
   if (aligned && K <= 512 * 5 * 8)
-    ti::launch_kernel(ti::quant_rows_fast_kernel, dim3(M), dim3(512), 0, (cudaStream_t)stream, true, (const __nv_bfloat16*)x, ldx,
+    ti::launch_kernel(ti::quant_rows_fast_kernel, dim3(M), dim3(std::min(512, ((K / 8 + 4) / 5 + 31) / 32 * 32)), 0, (cudaStream_t)stream, true, (const __nv_bfloat16*)x, ldx,
                       (const __nv_bfloat16*)norm_w, eps, K, (int8_t*)xh, (uint8_t*)xl, (float*)xscale);
   else
     ti::quant_rows_kernel<<<M, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)norm_w,
