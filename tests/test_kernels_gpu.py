@@ -861,13 +861,15 @@ def test_gdn_chunked_matches_recurrence(dk, hk, hv, state_bf16):
 
 
 def _limbs_equal_up_to_one_unit(a, b):
-    """Two quantisations of the same rows by kernels that add the squares of a row in a different order: the same
-    scales, the 16-bit values equal except for isolated roundings one unit apart."""
+    """Two quantisations of the same rows by kernels that add the squares of a row in a different order (the RMS factor
+    may differ in its last bit): the same scales; the normalised values are rounded to bf16 before they are quantised, so
+    isolated elements may sit one bf16 step (2^-7 of their magnitude) apart, all others are equal."""
     assert torch.equal(a.scale, b.scale)
     qa = a.hi.int() * 256 + a.lo.int()
     qb = b.hi.int() * 256 + b.lo.int()
     d = (qa - qb).abs()
-    assert int(d.max()) <= 1 and float((d > 0).float().mean()) < 1e-3, (int(d.max()), float((d > 0).float().mean()))
+    assert bool((d <= 1 + qa.abs() // 128).all()) and float((d > 0).float().mean()) < 1e-2, \
+        (int(d.max()), float((d > 0).float().mean()))
 
 
 @pytest.mark.parametrize("M,N,tp", [(40, 384, 2), (300, 5120, 4), (17, 1024, 8)])

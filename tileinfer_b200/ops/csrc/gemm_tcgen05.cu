@@ -71,7 +71,7 @@ struct GemmParams {
   unsigned* tile_count;            // [tiles_n * tiles_m] arrival counters, zero between launches
   int M, N, K, ldo, epi;
   int kb_per_split;                // 128-byte k stages per gridDim.z slice
-  int ablate;                      // timing experiments only (TI_GEMM_ABLATE): 1 no MMA, 2 no activation copies, 4 no weight copies
+  int ablate;                      // timing experiments only (TI_GEMM_ABLATE): 1 no MMA, 2 no activation copies, 4 no weight copies, 8 no epilogue, 16 no main loop, 32 no split-k reduction, 64 no fence before the split-k count
 };
 
 // kind::i8 instruction descriptor: D = s32, A = int8 (K-major), B = int8 / uint8 (K-major), M = 128, N = BN
@@ -87,7 +87,7 @@ template <int BN> TI_DEVICE constexpr uint32_t idesc_bf16() {
 enum { GEPI_STORE = 0, GEPI_SWIGLU = 1, GEPI_ROWPAR = 2, GEPI_F32 = 3 };
 
 // fused epilogue for four adjacent weight rows n..n+3 of one token (N is a multiple of 4 here): split-k reduction
-TI_DEVICE void gemm_epilogue4(const GemmParams& p, int m, int n, float4 v) {
+TI_DEVICE void gemm_epilogue4(const GemmParams& p, int m, int n, float4 v, uint2 r) {
   if (p.epi == GEPI_SWIGLU) {
     const float g0 = round_bf16(v.x), u0 = round_bf16(v.y), g1 = round_bf16(v.z), u1 = round_bf16(v.w);
     *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + (n >> 1)) =
@@ -98,8 +98,7 @@ TI_DEVICE void gemm_epilogue4(const GemmParams& p, int m, int n, float4 v) {
     *reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)m * p.ldo + n) = v;
     return;
   }
-  if (p.epi == GEPI_ROWPAR) {
-    const uint2 r = *reinterpret_cast<const uint2*>(p.resid + (size_t)m * p.N + n);
+  if (p.epi == GEPI_ROWPAR) {                      // r: the residual row's four values, loaded by the caller
     v.x += bf16lo(r.x);
     v.y += bf16hi(r.x);
     v.z += bf16lo(r.y);
@@ -331,7 +330,7 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
   }
   if (S > 1) {
     // ---- split-k: the last CTA of this output tile to arrive adds the partials in split order
-    __threadfence();
+    if (!(p.ablate & 64)) __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
       const unsigned prev = atomicAdd(p.tile_count + tile_n * gridDim.x + tile_m, 1u);
@@ -340,31 +339,49 @@ __global__ void __launch_bounds__(kGemmThreads, TI_GEMM_RING_KB <= 100 ? 2 : 1) 
       __threadfence();
     }
     __syncthreads();
-    if (s_last && warp >= 2 && warp < 6) {
-      // lane -> four adjacent output features, warp -> every fourth token; the loads of four tokens and all
-      // slices are issued before the first is used
+    if (s_last && warp >= 2 && warp < 6 && !(p.ablate & 32)) {
+      // lane -> four adjacent output features, warp -> every fourth token.  The partial sums of four tokens and four
+      // slices (and the residual rows) are requested together before the first is used: with the loads inside a
+      // loop of run-time length each one waited for the one before it (12 memory round trips per four tokens; the
+      // reduction of a 64-token tile took 27 us).  The slices are added in ascending order whatever the grouping.
       const int m_end = min(p.M, (tile_m + 1) * BN);
       for (int hh = 0; hh < BMH; ++hh) {
       const int n4 = tile_n * (BMH * kBM) + hh * kBM + lane * 4;
+      if (n4 >= p.N) continue;
       for (int m0 = tile_m * BN + (warp - 2); m0 < m_end; m0 += 16) {
         float4 acc[4];
+        uint2 rs[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          rs[u] = make_uint2(0u, 0u);
           const int m = m0 + 4 * u;
-          if (m < m_end && n4 < p.N)
-            for (int z = 0; z < S; ++z) {
-              const float4 v = __ldcg(reinterpret_cast<const float4*>(p.part + ((size_t)z * p.M + m) * p.N + n4));
-              acc[u].x += v.x;
-              acc[u].y += v.y;
-              acc[u].z += v.z;
-              acc[u].w += v.w;
+          if (m < m_end && p.epi == GEPI_ROWPAR) rs[u] = __ldcg(reinterpret_cast<const uint2*>(p.resid + (size_t)m * p.N + n4));
+        }
+        for (int z0 = 0; z0 < S; z0 += 4) {
+          float4 v[4][4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int zz = 0; zz < 4; ++zz) {
+              const int m = m0 + 4 * u, z = z0 + zz;
+              v[u][zz] = (m < m_end && z < S) ? __ldcg(reinterpret_cast<const float4*>(p.part + ((size_t)z * p.M + m) * p.N + n4))
+                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int zz = 0; zz < 4; ++zz) {
+              acc[u].x += v[u][zz].x;
+              acc[u].y += v[u][zz].y;
+              acc[u].z += v[u][zz].z;
+              acc[u].w += v[u][zz].w;
             }
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const int m = m0 + 4 * u;
-          if (m < m_end && n4 < p.N) gemm_epilogue4(p, m, n4, acc[u]);
+          if (m < m_end) gemm_epilogue4(p, m, n4, acc[u], rs[u]);
         }
       }
       }
@@ -592,25 +609,29 @@ static int pick_bmh(int M, int n_tiles) {
   const long long tiles256 = (long long)((n_tiles * 8 + 255) / 256) * ((M + 127) / 128);
   if (M <= 64) {
     // few tokens: the limb planes are as many bytes per stage as the weights of a 128-row tile; with 256 rows they
-    // would be a third.  Measured at 64 tokens on the 27B shapes: in_proj 32.7 -> 62.8 us, down 51 -> 91 us, out_proj
-    // 38 -> 72 us, gate_up 65 -> 62 us: halving the number of CTAs (and the deeper k split it forces) costs more
-    // than the bytes saved, so this stays off (TI_GEMM_BMH_SMALL=1 turns it on).
+    // are half.  That pays only where no k split follows from halving the number of tiles.  Measured at 64 tokens on
+    // the 27B shapes (us, 128-row -> 256-row tiles): gate_up 43.6 -> 37.6 (136 tiles, no split), in_proj 23 -> 49
+    // (65 tiles in two k slices), down 47 -> 80, out_proj 36 -> 71.  TI_GEMM_BMH_SMALL=1 forces 256 rows.
     static const int small = [] {
       const char* e = getenv("TI_GEMM_BMH_SMALL");
       return e == nullptr ? 0 : atoi(e);
     }();
-    return (small && n_tiles >= 64) ? 2 : 1;
+    if (small && n_tiles >= 64) return 2;
+    return tiles256 >= 120 ? 2 : 1;          // enough 256-row tiles to fill the GPU without a k split (gate_up: 44 -> 38 us)
   }
   return (n_tiles >= 32 && tiles256 >= 2 * 148) ? 2 : 1;
 }
 
-// k split that fills the 148 SMs when there are few output tiles (at least 8 stages = 1024 bytes of k per slice);
-// sets kb_per_split.  KB counts stages of 128 bytes of k.
+// k split that fills the 148 SMs when there are few output tiles; sets kb_per_split.  KB counts stages of 128 bytes
+// of k; a slice has at least 16 of them (TI_GEMM_SPLIT_STAGES).  Measured at 64 tokens on N = 5120 (us): K = 6144
+// unsplit 28.8, three slices 22.2; K = 17408 unsplit 57.5, three slices 32.3.
 static int plan_split(GemmParams& p, int KB, int tiles, int M, int N, int ldo, void* part, size_t part_bytes,
                       void* tile_count, int n_count) {
   int S = 1;
   if (part != nullptr && tile_count != nullptr && tiles < 120 && N % 4 == 0 && ldo % 4 == 0) {
-    S = std::min(std::min(148 / tiles, KB / 8), 16);
+    static const int max_split = [] { const char* e = getenv("TI_GEMM_MAX_SPLIT"); return e == nullptr ? 16 : atoi(e); }();
+    static const int min_stages = [] { const char* e = getenv("TI_GEMM_SPLIT_STAGES"); return e == nullptr ? 16 : std::max(1, atoi(e)); }();
+    S = std::min(std::min(std::min(148 / tiles, KB / min_stages), 16), max_split);
     while (S > 1 && ((size_t)S * M * N * 4 > part_bytes || tiles > n_count)) --S;
     if (S < 1) S = 1;
   }
