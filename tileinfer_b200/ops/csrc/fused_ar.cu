@@ -111,9 +111,13 @@ __global__ void __launch_bounds__(512) ar_reduce_bcast_kernel(const __grid_const
         float v[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.f;
-        for (int r = 0; r < p.tp; ++r) {         // rank order: the sum does not depend on who computes it
-          const uint4 q = ld_volatile16(reinterpret_cast<const uint8_t*>(p.part_peer[r]) + off);
-          const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+        uint4 q[kMaxRanks];                      // all ranks' loads in flight together, summed in rank order
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          q[r] = r < p.tp ? ld_volatile16(reinterpret_cast<const uint8_t*>(p.part_peer[r]) + off) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {
+          const uint32_t w4[4] = {q[r].x, q[r].y, q[r].z, q[r].w};
 #pragma unroll
           for (int i = 0; i < 4; ++i) { v[2 * i] += bf16lo(w4[i]); v[2 * i + 1] += bf16hi(w4[i]); }
         }
@@ -177,9 +181,13 @@ __global__ void __launch_bounds__(512) ar_rows_kernel(const __grid_constant__ Ar
         for (int i = 0; i < 4; ++i) { v[j][2 * i] = bf16lo(w4[i]); v[j][2 * i + 1] = bf16hi(w4[i]); }
       } else {
         const int r0 = p.two_shot ? p.rank : 0, r1 = p.two_shot ? p.rank + 1 : p.tp;     // two-shot: the sums are local
-        for (int r = r0; r < r1; ++r) {        // rank order: every rank computes bit-identical sums
-          const uint4 q = ld_volatile16(reinterpret_cast<const uint8_t*>(p.part_peer[r]) + off);
-          const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+        uint4 q[kMaxRanks];                    // all ranks' loads in flight together; rank order: bit-identical sums everywhere
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          q[r] = (r >= r0 && r < r1) ? ld_volatile16(reinterpret_cast<const uint8_t*>(p.part_peer[r]) + off) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {
+          const uint32_t w4[4] = {q[r].x, q[r].y, q[r].z, q[r].w};
 #pragma unroll
           for (int i = 0; i < 4; ++i) { v[j][2 * i] += bf16lo(w4[i]); v[j][2 * i + 1] += bf16hi(w4[i]); }
         }
