@@ -147,3 +147,22 @@ def test_edited_requests_stay_on_the_device_path_and_match_the_host_sampler():
     b = LLM("preset:tiny-hybrid", quantization="w8a16", num_kvcache_blocks=128, max_num_seqs=8, max_model_len=512)
     b.model_runner.model.EDIT_SLOTS = -1
     assert a.generate_token_ids([prompts[0]], sp) == b.generate_token_ids([prompts[0]], sp)
+
+
+def test_a_set_device_status_word_stops_the_engine():
+    """The status word the kernels raise when a bounded wait runs out travels to the host with every step's tokens; a
+    non-zero word must stop the step (its tokens are discarded) instead of letting wrong results through."""
+    from tileinfer_b200.engine.llm import LLM
+    from tileinfer_b200.engine.sampling_params import SamplingParams
+    from tileinfer_b200.parallel.watchdog import PeerLostError
+    llm = LLM("preset:tiny-hybrid", quantization="w8a16", num_kvcache_blocks=64, max_num_seqs=4, max_model_len=256)
+    prompt = [[5, 9, 200, 31, 77, 8]]
+    ok = llm.generate_token_ids(prompt, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    assert len(ok[0]) == 4
+    model = llm.model_runner.model
+    model.ctrl[1] = 1                                   # what wait_flag_ge / mbar_wait do on expiry
+    with pytest.raises(PeerLostError) as e:
+        llm.generate_token_ids(prompt, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    assert "status word" in str(e.value)
+    model.ctrl[1] = 0
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0

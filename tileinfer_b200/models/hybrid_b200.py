@@ -882,10 +882,13 @@ class _RunMixin:
         t.h_tok.copy_(t.tok, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         status = int(t.h_tok[t.tok.shape[0] - 1])
-        if status != 0 and self.peer is not None:
+        if status != 0:
+            # a bounded device wait ran out (a peer's flag or packet, an mbarrier) or a checked index was out of range:
+            # whatever the kernels computed after that is not to be trusted, on one GPU as on eight
             from ..parallel.watchdog import PeerLostError
             err = PeerLostError([])
-            err.args = (f"a bounded wait on a tensor-parallel peer ran out (device status word {status:#x}): "
+            err.args = (f"device status word {status:#x}: a bounded wait ran out"
+                        f"{' on a tensor-parallel peer' if self.peer is not None else ''} or an index check failed; "
                         "the tokens of this step are discarded",)
             raise err
         return t.h_tok[:n].tolist()
