@@ -6,8 +6,8 @@
 // (8 KB stages: 3.9 TB/s over the GPU; the GEMM's old 16 KB stage of three copies: 4.6; a 32 KB stage of three copies: 8.5
 // from one producer thread, 12.2 from two).  The GEMM's stage size and second producer thread follow from this.
 //
-// build: nvcc -gencode arch=compute_100a,code=sm_100a -O3 -std=c++17 -I tileinfer_b200/ops/csrc benchmarks/tma_issue_probe.cu -o /tmp/tma_issue_probe -lcuda
-// run:   /tmp/tma_issue_probe        (prints one line per mode x producers x grid: time, GB/s)
+// build: nvcc -gencode arch=compute_100a,code=sm_100a -O3 -std=c++17 -I tileinfer_b200/ops/csrc benchmarks/tma_issue_probe.cu -o benchmarks/tma_issue_probe -lcuda
+// run:   benchmarks/tma_issue_probe        (prints one line per mode x producers x grid: time, GB/s)
 #include <cstdio>
 #include <cstdlib>
 #include <vector>
