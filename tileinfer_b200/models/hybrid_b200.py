@@ -111,10 +111,11 @@ class _ModelBase:
         # steps in which some sequence has at least this many tokens use the chunk-parallel DeltaNet kernels
         self.gdn_chunk_min_tokens = int(os.environ.get("TI_GDN_CHUNK_MIN", "32"))
         self.gdn_ws = F.GdnChunkWorkspace(dev)
-        # more rows than this: tcgen05 GEMM.  (Measured on the 27B model, one GPU, ms per decode step: 4 rows 10.7 on
-        # the GEMV; 8 rows 16.0 on the GEMV, whose long-k products then need two passes over the weights; 16 rows 12.2
-        # on the GEMM.)
-        self.gemm_min_rows = int(os.environ.get("TI_GEMM_MIN_ROWS", "4"))
+        # more rows than this: tcgen05 GEMM; the persistent GEMV chain serves single rows.  (Measured on the 27B model,
+        # one GPU, ms per decode step: 1 row 6.6 on the GEMV chain; 2 / 3 / 4 rows 8.2 / - / 10.5 on the GEMV against
+        # 6.9 / 7.4 / 7.4 on the GEMM; 8 rows 16.0 on the GEMV, whose long-k products then need two passes over the
+        # weights, 7.7 on the GEMM.)
+        self.gemm_min_rows = int(os.environ.get("TI_GEMM_MIN_ROWS", "1"))
 
     # ------------------------------------------------------------------ weights: build / on-disk shard cache
     _LINEAR = ("gate_up", "down", "in_proj", "out", "qkv", "o")

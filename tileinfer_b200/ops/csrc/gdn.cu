@@ -742,7 +742,11 @@ int ti_gdn_step(const ti::GdnParams* p, int num_seqs, int dk, int dv, int state_
     // more (head, sequence) pairs than two waves of SMs: blocks walk several sequences with staged state
     const bool staged = (long long)p->hv * num_seqs > 2 * 148;
     // large batches without snapshots: column-split blocks (split 3 keeps the staged kernel: tests, comparisons)
-    if (staged && split == 2 && p->snap_rel == nullptr) {
+    static const long long split_min = [] {
+      const char* e = getenv("TI_GDN_SPLIT_MIN");            // (head, sequence) pairs from which the column-split kernel runs
+      return e == nullptr ? 2LL * 148 : atoll(e);
+    }();
+    if ((long long)p->hv * num_seqs > split_min && split == 2 && p->snap_rel == nullptr) {
       if (dk == 128 && dv == 128)
         e = state_bf16 ? ti::launch_token_split<128, 128, __nv_bfloat16>(*p, num_seqs, st) : ti::launch_token_split<128, 128, float>(*p, num_seqs, st);
       else if (dk == 64 && dv == 64)
