@@ -80,8 +80,9 @@ class _ModelBase:
                 rows = max(int(config.max_num_batched_tokens), int(config.max_num_seqs), 64)
             self.peer = PeerComm(comm, self.H, m_cap=64, ar_rows=rows)
         self._ar_pending = None            # a many-row all-reduce whose result nobody has consumed yet
-        self.ar_min_rows = int(os.environ.get("TI_AR_MIN_ROWS", "4"))   # more rows than this: GEMM + fused all-reduce
-        # (measured at TP = 2: batch 8 964 -> 1167 tok/s, batch 16 1400 -> 2181 tok/s against the packet GEMV in several passes)
+        self.ar_min_rows = int(os.environ.get("TI_AR_MIN_ROWS", "3"))   # more rows than this: GEMM + fused all-reduce
+        # (measured at TP = 2, tok/s, packet GEMV -> GEMM + ar_rows: batch 2 331 -> 323, batch 4 590 -> 617, batch 8
+        # 964 -> 1167, batch 16 1400 -> 2181)
         # two-shot all-reduce (reduce 1/tp of the rows, broadcast the sums, then read locally) from this many rows on this
         # many ranks: the one-shot form moves tp times more bytes per GPU, which only matters once the rows are many
         self.ar_two_shot_rows = int(os.environ.get("TI_AR_TWO_SHOT_ROWS", "256"))
