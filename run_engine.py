@@ -33,6 +33,7 @@ def main(argv=None):
         print(out["text"])
         if args.stats:
             print(json.dumps(llm.stats(), indent=1))
+    llm.close()
     return out
 
 

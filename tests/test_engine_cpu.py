@@ -77,3 +77,16 @@ def test_generate_and_stream_api():
     events = list(llm.generate_stream(["hello"], sp))
     assert [e[0] for e in events] == [0] * 5 and [e[2] for e in events] == [False] * 4 + [True]
     assert llm.stats()["finished_requests"] == 3
+
+
+def test_close_is_idempotent_and_cli_runs_through_it(capsys):
+    """`LLMEngine.close()` (graphs, peer buffers, own process group) is safe on the CPU executor and when called twice;
+    the command-line entry point ends with it."""
+    from tileinfer_b200.engine.llm import LLM
+    llm = LLM("preset:tiny-hybrid", device="cpu", num_kvcache_blocks=32, max_num_seqs=2, max_model_len=128)
+    llm.close()
+    llm.close()
+    import run_engine
+    out = run_engine.main(["--model", "preset:tiny-hybrid", "--device", "cpu", "--prompt", "hi", "--max-tokens", "3",
+                           "--temperature", "0"])
+    assert isinstance(out["text"], str)

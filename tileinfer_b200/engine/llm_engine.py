@@ -31,6 +31,7 @@ class LLMEngine:
     def __init__(self, model: str, comm=None, **kwargs):
         self.config = Config(model, **kwargs)
         cfg = self.config
+        self._owns_process_group = comm is None and cfg.tp_size > 1      # close() then also destroys the process group
         self.comm = comm if comm is not None else init_distributed(cfg.tp_size, cfg.nccl_timeout, cfg.device)
         if self.comm.world_size != cfg.tp_size:
             raise RuntimeError(f"communicator has {self.comm.world_size} ranks, tp_size={cfg.tp_size}")
@@ -227,6 +228,28 @@ class LLMEngine:
                 seq.finish_reason = seq.finish_reason or "abort"
             self.model_runner.free_deltanet_slot(seq.seq_id)
             self._all_seqs.pop(seq.seq_id, None)
+
+    def close(self):
+        """Orderly shutdown (every rank calls it): captured decode graphs go first (graphs that captured NCCL
+        collectives must not outlive the communicator), then the peer-memory buffers, then the process group this
+        engine created.  Safe to call twice; the CPU executor has nothing to release."""
+        if getattr(self, "_closed", False):
+            return
+        self._closed = True
+        if self.watchdog is not None and hasattr(self.watchdog, "stop"):
+            self.watchdog.stop()
+        model = getattr(self.model_runner, "model", None)
+        if hasattr(model, "release_graphs"):
+            model.release_graphs()
+        peer = getattr(model, "peer", None)
+        if peer is not None:
+            peer.close()
+            model.peer = None
+        if getattr(self, "_owns_process_group", False):
+            import torch.distributed as dist
+            if dist.is_initialized():
+                dist.barrier()
+                dist.destroy_process_group()
 
     def stats(self) -> dict:
         return self._stats.snapshot(self.scheduler, self.model_runner)
