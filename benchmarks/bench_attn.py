@@ -9,7 +9,7 @@ fraction of a hard-coded A100 peak).  Here:
 * decode: the split-KV paged kernel (ops/csrc/attn_paged.cu) for a batch of single-token queries; GB/s of K/V
   bytes against the MEASURED copy bandwidth (`hbm_gbs`).
 
-    python benchmarks/bench_attn.py [--out gpurun_out/attn.json]
+    python benchmarks/bench_attn.py [--out attn.json]
 """
 from __future__ import annotations
 

@@ -8,7 +8,7 @@ kernels/deltanet_fused.py:634-684, kernels/rms_norm.py, kernels/residual_rmsnorm
 run here is recorded with its one-line error; nothing of the reference is patched.  CUDA events, weights rotated over
 copies larger than L2.
 
-    python benchmarks/bench_reference_kernels.py [--out gpurun_out/ref_kernels.json]
+    python benchmarks/bench_reference_kernels.py [--out ref_kernels.json]
 """
 import argparse
 import json

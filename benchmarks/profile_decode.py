@@ -7,7 +7,7 @@ writes a Chrome trace.  That mode is the counterpart of the reference's tests/pr
 `TI_NVTX=1` adds an NVTX range per layer and block for external timeline tools.
 
     python benchmarks/profile_decode.py --model preset:qwen3.6-27b-8l --batch 1 --ctx 256 --steps 3
-    python benchmarks/profile_decode.py --model preset:qwen3.6-27b-8l --torch-profiler --trace gpurun_out/decode_trace.json
+    python benchmarks/profile_decode.py --model preset:qwen3.6-27b-8l --torch-profiler --trace decode_trace.json
 """
 import argparse
 import os

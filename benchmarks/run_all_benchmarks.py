@@ -6,7 +6,7 @@ tests/bench_multi_gpu.py:235-275: for every tensor-parallel degree in --gpus the
 processes (torchrun for more than one GPU); the aggregate holds every JSON line they print plus a scaling table
 (tok/s, speed-up over one GPU, efficiency = speed-up / GPUs) for decode and prefill.
 
-    python benchmarks/run_all_benchmarks.py --gpus 1,2,4,8 --out gpurun_out/all_benchmarks.json [--quick]
+    python benchmarks/run_all_benchmarks.py --gpus 1,2,4,8 --out all_benchmarks.json [--quick]
 """
 import argparse
 import json

@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(512) ar_reduce_bcast_kernel(const __grid_const
       }
     }
   }
-  // every thread's stores are visible system-wide before this block is counted; the last block publishes round 2
+  // every thread's stores are visible system-wide before this block is counted; the last block publishes the second flag
   __threadfence_system();
   __syncthreads();
   if (tid == 0) {
