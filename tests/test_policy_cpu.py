@@ -240,3 +240,60 @@ def test_prefix_hit_under_memory_pressure_does_not_crash():
     # a request that fits after evicting part of the cached prefix still gets blocks
     small = Sequence(shared[:32] + _prompt(8, 93))     # 40 tokens = 3 blocks
     assert sch._allocate_blocks_for_new_seq(small) and len(small.block_table) == 3
+
+
+def test_gdn_chunk_table_cuts_at_64_tokens_and_at_snapshot_points():
+    """Host side of the chunk-parallel DeltaNet prefill: chunks of at most 64 tokens that never straddle a snapshot
+    point; the snapshot entry rides on the chunk that ends there."""
+    from tileinfer_b200.ops import functional as F
+    ck, seq_ck = F.gdn_chunk_table([0, 1, 8, 208, 272])                       # lengths 1, 7, 200, 64; no snapshots
+    assert seq_ck.tolist() == [0, 1, 2, 6, 7]
+    assert ck[2].tolist() == [1, 7, 64, 64, 64, 8, 64] and ck[1].tolist() == [0, 1, 8, 72, 136, 200, 208]
+    assert ck[0].tolist() == [0, 1, 2, 2, 2, 2, 3] and set(ck[3].tolist()) == {-1}
+    # snapshots after 48 and 192 tokens of a 200-token sequence (entries 5 and 9), after 64 of a 64-token one (entry 2)
+    ck, seq_ck = F.gdn_chunk_table([0, 200, 264], [[48, 192], [64]], [[5, 9], [2]])
+    lens, snaps = ck[2].tolist(), ck[3].tolist()
+    assert sum(lens[:seq_ck[1]]) == 200 and max(lens) <= 64
+    ends = [int(ck[1][i]) + lens[i] for i in range(seq_ck[1])]
+    assert 48 in ends and 192 in ends
+    assert snaps[ends.index(48)] == 5 and snaps[ends.index(192)] == 9 and snaps[-1] == 2
+    assert [s for s in snaps if s >= 0] == [5, 9, 2]
+    # a point past the end of the step's tokens is ignored
+    ck, _ = F.gdn_chunk_table([0, 30], [[16, 40]], [[1, 7]])
+    assert ck[2].tolist() == [16, 14] and ck[3].tolist() == [1, -1]
+
+
+def test_device_sampling_spec_draws_like_the_host_sampler():
+    """What the device sampler is fed is built on the host: the uniform numbers come from the shared generator in row
+    order and only for rows that sample; an edited row carries the additive row its constraint makes of zeros and the
+    sorted ids that get the repetition penalty (rank-local)."""
+    from tileinfer_b200.engine.constraints import make_constraint
+    from tileinfer_b200.engine.sampler import Sampler
+    from tileinfer_b200.parallel.comm import SingleComm
+
+    def seqs():
+        out = []
+        for sp, toks in ((SamplingParams(temperature=0.0), [3, 4]), (SamplingParams(temperature=0.7, top_k=20), [9, 9, 5]),
+                         (SamplingParams(temperature=0.8, top_k=1), [1]),
+                         (SamplingParams(temperature=0.5, repetition_penalty=1.3, bad_token_ids=[7]), [40, 2, 40, 130])):
+            s = Sequence(list(toks), sp)
+            s.constraint = make_constraint(sp, None)                 # what LLMEngine.add_request does
+            out.append(s)
+        return out
+    a, b = Sampler(SingleComm(), 32, (127,), seed=11), Sampler(SingleComm(), 32, (127,), seed=11)
+    a._v_local = b._v_local = 96                                     # this rank owns token ids 32..127
+    ss = seqs()
+    spec = a.device_spec(ss, edit_rows=[3])
+    want = torch.rand(2, 1, generator=b.gen)                         # rows 1 and 3 sample; rows 0 (greedy) and 2 (top-k 1) do not
+    assert spec["u"][0] == 0.0 and spec["u"][2] == 0.0
+    assert spec["u"][1] == float(want[0, 0]) and spec["u"][3] == float(want[1, 0])
+    assert spec["temperature"] == [0.0, 0.7, 0.8, 0.5] and spec["top_k"][1] == 20
+    (row, add, pen, rp), = spec["edits"]
+    assert row == 3 and rp == 1.3
+    assert pen.tolist() == [8]                                       # ids 40 -> local 8; 2 belongs to another rank, 130 - 32 = 98 is past this shard
+    assert add is not None and add.shape == (96,) and float(add.max()) == 0.0 and int(torch.isinf(add).sum()) == 0    # bad id 7 is another rank's
+    # the same request on the rank that owns token 7: its additive row masks it
+    c = Sampler(SingleComm(), 0, (127,), seed=11)
+    c._v_local = 32
+    (_, add0, pen0, _), = c.device_spec(seqs(), edit_rows=[3])["edits"]
+    assert float(add0[7]) == float("-inf") and int(torch.isinf(add0).sum()) == 1 and pen0.tolist() == [2]
