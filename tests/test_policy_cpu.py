@@ -297,3 +297,28 @@ def test_device_sampling_spec_draws_like_the_host_sampler():
     c._v_local = 32
     (_, add0, pen0, _), = c.device_spec(seqs(), edit_rows=[3])["edits"]
     assert float(add0[7]) == float("-inf") and int(torch.isinf(add0).sum()) == 1 and pen0.tolist() == [2]
+
+
+def test_all_reduce_flags_are_rebased_behind_the_next_tags():
+    """The many-row all-reduce waits for 'flag >= tag' modulo 2^32.  A flag left by a collective long ago would look ahead
+    of the next tags once the step counter has advanced by more than 2^15; the periodic scrub therefore rewrites every
+    flag to step * 65536, which no tag of this or a later step counts as reached, across the 32-bit wrap too."""
+    from tileinfer_b200.parallel.symm_mem import flag_rebase_value
+
+    def ready(flag, want):                                  # wait_flag_ge in ops/csrc/common.cuh
+        d = (flag - want) & 0xFFFFFFFF
+        return d < (1 << 31)
+
+    def tag(step, order):
+        return (step * 65536 + order + 1) & 0xFFFFFFFF
+
+    stale = tag(10, 3)
+    assert ready(stale, tag(10, 3)) and not ready(stale, tag(11, 0))
+    assert ready(stale, tag(10 + 40000, 0))                 # the hazard: 40000 steps later the old flag passes for a fresh one
+    for step in (0, 7, 32767, 32768, 40010, 65535, 65536, 65537, 2 ** 20 + 5):
+        base = flag_rebase_value(step) & 0xFFFFFFFF
+        assert -(1 << 31) <= flag_rebase_value(step) < (1 << 31)
+        for later in (0, 1, 100, 32767):                    # until the next scrub, at most 2^15 steps away
+            for order in (0, 1, 200, 65534):
+                assert not ready(base, tag(step + later, order)), (step, later, order)
+        assert ready(tag(step, 5), tag(step, 5)) and ready(tag(step + 1, 0), tag(step, 5))

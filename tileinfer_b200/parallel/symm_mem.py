@@ -153,6 +153,14 @@ class PeerComm:
         self.comm.barrier()                   # nobody is still sending into anybody's buffer
         for ptr, n in zip(self._local, (self.ll_bytes, self.cand_bytes)):
             F.check(lib.ti_memset_async(ctypes.c_void_p(ptr), 0, n, None), "ti_memset_async")
+        # The flags of the many-row all-reduce are compared modulo 2^32 ("at least this tag"): a flag left behind by a
+        # collective more than 2^15 steps ago would look AHEAD of the next tags.  All ranks are at the same step here:
+        # every flag is put just behind the tags that come next (the block counter of the two-shot form stays zero).
+        if self.tp > 1:
+            flags = _tensor_from_ptr(self.flag_ptrs[self.rank], 64, torch.int32, self.device)
+            vals = torch.full((64,), flag_rebase_value(int(self.ctrl[0].item())), dtype=torch.int32)
+            vals[FLAG_COUNTER_WORD] = 0
+            flags.copy_(vals.to(self.device))
         torch.cuda.synchronize()
         self.comm.barrier()                   # nobody sends before every buffer is clean
         self.scrubs = getattr(self, "scrubs", 0) + 1
@@ -177,6 +185,16 @@ class PeerComm:
         for p in self._local:
             lib.ti_symm_free(ctypes.c_void_p(p))
         self._local = []
+
+
+FLAG_COUNTER_WORD = 16      # 2 * kMaxRanks in ops/csrc/fused_ar.cu: finished blocks of the two-shot reduce kernel
+
+
+def flag_rebase_value(step: int) -> int:
+    """The int32 bit pattern of step * 65536: the largest value every tag of this and of later steps (step * 65536 +
+    position + 1, modulo 2^32) still counts as 'not reached'."""
+    v = (step * 65536) & 0xFFFFFFFF
+    return v - (1 << 32) if v >= (1 << 31) else v
 
 
 class _PtrOwner:
