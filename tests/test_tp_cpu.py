@@ -132,6 +132,11 @@ llm = LLM("preset:tiny-hybrid-tp", device="cpu", quantization="bf16", num_kvcach
 out = llm.generate_token_ids([p], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
 if llm.comm.rank == 0:
     print("RESULT", json.dumps(out))
+import torch.distributed as dist
+llm.close()                                  # the engine made the process group, so it also takes it down
+assert not dist.is_initialized()
+llm.close()
+print("CLOSED", flush=True)
 ''' % ROOT
     path = tmp_path / "tp2_gloo.py"
     path.write_text(script)
@@ -141,6 +146,7 @@ if llm.comm.rank == 0:
                        capture_output=True, text=True, env=env, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
     line = [l for l in r.stdout.splitlines() if l.startswith("RESULT")][0]
+    assert r.stdout.count("CLOSED") == 2
     got = json.loads(line[7:])
     g = torch.Generator().manual_seed(1)
     p = torch.randint(0, 1023, (21,), generator=g).tolist()
