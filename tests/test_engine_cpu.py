@@ -90,3 +90,18 @@ def test_close_is_idempotent_and_cli_runs_through_it(capsys):
     out = run_engine.main(["--model", "preset:tiny-hybrid", "--device", "cpu", "--prompt", "hi", "--max-tokens", "3",
                            "--temperature", "0"])
     assert isinstance(out["text"], str)
+
+
+def test_optimisation_benchmark_runs_on_the_cpu_executor():
+    """`benchmarks/bench_optimizations.py` (one process per variant, public API only) produces its JSON rows."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "benchmarks", "bench_optimizations.py"), "--model", "preset:tiny-hybrid",
+                        "--device", "cpu", "--quick"], capture_output=True, text=True, timeout=600, cwd=root)
+    rows = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert r.returncode == 0 and len(rows) == 2, (r.stdout[-500:], r.stderr[-1500:])
+    assert all("error" not in x and x["decode_tok_s"] > 0 and x["prefill_tok_s"] > 0 for x in rows)
+    assert rows[0]["variant"] == "default" and rows[0]["decode_vs_default"] == 1.0
