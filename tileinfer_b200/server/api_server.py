@@ -236,7 +236,12 @@ def main(argv=None):
     llm = LLM(args.model, **engine_kwargs(args))
     if llm.comm.rank == 0:
         print(f"serving {args.model} on http://{args.host}:{args.port}", flush=True)
-    serve(llm, args.host, args.port)
+    try:
+        serve(llm, args.host, args.port)
+    except KeyboardInterrupt:
+        pass
+    finally:
+        llm.close()         # every rank gets here: the workers leave their loop when rank 0 shuts them down
 
 
 if __name__ == "__main__":
